@@ -1,0 +1,584 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c4|c3|c2|c1]
+    python bench.py --impl reference ...        # the CPU restatement, host cores
+
+One JSON line on stdout (rank 0).  The default workload is the large causal
+prefill (batch 64 x seq 8192 x 8 heads x 128, f16), reported as TFLOP/s against
+the measured tensor-core peak; the long-context decode (batch 512, KV 8192,
+8 x 52, f16) rides along under "decode" as HBM GB/s against the measured copy
+bandwidth.  Work is counted algorithmically: 4*hd FLOPs per visible
+(query, key) pair per query head for prefill; visible K and V rows + q + out for
+decode.  Inputs are seeded synthetic tensors of the named shapes.
+
+With N > 1 (torchrun, one rank per GPU) the total work is fixed and sharded:
+prefill by sequences with no collective; decode by KV rows with one NCCL
+all-gather of (m, l, acc) partials and a merge.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p["bf16_tflops"],
+                    tflops_sustained=p.get("bf16_tflops_sustained"), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+def load_traffic():
+    """Per-launch DRAM traffic figures taken from committed ncu captures."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    return json.load(open(path)) if os.path.exists(path) else {}
+
+
+# ----------------------------------------------------------------------------
+# workloads
+# ----------------------------------------------------------------------------
+
+CONFIGS = {
+    "c1": dict(kind="prefill", name="minilm_bidirectional_f32", dtype="f32", batch=8, seq=128,
+               qHeads=12, kvHeads=12, hd=32, lens=(16, 128), wl=None, wr=None, sigma=1.0,
+               fold=32 ** -0.25, layers=6),
+    "c3": dict(kind="prefill", name="embeddinggemma_gqa_prefill_f16", dtype="f16", batch=32,
+               seq=2048, qHeads=3, kvHeads=1, hd=256, lens=(512, 2048), wl=512, wr=512, sigma=0.5,
+               fold=1.0, layers=6),
+    "c5": dict(kind="prefill", name="causal_prefill_f16_b64_s8192_h8_d128", dtype="f16", batch=64,
+               seq=8192, qHeads=8, kvHeads=8, hd=128, lens=None, wl=None, wr=0, sigma=1.0,
+               fold=128 ** -0.25, layers=1),
+    "c2": dict(kind="decode", name="moonshine_tiny_decode_step_f16", dtype="f16", batch=64,
+               cacheRows=448, qHeads=8, kvHeads=8, hd=36, lens=(1, 448), cross=200),
+    "c4": dict(kind="decode", name="moonshine_base_long_decode_f16_b512_kv8192", dtype="f16",
+               batch=512, cacheRows=8192, qHeads=8, kvHeads=8, hd=52, lens=None, cross=0),
+}
+
+
+def visible_pairs(L, wl, wr):
+    """Visible (query, key) pairs of one sequence of length L under a window."""
+    if wl is None and wr is None:
+        return L * L
+    total = 0
+    lo_w = L if wl is None else wl
+    hi_w = L if wr is None else wr
+    # sum over i of (min(i+hi_w, L-1) - max(i-lo_w, 0) + 1), closed form by loop (L <= 8192)
+    for i in range(L):
+        total += min(i + hi_w, L - 1) - max(i - lo_w, 0) + 1
+    return total
+
+
+class Prefill:
+    def __init__(self, cfg, rank, world, ex, layer=0):
+        import torch
+        self.cfg, self.ex, self.torch = cfg, ex, torch
+        b = cfg["batch"]
+        per = b // world if b % world == 0 else -(-b // world)
+        self.b0, self.b1 = min(rank * per, b), min((rank + 1) * per, b)
+        self.nb = self.b1 - self.b0
+        S, hd = cfg["seq"], cfg["hd"]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        tdt = torch.float16 if cfg["dtype"] == "f16" else torch.float32
+        gl = torch.Generator(device="cpu").manual_seed(4242 + layer)
+        if cfg["lens"]:
+            lens = torch.randint(cfg["lens"][0], cfg["lens"][1] + 1, (b,), generator=gl)
+        else:
+            lens = torch.full((b,), S, dtype=torch.int64)
+        self.lens_all = lens.tolist()
+        self.lens = lens[self.b0:self.b1].to(torch.int32).to(dev)
+        gd = torch.Generator(device=dev).manual_seed(1000 + 17 * rank + layer)
+        rows = max(self.nb, 1) * S
+        f = cfg["fold"] * cfg["sigma"]
+        self.q = (torch.randn(rows, cfg["qHeads"] * hd, generator=gd, device=dev) * f).to(tdt)
+        self.k = (torch.randn(rows, cfg["kvHeads"] * hd, generator=gd, device=dev) * f).to(tdt)
+        self.v = (torch.randn(rows, cfg["kvHeads"] * hd, generator=gd, device=dev)
+                  * cfg["sigma"]).to(tdt)
+        self.out = torch.empty_like(self.q)
+        self.layers = cfg["layers"]
+
+    def windows(self, layer):
+        c = self.cfg
+        if c["name"].startswith("embeddinggemma") and layer % 6 == 5:
+            return None, None  # every sixth layer is global
+        return c["wl"], c["wr"]
+
+    def flops(self, layer=0, all_ranks=True):
+        c = self.cfg
+        wl, wr = self.windows(layer)
+        lens = self.lens_all if all_ranks else self.lens_all[self.b0:self.b1]
+        cache = {}
+        pairs = 0
+        for L in lens:
+            if L not in cache:
+                cache[L] = visible_pairs(L, wl, wr)
+            pairs += cache[L]
+        return 4.0 * c["hd"] * pairs * c["qHeads"]
+
+    def step(self, layer=0):
+        from runntime_b200.engine import prefill_batched
+        c = self.cfg
+        if self.nb == 0:
+            return
+        wl, wr = self.windows(layer)
+        prefill_batched(self.ex, self.q, self.k, self.v, self.out, dtype=c["dtype"], batch=self.nb,
+                        seqStride=c["seq"], seqLens=self.lens, qHeads=c["qHeads"],
+                        kvHeads=c["kvHeads"], headDim=c["hd"], windowLeft=wl, windowRight=wr)
+
+    def io_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.q, self.k, self.v)), \
+            self.out.numel() * self.out.element_size()
+
+    def make_host(self):
+        t = self.torch
+        self.hq, self.hk, self.hv = (x.cpu().pin_memory() for x in (self.q, self.k, self.v))
+        self.hout = t.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+
+    def e2e_step(self, layer=0):
+        self.q.copy_(self.hq, non_blocking=True)
+        self.k.copy_(self.hk, non_blocking=True)
+        self.v.copy_(self.hv, non_blocking=True)
+        self.step(layer)
+        self.hout.copy_(self.out, non_blocking=True)
+
+
+class Decode:
+    def __init__(self, cfg, rank, world, ex):
+        import torch
+        from runntime_b200.engine import ShardedDecode, shard_rows
+        self.cfg, self.ex, self.torch, self.world, self.rank = cfg, ex, torch, world, rank
+        dev = torch.device("cuda", torch.cuda.current_device())
+        b, hd, H = cfg["batch"], cfg["hd"], cfg["kvHeads"]
+        w = H * hd
+        self.shard_kv = cfg["lens"] is None  # long-context: split KV rows across ranks
+        gl = torch.Generator(device="cpu").manual_seed(77)
+        if self.shard_kv:
+            s, e = shard_rows(cfg["cacheRows"], world, rank)
+            self.rows = e - s
+            self.b = b
+            self.lens_all = [cfg["cacheRows"]] * b
+            self.lens = None
+        else:
+            per = -(-b // world)
+            b0, b1 = min(rank * per, b), min((rank + 1) * per, b)
+            self.b = b1 - b0
+            lens = torch.randint(cfg["lens"][0], cfg["lens"][1] + 1, (b,), generator=gl)
+            self.lens_all = lens.tolist()
+            self.lens_mine = self.lens_all[b0:b1]
+            self.lens = lens[b0:b1].to(torch.int32).to(dev)
+            self.rows = cfg["cacheRows"]
+        gd = torch.Generator(device=dev).manual_seed(2000 + rank)
+        nb = max(self.b, 1)
+        self.k = torch.randn(nb, self.rows, w, generator=gd, device=dev, dtype=torch.float16)
+        self.v = torch.randn(nb, self.rows, w, generator=gd, device=dev, dtype=torch.float16)
+        gq = torch.Generator(device=dev).manual_seed(3000)  # q is the same on every rank
+        self.q = (torch.randn(nb, cfg["qHeads"] * hd, generator=gq, device=dev)
+                  * hd ** -0.5).to(torch.float16)
+        self.out = torch.empty_like(self.q)
+        self.kNew = self.vNew = None
+        if not self.shard_kv:
+            self.kNew = torch.randn(nb, w, generator=gd, device=dev, dtype=torch.float16)
+            self.vNew = torch.randn(nb, w, generator=gd, device=dev, dtype=torch.float16)
+        if cfg["cross"]:
+            self.ck = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
+            self.cv = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
+            self.out2 = torch.empty_like(self.q)
+        self.sharded = ShardedDecode() if (self.shard_kv and world > 1) else None
+        self.partials = (torch.empty(nb * cfg["qHeads"], 2 + hd, dtype=torch.float32, device=dev)
+                         if self.sharded else None)
+
+    def bytes(self, all_ranks=True):
+        c = self.cfg
+        es = 2
+        w = c["kvHeads"] * c["hd"]
+        qo = 2 * c["qHeads"] * c["hd"] * es
+        lens = self.lens_all if (all_ranks or self.shard_kv) else self.lens_mine
+        total = 0
+        for L in lens:
+            total += 2 * L * w * es + qo
+            if not self.shard_kv:
+                total += 2 * w * es          # appended K/V row write
+            if c["cross"]:
+                total += 2 * c["cross"] * w * es + qo
+        if self.shard_kv and not all_ranks:
+            total = total * self.rows / c["cacheRows"]
+        return float(total)
+
+    def launches_per_step(self):
+        n = 1 + (1 if self.cfg["cross"] else 0)
+        return n + (1 if self.sharded else 0)
+
+    def step(self, layer=0):
+        from runntime_b200.engine import decode_batched
+        c = self.cfg
+        if self.b == 0:
+            return
+        common = dict(dtype="f16", batch=self.b, qHeads=c["qHeads"], kvHeads=c["kvHeads"],
+                      headDim=c["hd"])
+        if self.sharded:
+            self.sharded.step(self.ex, self.q, self.k, self.v, self.out, shardRows=self.rows,
+                              partials=self.partials, **common)
+            return
+        decode_batched(self.ex, self.q, self.out, self.k, self.v, cacheRows=self.rows,
+                       kvLen=max(self.lens_all) if self.lens is not None else self.rows,
+                       kvLens=self.lens, kNew=self.kNew, vNew=self.vNew, **common)
+        if c["cross"]:
+            decode_batched(self.ex, self.q, self.out2, self.ck, self.cv, cacheRows=c["cross"],
+                           kvLen=c["cross"], **common)
+
+    def io_bytes(self):
+        n = self.q.numel() * 2
+        if self.kNew is not None:
+            n += 2 * self.kNew.numel() * 2
+        return n, self.out.numel() * 2
+
+    def make_host(self):
+        # A decode step's inputs are the new token's q (and K/V row); the cache is
+        # device-resident state, as it is in the reference's decoder loop.
+        self.hq = self.q.cpu().pin_memory()
+        self.hout = self.torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+        if self.kNew is not None:
+            self.hkn, self.hvn = self.kNew.cpu().pin_memory(), self.vNew.cpu().pin_memory()
+
+    def e2e_step(self, layer=0):
+        self.q.copy_(self.hq, non_blocking=True)
+        if self.kNew is not None:
+            self.kNew.copy_(self.hkn, non_blocking=True)
+            self.vNew.copy_(self.hvn, non_blocking=True)
+        self.step(layer)
+        self.hout.copy_(self.out, non_blocking=True)
+
+
+# ----------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------
+# CPU baseline (the oracle's shader-order f32 loop on the host cores)
+# ----------------------------------------------------------------------------
+
+def cpu_sample(key, budget_s=12.0):
+    """Times the CPU restatement on a bounded slice of the workload and returns
+    (metric value, cores, description).  This is the one place the benchmark
+    executes oracle code, and only as the reported CPU baseline."""
+    import numpy as np
+    import oracle
+    cfg = CONFIGS[key]
+    rng = np.random.default_rng(5)
+    cores = oracle.num_threads()
+    if cfg["kind"] == "prefill":
+        hd = cfg["hd"]
+        npdt = np.float16 if cfg["dtype"] == "f16" else np.float32
+        if key == "c5":
+            S, heads = 2048, 1
+            sample = "1 sequence x 1 head, causal, first 2048 positions of 8192"
+        elif key == "c3":
+            S, heads = 2048, 3
+            sample = "1 sequence of 2048 x 3 q heads, window +-512"
+        else:
+            S, heads = cfg["seq"], cfg["qHeads"]
+            sample = f"1 sequence of {S} x {heads} heads"
+        kvh = max(1, heads * cfg["kvHeads"] // cfg["qHeads"])
+        q = (rng.standard_normal((S, heads * hd)) * cfg["fold"]).astype(npdt)
+        k = (rng.standard_normal((S, kvh * hd)) * cfg["fold"]).astype(npdt)
+        v = rng.standard_normal((S, kvh * hd)).astype(npdt)
+        kw = dict(qHeads=heads, kvHeads=kvh, headDim=hd,
+                  windowLeft=math.inf if cfg["wl"] is None else cfg["wl"],
+                  windowRight=math.inf if cfg["wr"] is None else cfg["wr"])
+        flops = 4.0 * hd * visible_pairs(S, cfg["wl"], cfg["wr"]) * heads
+        oracle.sdpa_rows(q[:64], k[:64], v[:64], **kw)  # warm the thread pool
+        n, t0 = 0, time.perf_counter()
+        while True:
+            oracle.sdpa_rows(q, k, v, **kw)
+            n += 1
+            if time.perf_counter() - t0 > budget_s or n >= 50:
+                break
+        dt = (time.perf_counter() - t0) / n
+        return flops / dt / 1e12, cores, f"{sample}; {n} passes of {dt * 1e3:.1f} ms", dt * 1e3
+    # decode: a few sequences, each a 1-row attention over its cache
+    hd, H = cfg["hd"], cfg["qHeads"]
+    nseq = 8 if key == "c4" else 64
+    L = cfg["cacheRows"]
+    q = (rng.standard_normal((nseq, 1, H * hd)) / math.sqrt(hd)).astype(np.float16)
+    k = rng.standard_normal((nseq, L, H * hd)).astype(np.float16)
+    v = rng.standard_normal((nseq, L, H * hd)).astype(np.float16)
+    kw = dict(qHeads=H, kvHeads=H, headDim=hd, windowRight=0, qPosOffset=L - 1)
+    nbytes = nseq * (2 * L * H * hd * 2 + 2 * H * hd * 2)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        for s in range(nseq):
+            oracle.sdpa_rows(q[s], k[s], v[s], **kw)
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 200:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return (nbytes / dt / 1e9, cores, f"{nseq} of {cfg['batch']} sequences, full {L}-row caches; "
+            f"{n} passes of {dt * 1e3:.1f} ms", dt * 1e3)
+
+
+def run_reference(args):
+    """--impl reference: the CPU restatement of the reference's shader math on
+    the host cores (the reference's own WebGPU path cannot run here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    key = args.workload
+    cfg = CONFIGS[key]
+    vals, mss = [], []
+    desc, cores = "", 1
+    for i in range(args.warmup + args.steps):
+        val, cores, desc, ms = cpu_sample(key, budget_s=max(2.0, 60.0 / (args.warmup + args.steps)))
+        if i >= args.warmup:
+            vals.append(val)
+            mss.append(ms)
+    value = statistics.mean(vals)
+    unit = "TFLOP/s" if cfg["kind"] == "prefill" else "GB/s"
+    line = {
+        "impl": "reference", "metric": metric_name(cfg), "value": value, "unit": unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": statistics.mean(mss),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": cfg["dtype"], "data": "synthetic",
+        "config": {"workload": cfg["name"], "note": "CPU restatement of the reference's shader "
+                   "math (oracle port) on host cores; each step is a bounded sample"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port",
+                         "sample": desc},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(cfg):
+    return "prefill_attn_tflops" if cfg["kind"] == "prefill" else "decode_attn_hbm_gbs"
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+
+def timed(torch, dist, world, fn, steps, warmup, flush=None):
+    """W warm-ups, then K timed steps bracketed by barrier + sync; returns the
+    max over ranks of the device time in ms (CUDA events on the launch stream)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    total = 0.0
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        total = e0.elapsed_time(e1)
+    else:
+        for i in range(steps):
+            flush()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([total], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total = float(t.item())
+    return total
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import runntime_b200 as rt
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ex = rt.CudaExecutor(local)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    peaks = load_peaks()
+    traffic = load_traffic()
+
+    def measure(key, steps, warmup, with_e2e):
+        cfg = CONFIGS[key]
+        wl = (Prefill if cfg["kind"] == "prefill" else Decode)(cfg, rank, world, ex)
+        layers = cfg.get("layers", 1)
+        small = key in ("c1", "c2")
+        flushbuf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if small else None
+        flush = (lambda: flushbuf.fill_(1)) if small else None
+        sampler = ClockSampler(local) if rank == 0 else None
+        n0 = ex.launchCount()
+        if sampler:
+            sampler.start()
+        ms = timed(torch, dist, world, lambda i: wl.step(i % layers), steps, warmup, flush)
+        clocks = sampler.stop() if sampler else None
+        ex.sync()
+        launches = (ex.launchCount() - n0) * steps // (steps + warmup)
+        if cfg["kind"] == "prefill":
+            work = sum(wl.flops(i % layers) for i in range(steps))
+            value, unit = work / (ms * 1e-3) / 1e12, "TFLOP/s"
+            peak, bound = peaks["tflops"], "tensor"
+            per_launch_local = sum(wl.flops(i % layers, all_ranks=False) for i in range(steps)) / steps
+        else:
+            work = wl.bytes() * steps
+            value, unit = work / (ms * 1e-3) / 1e9, "GB/s"
+            peak, bound = peaks["hbm_gbs"], "hbm"
+            per_launch_local = wl.bytes(all_ranks=False)
+        # roofline of the dominant kernel on this rank: its algorithmic work / its launch time
+        achieved = per_launch_local / (ms / steps * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+        res = {
+            "metric": metric_name(cfg), "value": value, "unit": unit, "ms_per_step": ms / steps,
+            "dtype": cfg["dtype"], "workload": cfg["name"],
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
+                         "frac": achieved / peak, "traffic": traffic.get(key),
+                         "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else "")},
+            "clocks": clocks, "gpu_launches": launches,
+            "l2": "256 MB flush between timed steps" if small else "inputs larger than L2",
+        }
+        if with_e2e:
+            wl.make_host()
+            h2d, d2h = wl.io_bytes()
+            e_steps = max(2, min(steps, 3)) if not small else steps
+            ems = timed(torch, dist, world, lambda i: wl.e2e_step(i % layers), e_steps, 1)
+            if cfg["kind"] == "prefill":
+                ework = sum(wl.flops(i % layers) for i in range(e_steps))
+                evalue = ework / (ems * 1e-3) / 1e12
+            else:
+                evalue = wl.bytes() * e_steps / (ems * 1e-3) / 1e9
+            res["e2e"] = {"value": evalue, "unit": unit, "h2d_bytes_per_step": h2d,
+                          "d2h_bytes_per_step": d2h, "ms_per_step": ems / e_steps}
+        del wl
+        torch.cuda.empty_cache()
+        return res
+
+    key = args.workload
+    cfg = CONFIGS[key]
+    main = measure(key, args.steps, args.warmup, True)
+    extra = None
+    if key == "c5" and not args.no_decode:
+        extra = measure("c4", max(args.steps, 5), max(args.warmup, 3), True)
+
+    if rank == 0:
+        line = {
+            "metric": main["metric"], "value": main["value"], "unit": main["unit"],
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": main["dtype"], "data": "synthetic",
+            "config": {"workload": cfg["name"], "l2": main["l2"],
+                       "parallelism": ("sequences sharded over ranks, no collective"
+                                       if cfg["kind"] == "prefill" else
+                                       "KV rows sharded over ranks, one all-gather of partials"
+                                       if cfg.get("lens") is None else "sequences sharded over ranks")},
+            "roofline": main["roofline"], "clocks": main["clocks"],
+            "e2e": main["e2e"], "gpu_launches": main["gpu_launches"],
+        }
+        if world == 1 and not args.no_cpu:
+            v, cores, desc, _ = cpu_sample(key)
+            line["cpu_baseline"] = {"value": v, "unit": main["unit"], "cores": cores,
+                                    "kind": "port", "sample": desc}
+        if extra:
+            line["decode"] = {k: extra[k] for k in ("metric", "value", "unit", "ms_per_step",
+                                                    "workload", "roofline", "e2e", "gpu_launches",
+                                                    "clocks")}
+            if world == 1 and not args.no_cpu:
+                v, cores, desc, _ = cpu_sample("c4", budget_s=6.0)
+                line["decode"]["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores,
+                                                  "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    ex.dispose()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c5", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode rider of c5")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

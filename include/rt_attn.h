@@ -1,0 +1,208 @@
+/* rt_attn.h — C ABI of the B200 attention library (librt_attn.so).
+ *
+ * This is the boundary a host runtime binds (N-API, ctypes, cgo ...): plain
+ * pointers, sizes and status codes.  Every pointer named "device" is a CUDA
+ * device address on the context's GPU; they stand where the reference holds
+ * GPUBuffer handles.  All work is enqueued on the context's stream in call
+ * order (the reference relies on in-pass dispatch order the same way,
+ * packages/runntime/src/core/kernels/attention/attnDecode.ts:228-235); only
+ * rt_sync and rt_buf_download wait for the device.
+ *
+ * Every function returns an rt_status.  On failure rt_last_error() gives the
+ * message; argument errors are detected before anything is enqueued.  A
+ * context is to be used from one thread at a time.
+ */
+#ifndef RT_ATTN_H
+#define RT_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define RT_API __attribute__((visibility("default")))
+#else
+#define RT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes, one per entry of the reference's RUNNTIME_ERROR_CODES
+ * (packages/runntime/src/core/error.ts:4-21), in the same order, after RT_OK. */
+typedef enum {
+  RT_OK = 0,
+  RT_LOAD_FAILED = 1,
+  RT_LOAD_ABORTED = 2,
+  RT_CHECKPOINT_MISMATCH = 3,
+  RT_UNSUPPORTED_DEVICE = 4,
+  RT_EXECUTION_FAILED = 5,
+  RT_INVALID_ARGUMENT = 6,
+  RT_RESOURCE_DISPOSED = 7,
+  RT_NOT_INITIALIZED = 8
+} rt_status;
+
+/* Storage element types (packages/runntime/src/core/kernels/elem.ts:1-6);
+ * accumulation and softmax state are always f32.  f16 is raw IEEE halfwords. */
+typedef enum { RT_F32 = 0, RT_F16 = 1 } rt_dtype;
+
+/* Finite stand-in for an unbounded window side
+ * (packages/runntime/src/core/graph/ops/shared.ts:37). */
+#define RT_WINDOW_INF 0x3fffffff
+
+typedef struct rt_ctx rt_ctx;
+
+/* ---- context: replaces initRuntime/gpuExecutor/dispose --------------------
+ * (packages/runntime/src/core/gpu/eval.ts:80-88,135,274-283).  Owns a stream
+ * and the split-KV scratch, which grows monotonically like the executor's
+ * scratch (eval.ts:194-203).  After rt_ctx_destroy every use of the handle is
+ * an error (RT_RESOURCE_DISPOSED is returned while the handle's memory is
+ * still recognisable; do not rely on it). */
+RT_API int rt_ctx_create(int device, rt_ctx** out);
+RT_API int rt_ctx_destroy(rt_ctx* ctx);
+/* external != 0: enqueue on the caller's stream `cuda_stream` (a cudaStream_t;
+ * NULL is the legacy default stream) instead of the context's own, so that
+ * the library's kernels order with the caller's other work.  external == 0
+ * restores the context's stream. */
+RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
+/* Message of the last failure on this context (or, with ctx == NULL, of the
+ * last failed call on this thread that had no context to record it in). */
+RT_API const char* rt_last_error(const rt_ctx* ctx);
+/* Waits for everything enqueued so far; reports asynchronous kernel status
+ * (a bounded device-side wait that ran out is RT_EXECUTION_FAILED). */
+RT_API int rt_sync(rt_ctx* ctx);
+/* Number of kernels this context has launched since creation. */
+RT_API int64_t rt_launch_count(const rt_ctx* ctx);
+
+/* ---- buffers: replace createStorageFor / writeF32 / writeF16 / readback ----
+ * (packages/runntime/src/core/gpu/buffers.ts:83-121,171-181,302-308).
+ * A zero-byte allocation is RT_INVALID_ARGUMENT, as uploading an empty tensor
+ * is in the reference (buffers.ts:108-111). */
+RT_API int rt_buf_alloc(rt_ctx* ctx, size_t bytes, void** device_ptr);
+RT_API int rt_buf_free(rt_ctx* ctx, void* device_ptr);
+RT_API int rt_buf_upload(rt_ctx* ctx, void* device_ptr, size_t offset, const void* host, size_t bytes);
+RT_API int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* host,
+                    size_t bytes);
+
+/* ---- the 'attn' op ---------------------------------------------------------
+ * One call = one pending 'attn' node of the reference; the fields are its
+ * attrs vector and inputs (packages/runntime/src/core/graph/ops/attention.ts:
+ * 122-140, 207-211) and the dispatch it replaces is attnSpec
+ * (packages/runntime/src/core/gpu/dispatch/attention.ts:45-199).
+ *
+ * Layouts, all row-major: q [qLen, qHeads*headDim], k and v
+ * [kvLen, kvHeads*headDim], out [qLen, qHeads*headDim]; with qkvPacked = 1,
+ * q == k == v point at one [qLen, (qHeads+2*kvHeads)*headDim] tensor whose
+ * column blocks are q|k|v and kvLen == qLen.  Key j is visible to row i when
+ * qPos-windowLeft <= j <= qPos+windowRight (qPos = qPosOffset+i), clipped to
+ * [segments[2i], segments[2i+1]) when segments is given.  No score scale is
+ * applied.  sinks[h]*ln2 seeds the running max with weight 1 in the
+ * denominator only.  A row that sees no key is written as zeros.
+ *
+ * Two batch extensions (zero / NULL for the plain reference op):
+ *   seqStride > 0 with seqLens != NULL: rows are `batch` sequences of
+ *   seqStride rows back to back (qLen == kvLen == batch*seqStride); row r of
+ *   sequence b = r / seqStride sees only keys [b*seqStride, b*seqStride +
+ *   seqLens[b]) and rows at or past seqLens[b] are written as zeros.  This is
+ *   the segments form computed on the fly; segments must then be NULL.
+ */
+typedef struct {
+  const void* q;          /* device */
+  const void* k;          /* device */
+  const void* v;          /* device */
+  void* out;              /* device */
+  const float* sinks;     /* device [qHeads] or NULL */
+  const float* segments;  /* device [qLen, 2] f32 or NULL */
+  int32_t dtype;          /* rt_dtype of q, k, v and out */
+  int32_t qkvPacked;
+  int64_t qLen;
+  int64_t kvLen;
+  int32_t qHeads;
+  int32_t kvHeads;
+  int32_t headDim;
+  int32_t windowLeft;     /* RT_WINDOW_INF = unbounded */
+  int32_t windowRight;
+  int32_t maxSegment;     /* longest segment, 0 = unknown; a sizing hint only */
+  int64_t qPosOffset;
+  int32_t hasKeyBias;
+  int32_t biasStart;
+  int32_t biasEnd;
+  float biasValue;
+  int32_t seqStride;        /* batch extension, see above */
+  const int32_t* seqLens;   /* device [qLen / seqStride] or NULL */
+} rt_attn_args;
+
+/* Runs the op.  qLen == 1 takes the decode kernel (headDim <= 128, no
+ * segments, no key bias — the reference's limits, ops/attention.ts:10-12,
+ * 96-98,119-120); otherwise a prefill kernel (headDim <= 512; qkvPacked
+ * needs headDim <= 128). */
+RT_API int rt_attn(rt_ctx* ctx, const rt_attn_args* args);
+
+/* Which kernel rt_attn would run for these arguments: writes a short static
+ * name ("prefill_simt", "prefill_tc", "decode") into *route. */
+RT_API int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route);
+
+/* ---- batched single-token decode over KV caches -----------------------------
+ * The decode step of the KV-cache engine (packages/runntime/src/zoo/moonshine/
+ * decoder.ts:58-76,105-109; transcriber.ts:111-118,161-203) for `batch`
+ * independent sequences in one launch.  The reference runs one sequence per
+ * call; batch = 1 is that call.
+ *
+ * kCache/vCache: `batch` caches of [cacheRows, kvHeads*headDim] each,
+ * cacheSeqStride ELEMENTS apart.  Sequence b attends, with its single query
+ * row q[b], to cache rows [max(0, L_b-1-windowLeft), L_b-1] where
+ * L_b = kvLens[b] (or kvLen when kvLens is NULL): causal self-attention with
+ * the query at the last position, or cross-attention over all L_b rows when
+ * windowLeft is RT_WINDOW_INF.
+ *
+ * Fused append: when kNew and vNew are given ([batch, kvHeads*headDim]) the
+ * kernel first stores kNew[b]/vNew[b] into cache row L_b-1 — exactly what
+ * writeRows(cache, new, L_b-1) does (ops/shape.ts:230-259), rows past the view
+ * keep their contents — and attends to them.
+ *
+ * partialsOut != NULL: instead of `out`, writes un-normalised partials
+ * f32 [batch, qHeads, 2+headDim] = (m, l, acc) per head for a later
+ * rt_attn_merge_partials (KV-sequence sharding across GPUs); keyOffset is
+ * not needed because the softmax algebra is position-free. */
+typedef struct {
+  const void* q;          /* device [batch, qHeads*headDim] */
+  void* out;              /* device [batch, qHeads*headDim] (unused with partialsOut) */
+  void* kCache;           /* device */
+  void* vCache;           /* device */
+  const void* kNew;       /* device [batch, kvHeads*headDim] or NULL */
+  const void* vNew;       /* device or NULL (both or neither) */
+  const int32_t* kvLens;  /* device [batch] or NULL */
+  const float* sinks;     /* device [qHeads] or NULL */
+  float* partialsOut;     /* device [batch, qHeads, 2+headDim] or NULL */
+  int64_t cacheSeqStride; /* elements between consecutive sequences' caches */
+  int32_t dtype;
+  int32_t batch;
+  int32_t cacheRows;      /* capacity of each cache, rows */
+  int32_t kvLen;          /* used when kvLens == NULL */
+  int32_t qHeads;
+  int32_t kvHeads;
+  int32_t headDim;
+  int32_t windowLeft;
+  int32_t splits;         /* key splits per sequence; 0 = let the library choose */
+} rt_decode_args;
+
+RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);
+
+/* Merges `parts` sets of partials (m, l, acc) — the algebra of attnDecodeMerge
+ * (packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422) lifted
+ * across devices.  partials: f32 [parts, units, 2+headDim]; out:
+ * [units, headDim] in `dtype`.  An empty shard contributes (-1e30, 0, 0...). */
+RT_API int rt_attn_merge_partials(rt_ctx* ctx, const float* partials, int32_t parts, int64_t units,
+                           int32_t headDim, void* out, int32_t dtype);
+
+/* ---- writeRows: the KV-cache append as its own op ----------------------------
+ * dst rows [startRow, startRow+rows) = src (packages/runntime/src/core/graph/
+ * ops/shape.ts:236-259; kernel packages/runntime/src/core/kernels/shape/
+ * rows.ts:143-162).  dst is caller-owned and never freed by the library. */
+RT_API int rt_kv_append(rt_ctx* ctx, void* dst, const void* src, int64_t startRow, int64_t rows,
+                 int64_t cols, int64_t dstRows, int32_t dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RT_ATTN_H */

@@ -1,0 +1,21 @@
+"""runntime_b200 — the attention hot path of ruNNtime as hand-written sm_100a
+CUDA behind the runtime's own operator API.
+
+``sdpa``, ``sdpaPacked``, ``writeRows`` and ``MultiHeadAttention`` keep the
+reference's names, options and errors; ``CudaExecutor`` + ``evalValues`` /
+``toArray`` stand where its WebGPU executor does.  ``engine`` holds the batched
+entry points (padded-batch prefill, batched KV-cache decode, KV-sequence
+sharded decode).  Everything computes through librt_attn.so (include/rt_attn.h);
+there is no CPU path.
+"""
+from .errors import RUNNTIME_ERROR_CODES, RunntimeError
+from .executor import CudaExecutor, evalValues, gpuExecutor, toArray
+from .nn import MultiHeadAttention, Parameter
+from .ops import sdpa, sdpaPacked, writeRows
+from .value import DeviceBuffer, Value, ValueMeta, materialized, matrix, pending
+
+__all__ = [
+    "RUNNTIME_ERROR_CODES", "RunntimeError", "CudaExecutor", "gpuExecutor", "evalValues",
+    "toArray", "MultiHeadAttention", "Parameter", "sdpa", "sdpaPacked", "writeRows",
+    "DeviceBuffer", "Value", "ValueMeta", "materialized", "matrix", "pending",
+]

@@ -1,0 +1,506 @@
+// The C ABI: context, buffers, argument validation and kernel routing.
+// Declarations and the reference interfaces they replace are in rt_attn.h.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+struct rt_ctx {
+  uint32_t magic;
+  int device;
+  int smCount;
+  cudaStream_t own;
+  cudaStream_t stream;
+  float* scratch;
+  size_t scratchBytes;
+  unsigned* counters;
+  size_t counterCount;
+  int* statusDev;
+  int64_t launches;
+  std::string err;
+};
+
+namespace {
+
+constexpr uint32_t kLive = 0x52544358u;  // 'RTCX'
+constexpr uint32_t kDead = 0x44454144u;  // 'DEAD'
+
+thread_local std::string tlsError;
+
+// Disposed contexts stay allocated (a few dozen bytes each) so that a late use
+// of the handle is recognised instead of touching freed memory.
+std::mutex gGraveyardMutex;
+std::vector<rt_ctx*> gGraveyard;
+
+int fail(rt_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx && ctx->magic == kLive) ctx->err = buf;
+  tlsError = buf;
+  return code;
+}
+
+int enter(rt_ctx* ctx) {
+  if (!ctx) return fail(nullptr, RT_NOT_INITIALIZED, "no context: call rt_ctx_create first");
+  if (ctx->magic == kDead) return fail(nullptr, RT_RESOURCE_DISPOSED, "context was destroyed");
+  if (ctx->magic != kLive) return fail(nullptr, RT_INVALID_ARGUMENT, "not a context handle");
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess)
+    return fail(ctx, RT_EXECUTION_FAILED, "cudaSetDevice(%d): %s", ctx->device,
+                cudaGetErrorString(e));
+  return RT_OK;
+}
+
+#define RT_ENTER(ctx)                     \
+  do {                                    \
+    int _s = enter(ctx);                  \
+    if (_s != RT_OK) return _s;           \
+  } while (0)
+
+#define RT_CUDA(ctx, call)                                                              \
+  do {                                                                                  \
+    cudaError_t _e = (call);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return fail(ctx, RT_EXECUTION_FAILED, "%s: %s", #call, cudaGetErrorString(_e));   \
+  } while (0)
+
+const char* dtype_name(int d) { return d == RT_F16 ? "f16" : "f32"; }
+int elem_size(int d) { return d == RT_F16 ? 2 : 4; }
+
+int ensure_scratch(rt_ctx* ctx, size_t bytes, size_t counters) {
+  if (bytes > ctx->scratchBytes) {
+    // The old block may still be read by enqueued work.
+    RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch) RT_CUDA(ctx, cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratchBytes = 0;
+    size_t want = bytes + bytes / 2;
+    RT_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
+    ctx->scratchBytes = want;
+  }
+  if (counters > ctx->counterCount) {
+    RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->counters) RT_CUDA(ctx, cudaFree(ctx->counters));
+    ctx->counters = nullptr;
+    ctx->counterCount = 0;
+    size_t want = counters * 2;
+    RT_CUDA(ctx, cudaMalloc(&ctx->counters, want * sizeof(unsigned)));
+    RT_CUDA(ctx, cudaMemsetAsync(ctx->counters, 0, want * sizeof(unsigned), ctx->stream));
+    ctx->counterCount = want;
+  }
+  return RT_OK;
+}
+
+// Argument rules of the 'attn' op; messages follow
+// packages/runntime/src/core/graph/ops/attention.ts:45-121,160-205.
+int validate_attn(rt_ctx* ctx, const rt_attn_args* a) {
+  const char* op = a->qkvPacked ? "sdpaPacked" : "sdpa";
+  if (!a->q || !a->k || !a->v || !a->out)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: q, k, v and out must be device pointers", op);
+  if (a->dtype != RT_F32 && a->dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: dtype %d is neither f32 nor f16", op, a->dtype);
+  if (a->qLen < 1 || a->kvLen < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: empty tensor (qLen %lld, kvLen %lld)", op,
+                (long long)a->qLen, (long long)a->kvLen);
+  if (a->headDim < 1 || a->qHeads < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: qHeads %d and headDim %d must be positive", op,
+                a->qHeads, a->headDim);
+  if (a->kvHeads <= 0 || a->qHeads % a->kvHeads != 0)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: qHeads %d not divisible by kvHeads %d", op,
+                a->qHeads, a->kvHeads);
+  if (a->qHeads > 65535)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: qHeads %d exceeds 65535", op, a->qHeads);
+  if (a->qkvPacked) {
+    if (a->headDim > 128)
+      return fail(ctx, RT_INVALID_ARGUMENT, "sdpaPacked: headDim %d exceeds the kernel's max (128)",
+                  a->headDim);
+    if (a->qLen == 1)
+      return fail(ctx, RT_INVALID_ARGUMENT,
+                  "sdpaPacked: qLen must be > 1 (decode has no packed route)");
+    if (a->kvLen != a->qLen || a->k != a->q || a->v != a->q)
+      return fail(ctx, RT_INVALID_ARGUMENT,
+                  "sdpaPacked: q, k and v must be the one packed tensor and kvLen == qLen");
+    if (a->hasKeyBias)
+      return fail(ctx, RT_INVALID_ARGUMENT, "sdpaPacked: no key bias on the packed form");
+  }
+  const int maxHd = a->qLen == 1 ? 128 : 512;
+  if (a->headDim > maxHd)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: headDim %d exceeds the kernel's max (%d)", op,
+                a->headDim, maxHd);
+  if (a->windowLeft < 0 || a->windowLeft > RT_WINDOW_INF)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "%s: windowLeft %d must be a non-negative integer or Infinity", op, a->windowLeft);
+  if (a->windowRight < 0 || a->windowRight > RT_WINDOW_INF)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "%s: windowRight %d must be a non-negative integer or Infinity", op,
+                a->windowRight);
+  if (a->qPosOffset < 0)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: qPosOffset %lld must be a non-negative integer", op,
+                (long long)a->qPosOffset);
+  if (a->windowRight != RT_WINDOW_INF && a->qPosOffset + a->qLen > a->kvLen)
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s: qPosOffset+qLen %lld exceeds key rows kvLen %lld", op,
+                (long long)(a->qPosOffset + a->qLen), (long long)a->kvLen);
+  if (a->segments && a->qLen == 1)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "sdpa: segments need qLen > 1 (decode has no segment route)");
+  if (a->maxSegment != 0) {
+    if (!a->segments) return fail(ctx, RT_INVALID_ARGUMENT, "%s: maxSegment needs segments", op);
+    if (a->maxSegment < 1)
+      return fail(ctx, RT_INVALID_ARGUMENT, "%s: maxSegment %d must be a positive integer", op,
+                  a->maxSegment);
+  }
+  if (a->hasKeyBias) {
+    if (a->biasStart < 0 || a->biasStart > a->biasEnd || a->biasEnd > a->kvLen)
+      return fail(ctx, RT_INVALID_ARGUMENT, "sdpa: keyBias keys [%d, %d) must lie within the %lld keys",
+                  a->biasStart, a->biasEnd, (long long)a->kvLen);
+    if (!(a->biasValue - a->biasValue == 0.f))
+      return fail(ctx, RT_INVALID_ARGUMENT, "sdpa: keyBias value %f must be finite",
+                  (double)a->biasValue);
+    if (a->qLen == 1)
+      return fail(ctx, RT_INVALID_ARGUMENT,
+                  "sdpa: keyBias needs qLen > 1 (decode has no key bias route)");
+  }
+  if (a->seqStride != 0 || a->seqLens) {
+    if (a->seqStride < 1 || !a->seqLens)
+      return fail(ctx, RT_INVALID_ARGUMENT, "%s: seqStride and seqLens go together", op);
+    if (a->segments)
+      return fail(ctx, RT_INVALID_ARGUMENT, "%s: seqLens and segments are exclusive", op);
+    if (a->kvLen != a->qLen || a->qLen % a->seqStride != 0)
+      return fail(ctx, RT_INVALID_ARGUMENT,
+                  "%s: the batched form needs qLen == kvLen == batch*seqStride", op);
+  }
+  return RT_OK;
+}
+
+rt::AttnParams to_params(const rt_attn_args* a) {
+  rt::AttnParams p{};
+  const int es = elem_size(a->dtype);
+  const int64_t qw = (int64_t)a->qHeads * a->headDim, kvw = (int64_t)a->kvHeads * a->headDim;
+  p.q = a->q;
+  p.out = a->out;
+  if (a->qkvPacked) {
+    p.qStride = p.kvStride = qw + 2 * kvw;
+    p.k = static_cast<const char*>(a->q) + qw * es;
+    p.v = static_cast<const char*>(a->q) + (qw + kvw) * es;
+  } else {
+    p.qStride = qw;
+    p.kvStride = kvw;
+    p.k = a->k;
+    p.v = a->v;
+  }
+  p.sinks = a->sinks;
+  p.segs = a->segments;
+  p.seqLens = a->seqLens;
+  p.seqStride = a->seqStride;
+  p.qLen = a->qLen;
+  p.kvLen = a->kvLen;
+  p.qPosOffset = a->qPosOffset;
+  p.qHeads = a->qHeads;
+  p.kvHeads = a->kvHeads;
+  p.hd = a->headDim;
+  p.wl = a->windowLeft;
+  p.wr = a->windowRight;
+  p.hasKeyBias = a->hasKeyBias;
+  p.biasStart = a->biasStart;
+  p.biasEnd = a->biasEnd;
+  p.biasValue = a->biasValue;
+  p.maxSegment = a->maxSegment;
+  return p;
+}
+
+int run_decode(rt_ctx* ctx, rt::DecodeParams& p, int dtype) {
+  std::string err;
+  if (!rt::plan_decode(p, dtype, ctx->smCount, &err))
+    return fail(ctx, RT_INVALID_ARGUMENT, "%s", err.c_str());
+  const int zBlocks = (p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
+  if (p.splits > 1) {
+    const size_t bytes = (size_t)p.batch * p.splits * p.qHeads * (2 + p.hd) * sizeof(float);
+    int s = ensure_scratch(ctx, bytes, (size_t)p.batch * zBlocks);
+    if (s != RT_OK) return s;
+  }
+  p.scratch = ctx->scratch;
+  p.counters = ctx->counters;
+  p.status = ctx->statusDev;
+  RT_CUDA(ctx, rt::launch_decode(p, dtype, ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rt_ctx_create(int device, rt_ctx** out) {
+  if (!out) return fail(nullptr, RT_INVALID_ARGUMENT, "rt_ctx_create: out is NULL");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(nullptr, RT_UNSUPPORTED_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= count)
+    return fail(nullptr, RT_INVALID_ARGUMENT, "device %d out of range (%d devices)", device, count);
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess)
+    return fail(nullptr, RT_UNSUPPORTED_DEVICE, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return fail(nullptr, RT_UNSUPPORTED_DEVICE,
+                "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                prop.minor);
+  rt_ctx* ctx = new rt_ctx();
+  ctx->magic = kLive;
+  ctx->device = device;
+  ctx->smCount = prop.multiProcessorCount;
+  ctx->scratch = nullptr;
+  ctx->scratchBytes = 0;
+  ctx->counters = nullptr;
+  ctx->counterCount = 0;
+  ctx->launches = 0;
+  if ((e = cudaSetDevice(device)) != cudaSuccess ||
+      (e = cudaStreamCreateWithFlags(&ctx->own, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaMalloc(&ctx->statusDev, sizeof(int))) != cudaSuccess ||
+      (e = cudaMemset(ctx->statusDev, 0, sizeof(int))) != cudaSuccess) {
+    delete ctx;
+    return fail(nullptr, RT_EXECUTION_FAILED, "context setup: %s", cudaGetErrorString(e));
+  }
+  ctx->stream = ctx->own;
+  *out = ctx;
+  return RT_OK;
+}
+
+int rt_ctx_destroy(rt_ctx* ctx) {
+  RT_ENTER(ctx);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->counters) cudaFree(ctx->counters);
+  cudaFree(ctx->statusDev);
+  cudaStreamDestroy(ctx->own);
+  ctx->scratch = nullptr;
+  ctx->counters = nullptr;
+  ctx->statusDev = nullptr;
+  ctx->magic = kDead;
+  std::lock_guard<std::mutex> lock(gGraveyardMutex);
+  gGraveyard.push_back(ctx);
+  return RT_OK;
+}
+
+int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
+  RT_ENTER(ctx);
+  ctx->stream = external ? static_cast<cudaStream_t>(cuda_stream) : ctx->own;
+  return RT_OK;
+}
+
+const char* rt_last_error(const rt_ctx* ctx) {
+  if (ctx && ctx->magic == kLive) return ctx->err.c_str();
+  return tlsError.c_str();
+}
+
+int rt_sync(rt_ctx* ctx) {
+  RT_ENTER(ctx);
+  RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  int status = 0;
+  RT_CUDA(ctx, cudaMemcpy(&status, ctx->statusDev, sizeof(int), cudaMemcpyDeviceToHost));
+  if (status != 0) {
+    cudaMemset(ctx->statusDev, 0, sizeof(int));
+    return fail(ctx, RT_EXECUTION_FAILED,
+                "a kernel reported status 0x%x (%s)", status,
+                (status & rt::kStatusWaitTimeout) ? "a bounded device-side wait ran out"
+                                                  : "inconsistent kernel state");
+  }
+  return RT_OK;
+}
+
+int64_t rt_launch_count(const rt_ctx* ctx) {
+  return (ctx && ctx->magic == kLive) ? ctx->launches : -1;
+}
+
+int rt_buf_alloc(rt_ctx* ctx, size_t bytes, void** device_ptr) {
+  RT_ENTER(ctx);
+  if (!device_ptr) return fail(ctx, RT_INVALID_ARGUMENT, "rt_buf_alloc: device_ptr is NULL");
+  *device_ptr = nullptr;
+  if (bytes == 0) return fail(ctx, RT_INVALID_ARGUMENT, "rt_buf_alloc: empty tensor (0 bytes)");
+  RT_CUDA(ctx, cudaMalloc(device_ptr, bytes));
+  return RT_OK;
+}
+
+int rt_buf_free(rt_ctx* ctx, void* device_ptr) {
+  RT_ENTER(ctx);
+  if (!device_ptr) return RT_OK;
+  RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  RT_CUDA(ctx, cudaFree(device_ptr));
+  return RT_OK;
+}
+
+int rt_buf_upload(rt_ctx* ctx, void* device_ptr, size_t offset, const void* host, size_t bytes) {
+  RT_ENTER(ctx);
+  if (!device_ptr || !host) return fail(ctx, RT_INVALID_ARGUMENT, "rt_buf_upload: NULL pointer");
+  RT_CUDA(ctx, cudaMemcpyAsync(static_cast<char*>(device_ptr) + offset, host, bytes,
+                               cudaMemcpyHostToDevice, ctx->stream));
+  return RT_OK;
+}
+
+int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* host, size_t bytes) {
+  RT_ENTER(ctx);
+  if (!device_ptr || !host) return fail(ctx, RT_INVALID_ARGUMENT, "rt_buf_download: NULL pointer");
+  RT_CUDA(ctx, cudaMemcpyAsync(host, static_cast<const char*>(device_ptr) + offset, bytes,
+                               cudaMemcpyDeviceToHost, ctx->stream));
+  return rt_sync(ctx);
+}
+
+static const char* route_of(const rt_attn_args* a) {
+  if (a->qLen == 1) return "decode";
+  return rt::prefill_tc_supported(to_params(a), a->dtype) ? "prefill_tc" : "prefill_simt";
+}
+
+int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
+  RT_ENTER(ctx);
+  if (!args || !route) return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_route: NULL argument");
+  int s = validate_attn(ctx, args);
+  if (s != RT_OK) return s;
+  *route = route_of(args);
+  return RT_OK;
+}
+
+int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
+  RT_ENTER(ctx);
+  if (!a) return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn: args is NULL");
+  int s = validate_attn(ctx, a);
+  if (s != RT_OK) return s;
+  if (a->qLen == 1) {
+    rt::DecodeParams p{};
+    p.q = a->q;
+    p.out = a->out;
+    p.kCache = const_cast<void*>(a->k);
+    p.vCache = const_cast<void*>(a->v);
+    p.sinks = a->sinks;
+    p.useRange = 1;
+    const int64_t qPos = a->qPosOffset;
+    p.lo = qPos - a->windowLeft < 0 ? 0 : qPos - a->windowLeft;
+    p.end = qPos + a->windowRight > a->kvLen - 1 ? a->kvLen - 1 : qPos + a->windowRight;
+    p.batch = 1;
+    p.kvLen = (int32_t)(a->kvLen > INT32_MAX ? INT32_MAX : a->kvLen);
+    p.qHeads = a->qHeads;
+    p.kvHeads = a->kvHeads;
+    p.hd = a->headDim;
+    p.wl = a->windowLeft;
+    p.splits = 0;
+    return run_decode(ctx, p, a->dtype);
+  }
+  const rt::AttnParams p = to_params(a);
+  if (rt::prefill_tc_supported(p, a->dtype)) {
+    std::string err;
+    cudaError_t e = rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
+    if (e != cudaSuccess)
+      return fail(ctx, RT_EXECUTION_FAILED, "prefill_tc launch: %s %s", cudaGetErrorString(e),
+                  err.c_str());
+  } else {
+    RT_CUDA(ctx, rt::launch_prefill_simt(p, a->dtype, ctx->stream));
+  }
+  ctx->launches++;
+  return RT_OK;
+}
+
+int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
+  RT_ENTER(ctx);
+  if (!a) return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: args is NULL");
+  if (!a->q || !a->kCache || !a->vCache || (!a->out && !a->partialsOut))
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "rt_attn_decode: q, kCache, vCache and out (or partialsOut) must be device pointers");
+  if (a->dtype != RT_F32 && a->dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: dtype %d is neither f32 nor f16", a->dtype);
+  if (a->batch < 1 || a->cacheRows < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: empty tensor (batch %d, cacheRows %d)",
+                a->batch, a->cacheRows);
+  if (a->batch > 65535)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: batch %d exceeds 65535", a->batch);
+  if (a->headDim < 1 || a->qHeads < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: qHeads %d and headDim %d must be positive",
+                a->qHeads, a->headDim);
+  if (a->kvHeads <= 0 || a->qHeads % a->kvHeads != 0)
+    return fail(ctx, RT_INVALID_ARGUMENT, "sdpa: qHeads %d not divisible by kvHeads %d", a->qHeads,
+                a->kvHeads);
+  if (a->headDim > 128)
+    return fail(ctx, RT_INVALID_ARGUMENT, "sdpa: headDim %d exceeds the kernel's max (128)",
+                a->headDim);
+  if (a->kvLen < 0 || a->kvLen > a->cacheRows)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "writeRows: rows [%d, %d) exceed dst capacity %d", a->kvLen - 1, a->kvLen,
+                a->cacheRows);
+  if (!a->kvLens && a->kvLen < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: kvLen %d must be positive", a->kvLen);
+  if ((a->kNew == nullptr) != (a->vNew == nullptr))
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: kNew and vNew go together");
+  if (a->windowLeft < 0 || a->windowLeft > RT_WINDOW_INF)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "sdpa: windowLeft %d must be a non-negative integer or Infinity", a->windowLeft);
+  if (a->splits < 0 || a->splits > 64)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: splits %d out of range [0, 64]",
+                a->splits);
+  if (a->cacheSeqStride < 0 ||
+      (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim))
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "rt_attn_decode: cacheSeqStride %lld is smaller than one cache",
+                (long long)a->cacheSeqStride);
+  rt::DecodeParams p{};
+  p.q = a->q;
+  p.out = a->out;
+  p.kCache = a->kCache;
+  p.vCache = a->vCache;
+  p.kNew = a->kNew;
+  p.vNew = a->vNew;
+  p.kvLens = a->kvLens;
+  p.sinks = a->sinks;
+  p.partialsOut = a->partialsOut;
+  p.cacheSeqStride = a->cacheSeqStride;
+  p.batch = a->batch;
+  p.kvLen = a->kvLens ? (a->kvLen > 0 ? a->kvLen : a->cacheRows) : a->kvLen;
+  p.qHeads = a->qHeads;
+  p.kvHeads = a->kvHeads;
+  p.hd = a->headDim;
+  p.wl = a->windowLeft;
+  p.splits = a->splits;
+  return run_decode(ctx, p, a->dtype);
+}
+
+int rt_attn_merge_partials(rt_ctx* ctx, const float* partials, int32_t parts, int64_t units,
+                           int32_t headDim, void* out, int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!partials || !out)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_merge_partials: NULL pointer");
+  if (parts < 1 || units < 1 || headDim < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "rt_attn_merge_partials: empty tensor (parts %d, units %lld, headDim %d)", parts,
+                (long long)units, headDim);
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_merge_partials: bad dtype %d", dtype);
+  RT_CUDA(ctx, rt::launch_merge_partials(partials, parts, units, headDim, out, dtype, ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
+int rt_kv_append(rt_ctx* ctx, void* dst, const void* src, int64_t startRow, int64_t rows,
+                 int64_t cols, int64_t dstRows, int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!dst || !src) return fail(ctx, RT_INVALID_ARGUMENT, "writeRows: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "writeRows: bad dtype %d", dtype);
+  if (rows < 1 || cols < 1 || dstRows < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "writeRows: empty tensor (%lld x %lld into %lld rows)",
+                (long long)rows, (long long)cols, (long long)dstRows);
+  if (startRow < 0 || startRow + rows > dstRows)
+    return fail(ctx, RT_INVALID_ARGUMENT, "writeRows: rows [%lld, %lld) exceed dst capacity %lld",
+                (long long)startRow, (long long)(startRow + rows), (long long)dstRows);
+  const int es = elem_size(dtype);
+  (void)dtype_name;
+  RT_CUDA(ctx, rt::launch_write_rows(dst, src, startRow * cols * es, rows * cols * es, ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,133 @@
+// Shared declarations of the attention library's translation units.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "rt_attn.h"
+
+namespace rt {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kNegSeed = -1e30f;  // finite seed of the running max: buffers never hold +-Inf
+
+// Bits of the device-side status word (rt_ctx::status_dev).  A kernel whose
+// bounded wait runs out ORs a bit in and returns; rt_sync reports it.
+constexpr int kStatusWaitTimeout = 1;
+constexpr int kStatusBadState = 2;
+
+// One attention problem as the kernels see it.  k and v already point at
+// their column block when the tensors are packed; strides are in elements.
+struct AttnParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  const float* sinks;
+  const float* segs;
+  const int32_t* seqLens;
+  int64_t qLen, kvLen;
+  int64_t qStride, kvStride;
+  int64_t qPosOffset;
+  int32_t qHeads, kvHeads, hd;
+  int32_t wl, wr;
+  int32_t hasKeyBias, biasStart, biasEnd;
+  float biasValue;
+  int32_t seqStride;
+  int32_t maxSegment;
+};
+
+// Visible key range [lo, end] (inclusive) of query row `row`; empty when lo > end.
+// Rule: packages/runntime/src/core/kernels/attention/attn.ts:150-156 (window,
+// then segment clip), with the padded-batch form derived from seqLens.
+__device__ __forceinline__ void row_band(const AttnParams& p, int64_t row, int64_t& lo,
+                                         int64_t& end) {
+  const int64_t qPos = p.qPosOffset + row;
+  lo = qPos - p.wl;
+  if (lo < 0) lo = 0;
+  end = qPos + p.wr;
+  if (end > p.kvLen - 1) end = p.kvLen - 1;
+  if (p.segs) {
+    const int64_t s0 = (int64_t)p.segs[2 * row];
+    const int64_t s1 = (int64_t)p.segs[2 * row + 1] - 1;
+    if (s0 > lo) lo = s0;
+    if (s1 < end) end = s1;
+  } else if (p.seqStride > 0) {
+    const int64_t b = row / p.seqStride;
+    const int64_t r = row - b * p.seqStride;
+    const int64_t len = p.seqLens[b];
+    if (r >= len) {
+      lo = 1;
+      end = 0;
+    } else {
+      const int64_t s0 = b * p.seqStride;
+      if (s0 > lo) lo = s0;
+      if (s0 + len - 1 < end) end = s0 + len - 1;
+    }
+  }
+}
+
+struct DecodeParams {
+  const void* q;
+  void* out;
+  void* kCache;
+  void* vCache;
+  const void* kNew;
+  const void* vNew;
+  const int32_t* kvLens;
+  const float* sinks;
+  float* partialsOut;   // final destination is partials (m, l, acc) instead of out
+  float* scratch;       // [batch, splits, qHeads, 2+hd] f32, used when splits > 1
+  unsigned* counters;   // [batch * headBlocks], zero between launches
+  int* status;
+  int64_t cacheSeqStride;
+  int64_t lo, end;      // explicit key range (useRange), for the single-sequence op
+  int32_t useRange;
+  int32_t batch, kvLen, qHeads, kvHeads, hd, wl, splits;
+  int32_t kvPerCta;     // kv heads handled by one CTA
+  int32_t keySlots;     // keys processed concurrently by one CTA
+  int32_t stages;       // smem ring depth (bulk path)
+};
+
+// Launchers (defined one per .cu).  Each returns a cudaError_t from the launch.
+cudaError_t launch_prefill_simt(const AttnParams& p, int dtype, cudaStream_t s);
+bool prefill_tc_supported(const AttnParams& p, int dtype);
+cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaStream_t s,
+                              std::string* err);
+// Fills kvPerCta/keySlots/stages/splits; returns false with a message when the shape cannot run.
+bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
+cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_merge_partials(const float* partials, int parts, int64_t units, int hd,
+                                  void* out, int dtype, cudaStream_t s);
+cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes, int64_t bytes,
+                              cudaStream_t s);
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+}  // namespace rt

@@ -1,0 +1,524 @@
+// Single-token decode attention over KV caches: bandwidth-bound split-KV.
+//
+// Grid = (key splits, sequences, head blocks).  A CTA streams its slice of one
+// sequence's K and V cache rows through a shared-memory ring filled by bulk
+// async copies (TMA, 16-byte aligned, whole rows so every DRAM sector fetched is
+// used), issued by a producer warp and signalled through mbarriers.  The 256
+// consumer threads are laid out as (key slot, query head): each thread runs a
+// private online softmax over the keys of its slot in f32 registers.  At the
+// end the slots of a head are merged with a log-sum-exp; with more than one
+// split the per-split (m, l, acc) partials go to scratch and the last CTA to
+// arrive for the sequence merges them — no second launch, no waiting.
+//
+// The KV-cache append is fused: the new K/V row is stored to the cache by the
+// CTA of split 0 and attended to straight from its source.
+//
+// Replaces packages/runntime/src/core/kernels/attention/attnDecode.ts:81-187
+// (decode), :263-424 (decodeSplit + merge) and the writeRows dispatches that
+// precede them (packages/runntime/src/core/kernels/shape/rows.ts:143-162).
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace rt {
+namespace {
+
+using namespace sm100;
+
+constexpr int kConsumers = 256;
+constexpr int kConsumerWarps = kConsumers / 32;
+constexpr int kMaxStages = 8;
+constexpr size_t kSmemBudget = 200 * 1024;
+
+__host__ __device__ constexpr int q_stride(int hdp) { return ((hdp / 4) & 1) ? hdp : hdp + 4; }
+
+template <typename T, int VEC>
+struct Loader;
+
+// 8 halves per 16-byte load
+template <>
+struct Loader<__half, 8> {
+  static __device__ __forceinline__ void load(const __half* p, float (&f)[8]) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+template <>
+struct Loader<__half, 4> {
+  static __device__ __forceinline__ void load(const __half* p, float (&f)[4]) {
+    const uint2 w = *reinterpret_cast<const uint2*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+template <>
+struct Loader<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+    const float4 w = *reinterpret_cast<const float4*>(p);
+    f[0] = w.x; f[1] = w.y; f[2] = w.z; f[3] = w.w;
+  }
+};
+template <typename T>
+struct Loader<T, 1> {
+  static __device__ __forceinline__ void load(const T* p, float (&f)[1]) { f[0] = to_f32<T>(*p); }
+};
+
+// One key for one head: score, online-softmax update, accumulate p*v.
+// kp/vp may point at shared memory (cache tile) or global memory (appended row).
+template <typename T, int HDP, bool EXACT, int VEC, bool QSMEM>
+__device__ __forceinline__ void process_key(const T* kp, const T* vp, const float* qv, int hd,
+                                            float& m, float& l, float (&acc)[HDP]) {
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < HDP / VEC; i++) {
+    if (EXACT || i * VEC < hd) {
+      float f[VEC];
+      Loader<T, VEC>::load(kp + i * VEC, f);
+#pragma unroll
+      for (int e = 0; e < VEC; e++) {
+        if ((i * VEC + e) & 1) s1 = fmaf(qv[i * VEC + e], f[e], s1);
+        else s0 = fmaf(qv[i * VEC + e], f[e], s0);
+      }
+    }
+  }
+  const float s = (s0 + s1) * kLog2e;  // log2 domain
+  if (s > m) {
+    const float c = fast_exp2(m - s);
+    l *= c;
+#pragma unroll
+    for (int x = 0; x < HDP; x++) acc[x] *= c;
+    m = s;
+  }
+  const float pe = fast_exp2(s - m);
+  l += pe;
+#pragma unroll
+  for (int i = 0; i < HDP / VEC; i++) {
+    if (EXACT || i * VEC < hd) {
+      float f[VEC];
+      Loader<T, VEC>::load(vp + i * VEC, f);
+#pragma unroll
+      for (int e = 0; e < VEC; e++) acc[i * VEC + e] = fmaf(pe, f[e], acc[i * VEC + e]);
+    }
+  }
+}
+
+template <typename T, int HDP, bool EXACT, int VEC, bool BULK>
+__global__ void __launch_bounds__(BULK ? kConsumers + 32 : kConsumers)
+decode_kernel(const DecodeParams p) {
+  constexpr bool QSMEM = HDP > 64;
+  constexpr int QS = q_stride(HDP);
+  extern __shared__ __align__(128) unsigned char smemRaw[];
+  __shared__ int sAbort;
+  __shared__ int sIsLast;
+  __shared__ __align__(8) uint64_t sFull[kMaxStages], sEmpty[kMaxStages];
+
+  const int tid = threadIdx.x;
+  const int split = blockIdx.x, b = blockIdx.y, zb = blockIdx.z;
+  const int hd = p.hd;
+  const int group = p.qHeads / p.kvHeads;
+  const int kvh0 = zb * p.kvPerCta;
+  const int nkv = min(p.kvPerCta, p.kvHeads - kvh0);
+  const int hqMax = p.kvPerCta * group;
+  const int hq = nkv * group;
+  const int KS = p.keySlots;
+  const int sliceElems = nkv * hd;
+  const int rowElems = p.kvHeads * hd;
+  const bool hasNew = p.kNew != nullptr;
+
+  // Key range of this sequence that lives in the cache.
+  int64_t lo, end;
+  if (p.useRange) {
+    lo = p.lo;
+    end = p.end;
+  } else {
+    const int64_t L = p.kvLens ? p.kvLens[b] : p.kvLen;
+    end = L - 1;
+    lo = L - 1 - p.wl;
+    if (lo < 0) lo = 0;
+    if (hasNew) end -= 1;  // row L-1 is the appended one, taken from kNew/vNew
+    if (L <= 0) { lo = 1; end = -1; }
+  }
+  const int64_t n = end >= lo ? end - lo + 1 : 0;
+  int64_t chunk = (n + p.splits - 1) / p.splits;
+  chunk = (chunk + KS - 1) / KS * KS;
+  int64_t s0 = lo + (int64_t)split * chunk, s1 = s0 + chunk;
+  if (s1 > end + 1) s1 = end + 1;
+  const int ntiles = s1 > s0 ? (int)((s1 - s0 + KS - 1) / KS) : 0;
+
+  const T* kBase = static_cast<const T*>(p.kCache) + (int64_t)b * p.cacheSeqStride + kvh0 * hd;
+  const T* vBase = static_cast<const T*>(p.vCache) + (int64_t)b * p.cacheSeqStride + kvh0 * hd;
+
+  // Shared-memory carve-up: [q][ring: stages x (K tile, V tile)]; the ring is
+  // reused for the slot merge at the end.
+  float* sQ = reinterpret_cast<float*>(smemRaw);
+  const int qBytes = QSMEM ? ((hqMax * QS * 4 + 127) / 128) * 128 : 0;
+  unsigned char* ring = smemRaw + qBytes;
+  const int tileBytes = ((KS * p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128;
+  const int stages = BULK ? p.stages : 1;
+
+  if (tid == 0) {
+    sAbort = 0;
+    sIsLast = 0;
+    if (BULK) {
+      for (int s = 0; s < stages; s++) {
+        mbar_init(smem_u32(&sFull[s]), 1);
+        mbar_init(smem_u32(&sEmpty[s]), kConsumerWarps);
+      }
+      fence_barrier_init();
+    }
+  }
+  __syncthreads();
+
+  if (BULK && tid >= kConsumers) {
+    // ---------------- producer warp ----------------
+    const int lane = tid - kConsumers;
+    const bool flat = (nkv == p.kvHeads);
+    for (int it = 0; it < ntiles; it++) {
+      const int s = it % stages;
+      if (it >= stages) {
+        if (!mbar_wait(smem_u32(&sEmpty[s]), ((it / stages) - 1) & 1, &sAbort)) break;
+      }
+      const int64_t k0 = s0 + (int64_t)it * KS;
+      const int nk = (int)min((int64_t)KS, s1 - k0);
+      const uint32_t bar = smem_u32(&sFull[s]);
+      const uint32_t dK = smem_u32(ring + (size_t)s * 2 * tileBytes);
+      const uint32_t dV = dK + tileBytes;
+      const uint32_t rowBytes = (uint32_t)sliceElems * sizeof(T);
+      if (lane == 0) mbar_expect_tx(bar, 2u * nk * rowBytes);
+      __syncwarp();
+      if (flat) {
+        if (lane == 0) {
+          bulk_g2s(dK, kBase + k0 * rowElems, nk * rowBytes, bar);
+          bulk_g2s(dV, vBase + k0 * rowElems, nk * rowBytes, bar);
+        }
+      } else {
+        for (int r = lane; r < nk; r += 32) {
+          bulk_g2s(dK + r * rowBytes, kBase + (k0 + r) * rowElems, rowBytes, bar);
+          bulk_g2s(dV + r * rowBytes, vBase + (k0 + r) * rowElems, rowBytes, bar);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  const int hl = tid % hqMax;
+  const int slot = tid / hqMax;
+  const bool active = slot < KS && hl < hq;
+  const int h = kvh0 * group + hl;   // query head
+  const int kvl = hl / group;        // kv head within the CTA's slice
+
+  float qreg[QSMEM ? 1 : HDP];
+  const float* qv;
+  {
+    const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qHeads * hd;
+    if (QSMEM) {
+      for (int idx = tid; idx < hq * hd; idx += kConsumers) {
+        const int hh = idx / hd, x = idx - hh * hd;
+        sQ[hh * QS + x] = to_f32<T>(qg[(kvh0 * group + hh) * hd + x]);
+      }
+      named_barrier_sync(1, kConsumers);
+      qv = sQ + hl * QS;
+    } else {
+#pragma unroll
+      for (int x = 0; x < HDP; x++)
+        qreg[x] = (active && (EXACT || x < hd)) ? to_f32<T>(qg[h * hd + x]) : 0.f;
+      qv = qreg;
+    }
+  }
+
+  float m = kNegSeed, l = 0.f;
+  float acc[HDP];
+#pragma unroll
+  for (int x = 0; x < HDP; x++) acc[x] = 0.f;
+  if (active && slot == 0 && split == 0 && p.sinks) {
+    m = p.sinks[h];  // sinks are log2-space: sink * ln2 * log2e
+    l = 1.f;
+  }
+
+  bool ok = true;
+  for (int it = 0; it < ntiles; it++) {
+    const int64_t k0 = s0 + (int64_t)it * KS;
+    const int nk = (int)min((int64_t)KS, s1 - k0);
+    const int s = BULK ? it % stages : 0;
+    T* tK = reinterpret_cast<T*>(ring + (size_t)s * 2 * tileBytes);
+    T* tV = reinterpret_cast<T*>(ring + (size_t)s * 2 * tileBytes + tileBytes);
+    if (BULK) {
+      if (!mbar_wait(smem_u32(&sFull[s]), (it / stages) & 1, &sAbort)) { ok = false; break; }
+    } else {
+      named_barrier_sync(1, kConsumers);
+      for (int idx = tid; idx < nk * sliceElems; idx += kConsumers) {
+        const int jj = idx / sliceElems, x = idx - jj * sliceElems;
+        tK[idx] = kBase[(k0 + jj) * rowElems + x];
+        tV[idx] = vBase[(k0 + jj) * rowElems + x];
+      }
+      named_barrier_sync(1, kConsumers);
+    }
+    if (active && slot < nk) {
+      const int off = slot * sliceElems + kvl * hd;
+      process_key<T, HDP, EXACT, VEC, QSMEM>(tK + off, tV + off, qv, hd, m, l, acc);
+    }
+    if (BULK) {
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(smem_u32(&sEmpty[s]));
+    }
+  }
+
+  // Fused append: split 0 stores the new row into the cache and attends to it.
+  if (hasNew && split == 0 && !p.useRange) {
+    const int64_t L = p.kvLens ? p.kvLens[b] : p.kvLen;
+    if (L >= 1) {
+      const T* kn = static_cast<const T*>(p.kNew) + (int64_t)b * rowElems + kvh0 * hd;
+      const T* vn = static_cast<const T*>(p.vNew) + (int64_t)b * rowElems + kvh0 * hd;
+      T* kc = const_cast<T*>(kBase) + (L - 1) * rowElems;
+      T* vc = const_cast<T*>(vBase) + (L - 1) * rowElems;
+      for (int x = tid; x < sliceElems; x += kConsumers) {
+        kc[x] = kn[x];
+        vc[x] = vn[x];
+      }
+      if (active && slot == 0)
+        process_key<T, HDP, EXACT, VEC, QSMEM>(kn + kvl * hd, vn + kvl * hd, qv, hd, m, l, acc);
+    }
+  }
+
+  if (!ok || sAbort) {
+    // A wait ran out: record it, let copies in flight land, leave.
+    if (tid == 0) atomicOr(p.status, kStatusWaitTimeout);
+    for (int i = 0; i < 64; i++) __nanosleep(4000);
+    return;
+  }
+
+  // ---- merge the key slots of each head (log-sum-exp) ----
+  named_barrier_sync(1, kConsumers);  // every tile consumed: the ring is free
+  float* sM = reinterpret_cast<float*>(ring);  // [KS][hqMax][2 + HDP]
+  constexpr int MS = 2 + HDP;
+  if (active) {
+    float* r = sM + (slot * hqMax + hl) * MS;
+    r[0] = m;
+    r[1] = l;
+#pragma unroll
+    for (int x = 0; x < HDP; x++) r[2 + x] = acc[x];
+  }
+  named_barrier_sync(1, kConsumers);
+
+  const int stride = 2 + hd;  // partials row in global memory
+  if (active) {
+    float M = kNegSeed;
+    for (int s = 0; s < KS; s++) M = fmaxf(M, sM[(s * hqMax + hl) * MS]);
+    float L = 0.f;
+    float o[HDP];  // entry c holds output column slot + c*KS
+    for (int c = 0, x = slot; x < hd; x += KS, c++) o[c] = 0.f;
+    for (int s = 0; s < KS; s++) {
+      const float* r = sM + (s * hqMax + hl) * MS;
+      const float w = fast_exp2(r[0] - M);
+      L = fmaf(r[1], w, L);
+      for (int c = 0, x = slot; x < hd; x += KS, c++) o[c] = fmaf(r[2 + x], w, o[c]);
+    }
+    const bool toPartials = p.partialsOut != nullptr;
+    if (p.splits == 1) {
+      if (toPartials) {
+        float* dst = p.partialsOut + ((int64_t)b * p.qHeads + h) * stride;
+        if (slot == 0) {
+          dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
+          dst[1] = L;
+        }
+        int c = 0;
+        for (int x = slot; x < hd; x += KS) dst[2 + x] = o[c++];
+      } else {
+        const float invL = L > 0.f ? 1.f / L : 0.f;
+        T* dst = static_cast<T*>(p.out) + ((int64_t)b * p.qHeads + h) * hd;
+        int c = 0;
+        for (int x = slot; x < hd; x += KS) dst[x] = from_f32<T>(o[c++] * invL);
+      }
+    } else {
+      float* dst = p.scratch + (((int64_t)b * p.splits + split) * p.qHeads + h) * stride;
+      if (slot == 0) {
+        dst[0] = M;
+        dst[1] = L;
+      }
+      int c = 0;
+      for (int x = slot; x < hd; x += KS) dst[2 + x] = o[c++];
+    }
+  }
+  if (p.splits == 1) return;
+
+  // ---- last CTA of the sequence merges the splits ----
+  __threadfence();
+  named_barrier_sync(1, kConsumers);
+  if (tid == 0) {
+    const unsigned old = atomicAdd(&p.counters[b * gridDim.z + zb], 1u);
+    sIsLast = (old == (unsigned)p.splits - 1);
+  }
+  named_barrier_sync(1, kConsumers);
+  if (!sIsLast) return;
+  __threadfence();
+  if (active) {
+    const float* base = p.scratch + ((int64_t)b * p.splits * p.qHeads + h) * stride;
+    const int64_t ss = (int64_t)p.qHeads * stride;  // between splits
+    float M = kNegSeed;
+    for (int s = 0; s < p.splits; s++) M = fmaxf(M, __ldcg(base + s * ss));
+    float L = 0.f;
+    for (int s = 0; s < p.splits; s++)
+      L = fmaf(__ldcg(base + s * ss + 1), fast_exp2(__ldcg(base + s * ss) - M), L);
+    const bool toPartials = p.partialsOut != nullptr;
+    const float invL = L > 0.f ? 1.f / L : 0.f;
+    for (int x = slot; x < hd; x += KS) {
+      float o = 0.f;
+      for (int s = 0; s < p.splits; s++)
+        o = fmaf(__ldcg(base + s * ss + 2 + x), fast_exp2(__ldcg(base + s * ss) - M), o);
+      if (toPartials)
+        p.partialsOut[((int64_t)b * p.qHeads + h) * stride + 2 + x] = o;
+      else
+        static_cast<T*>(p.out)[((int64_t)b * p.qHeads + h) * hd + x] = from_f32<T>(o * invL);
+    }
+    if (toPartials && slot == 0) {
+      float* dst = p.partialsOut + ((int64_t)b * p.qHeads + h) * stride;
+      dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
+      dst[1] = L;
+    }
+  }
+  if (tid == 0) p.counters[b * gridDim.z + zb] = 0;  // ready for the next launch
+}
+
+size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
+  const int group = p.qHeads / p.kvHeads;
+  const int hqMax = p.kvPerCta * group;
+  const size_t qBytes = hdp > 64 ? (((size_t)hqMax * q_stride(hdp) * 4 + 127) / 128) * 128 : 0;
+  const size_t tileBytes = (((size_t)p.keySlots * p.kvPerCta * p.hd * esize + 127) / 128) * 128;
+  const size_t ringBytes = (size_t)(bulk ? p.stages : 1) * 2 * tileBytes;
+  const size_t mergeBytes = (size_t)p.keySlots * hqMax * (2 + hdp) * 4;
+  return qBytes + (ringBytes > mergeBytes ? ringBytes : mergeBytes);
+}
+
+int padded_hd(int hd) { return hd <= 32 ? 32 : hd <= 64 ? 64 : 128; }
+bool exact_hd(int hd) { return hd == 36 || hd == 52 || hd == 64 || hd == 128; }
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+// The bulk (TMA) path needs 16-byte aligned rows and slices.
+bool bulk_ok(const DecodeParams& p, int esize) {
+  if (!exact_hd(p.hd)) return false;
+  const int64_t rowBytes = (int64_t)p.kvHeads * p.hd * esize;
+  const int64_t sliceBytes = (int64_t)p.kvPerCta * p.hd * esize;
+  if (rowBytes % 16 || sliceBytes % 16 || (p.cacheSeqStride * esize) % 16) return false;
+  if (!aligned16(p.kCache) || !aligned16(p.vCache)) return false;
+  if (p.kNew && (!aligned16(p.kNew) || !aligned16(p.vNew))) return false;
+  if (p.kvHeads % p.kvPerCta) return false;  // a ragged last block changes the slice size
+  return true;
+}
+
+template <typename T, int HDP, bool EXACT, int VEC, bool BULK>
+cudaError_t launch_one(const DecodeParams& p, size_t smem, cudaStream_t s) {
+  auto kern = decode_kernel<T, HDP, EXACT, VEC, BULK>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int zBlocks = (p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
+  dim3 grid(p.splits, p.batch, zBlocks);
+  kern<<<grid, BULK ? kConsumers + 32 : kConsumers, smem, s>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_typed(const DecodeParams& p, cudaStream_t s) {
+  constexpr int esize = sizeof(T);
+  constexpr int V = sizeof(T) == 2 ? 8 : 4;   // widest vector for the exact paths
+  if (bulk_ok(p, esize)) {
+    const size_t smem = smem_bytes(p, esize, p.hd, true);
+    switch (p.hd) {
+      case 36: return launch_one<T, 36, true, 4, true>(p, smem, s);
+      case 52: return launch_one<T, 52, true, 4, true>(p, smem, s);
+      case 64: return launch_one<T, 64, true, V, true>(p, smem, s);
+      case 128: return launch_one<T, 128, true, V, true>(p, smem, s);
+    }
+  }
+  const int hdp = padded_hd(p.hd);
+  const size_t smem = smem_bytes(p, esize, hdp, false);
+  if (hdp == 32) return launch_one<T, 32, false, 1, false>(p, smem, s);
+  if (hdp == 64) return launch_one<T, 64, false, 1, false>(p, smem, s);
+  return launch_one<T, 128, false, 1, false>(p, smem, s);
+}
+
+}  // namespace
+
+bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
+  const int esize = dtype == RT_F16 ? 2 : 4;
+  const int group = p.qHeads / p.kvHeads;
+  if (group > kConsumers) {
+    *err = "decode: more than 256 query heads per kv head";
+    return false;
+  }
+  int kvPerCta = p.kvHeads;
+  while (kvPerCta * group > kConsumers) kvPerCta = (kvPerCta + 1) / 2;
+  const int hdp = padded_hd(p.hd);
+  const size_t qBytes = hdp > 64 ? (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128 : 0;
+  const size_t budget = kSmemBudget - qBytes;
+  int keySlots;
+  for (;;) {
+    keySlots = kConsumers / (kvPerCta * group);
+    const size_t tile = 2ull * keySlots * kvPerCta * p.hd * esize + 256;
+    if (2 * tile > budget && kvPerCta > 1) {
+      kvPerCta = (kvPerCta + 1) / 2;
+      continue;
+    }
+    break;
+  }
+  {
+    const size_t perSlot = 2ull * kvPerCta * p.hd * esize;            // K+V bytes of one key
+    const size_t mergePerSlot = (size_t)kvPerCta * group * (2 + hdp) * 4;
+    const size_t capTile = (budget / 2 - 256) / perSlot;               // two stages must fit
+    const size_t capMerge = budget / mergePerSlot;
+    size_t cap = capTile < capMerge ? capTile : capMerge;
+    if (cap < 1) {
+      *err = "decode: heads too wide for shared memory";
+      return false;
+    }
+    if ((size_t)keySlots > cap) keySlots = (int)cap;
+  }
+  p.kvPerCta = kvPerCta;
+  p.keySlots = keySlots;
+  const size_t tile = ((2ull * keySlots * kvPerCta * p.hd * esize + 255) / 256) * 256 + 256;
+  int stages = (int)(budget / tile);
+  p.stages = stages < 2 ? 2 : stages > kMaxStages ? kMaxStages : stages;
+
+  if (p.splits <= 0) {
+    const int zBlocks = (p.kvHeads + kvPerCta - 1) / kvPerCta;
+    const int64_t ctas = (int64_t)p.batch * zBlocks;
+    int64_t nmax = p.useRange ? (p.end >= p.lo ? p.end - p.lo + 1 : 0) : p.kvLen;
+    if (!p.useRange && p.wl < nmax) nmax = (int64_t)p.wl + 1;
+    int64_t maxS = nmax / (4ll * keySlots);  // at least four tiles per split
+    if (maxS > 32) maxS = 32;
+    if (maxS < 1) maxS = 1;
+    int best = 1;
+    if (ctas * maxS <= smCount) {
+      best = (int)maxS;
+    } else {
+      double bestEff = 0.0;
+      for (int s = 1; s <= maxS; s++) {
+        const double waves = (double)(ctas * s) / smCount;
+        const double eff = waves / (double)((ctas * s + smCount - 1) / smCount);
+        if (eff > bestEff + 0.02) {
+          bestEff = eff;
+          best = s;
+        }
+      }
+    }
+    p.splits = best;
+  }
+  return true;
+}
+
+cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s) {
+  return dtype == RT_F16 ? launch_typed<__half>(p, s) : launch_typed<float>(p, s);
+}
+
+}  // namespace rt

@@ -1,0 +1,202 @@
+"""Operator constructors of the attention path: ``sdpa``, ``sdpaPacked`` and
+``writeRows`` with the reference's names, option names, defaults, synchronous
+validation and error texts
+(packages/runntime/src/core/graph/ops/attention.ts:28-212,
+packages/runntime/src/core/graph/ops/shape.ts:236-259).  They only build a
+pending node; ``evalValues``/``toArray`` run it on the GPU."""
+from __future__ import annotations
+
+import json
+import math
+from typing import Optional, Sequence
+
+from ._lib import WINDOW_INF
+from .value import Value, ValueMeta, pending
+
+FLOAT_DTYPES = ("f32", "f16")
+MAX_HEAD_DIM = 512          # widest head with more than one query row
+MAX_DECODE_HEAD_DIM = 128   # widest head with one query row
+
+
+def _js(x) -> str:
+    """A number as JavaScript's template literals print it."""
+    if isinstance(x, bool):
+        return "true" if x else "false"
+    if isinstance(x, float):
+        if math.isinf(x):
+            return "Infinity" if x > 0 else "-Infinity"
+        if math.isnan(x):
+            return "NaN"
+        if x.is_integer():
+            return str(int(x))
+        return repr(x)
+    return str(x)
+
+
+def _is_int(x) -> bool:
+    if isinstance(x, bool):
+        return False
+    if isinstance(x, int):
+        return True
+    return isinstance(x, float) and math.isfinite(x) and x.is_integer()
+
+
+def want2d(name: str, x: Value, allow: Sequence[str]):
+    """[rows, cols, dtype] of a 2-D row-major tensor whose dtype is allowed
+    (packages/runntime/src/core/graph/ops/shared.ts:46-75)."""
+    dims, dtype = x.shape.dims, x.shape.dtype
+    if dims is None or len(dims) != 2 or dtype not in allow:
+        got = "undefined" if dims is None else json.dumps(list(dims), separators=(",", ":"))
+        raise ValueError(
+            f"{name}: expected a 2D {' or '.join(allow)} tensor, got dims={got} dtype={dtype}")
+    return dims[0], dims[1], dtype
+
+
+def _lower_window(op: str, name: str, w) -> int:
+    if w == math.inf:
+        return WINDOW_INF
+    if not _is_int(w) or w < 0:
+        raise ValueError(f"{op}: {name} {_js(w)} must be a non-negative integer or Infinity")
+    return min(int(w), WINDOW_INF)
+
+
+def sdpa(q: Value, k: Value, v: Value, opts: dict) -> Value:
+    """Scaled-dot-product attention over the band-mask family, with GQA and
+    optional sinks; kvLen is independent of qLen.  Key j is visible to row i
+    when qPos - windowLeft <= j <= qPos + windowRight, qPos = qPosOffset + i.
+    ``segments`` clips each row to its own key range; ``keyBias`` adds ``value``
+    to the scores of keys [start, end).  No score scale is applied."""
+    qHeads, kvHeads, headDim = opts["qHeads"], opts["kvHeads"], opts["headDim"]
+    sinks: Optional[Value] = opts.get("sinks")
+    segments: Optional[Value] = opts.get("segments")
+    keyBias = opts.get("keyBias")
+    qPosOffset = opts.get("qPosOffset")
+    qPosOffset = 0 if qPosOffset is None else qPosOffset
+    qLen, qw, dtype = want2d("sdpa", q, FLOAT_DTYPES)
+    if qw != qHeads * headDim:
+        raise ValueError(f"sdpa: q cols {qw} != qHeads*headDim {qHeads * headDim}")
+    if kvHeads <= 0 or qHeads % kvHeads != 0:
+        raise ValueError(f"sdpa: qHeads {qHeads} not divisible by kvHeads {kvHeads}")
+    maxHeadDim = MAX_DECODE_HEAD_DIM if qLen == 1 else MAX_HEAD_DIM
+    if headDim > maxHeadDim:
+        raise ValueError(f"sdpa: headDim {headDim} exceeds the kernel's max ({maxHeadDim})")
+    wl = _lower_window("sdpa", "windowLeft", opts["windowLeft"])
+    wr = _lower_window("sdpa", "windowRight", opts["windowRight"])
+    if not _is_int(qPosOffset) or qPosOffset < 0:
+        raise ValueError(f"sdpa: qPosOffset {_js(qPosOffset)} must be a non-negative integer")
+    qPosOffset = int(qPosOffset)
+    kvw = kvHeads * headDim
+    kvLen, kw, kDtype = want2d("sdpa.k", k, FLOAT_DTYPES)
+    if kw != kvw:
+        raise ValueError(f"sdpa: k cols {kw} != kvHeads*headDim {kvw}")
+    vt, vw, vDtype = want2d("sdpa.v", v, FLOAT_DTYPES)
+    if kDtype != dtype or vDtype != dtype:
+        raise ValueError(f"sdpa: q, k and v must share a dtype, got {dtype}/{kDtype}/{vDtype}")
+    if vt != kvLen:
+        raise ValueError(f"sdpa: v rows {vt} != k rows {kvLen}")
+    if vw != kvw:
+        raise ValueError(f"sdpa: v cols {vw} != kvHeads*headDim {kvw}")
+    if wr != WINDOW_INF and qPosOffset + qLen > kvLen:
+        raise ValueError(
+            f"sdpa: qPosOffset+qLen {qPosOffset + qLen} exceeds key rows kvLen {kvLen}")
+    if sinks is not None and (sinks.shape.dtype != "f32" or sinks.shape.elems != qHeads):
+        raise ValueError(f"sdpa: sinks must be f32 with {qHeads} elems, got {sinks.shape.elems}")
+    if segments is not None:
+        if segments.shape.dtype != "f32" or segments.shape.elems != 2 * qLen:
+            raise ValueError(
+                f"sdpa: segments must be f32 [qLen, 2] = {2 * qLen} elems, got "
+                f"({segments.shape.elems},{segments.shape.dtype})")
+        if qLen == 1:
+            raise ValueError("sdpa: segments need qLen > 1 (decode has no segment route)")
+    maxSegment = opts.get("maxSegment")
+    maxSegment = 0 if maxSegment is None else maxSegment
+    if maxSegment != 0:
+        if segments is None:
+            raise ValueError("sdpa: maxSegment needs segments")
+        if not _is_int(maxSegment) or maxSegment < 1:
+            raise ValueError(f"sdpa: maxSegment {_js(maxSegment)} must be a positive integer")
+    bias_attrs = []
+    if keyBias:
+        start, end, value = keyBias["start"], keyBias["end"], keyBias["value"]
+        if (not _is_int(start) or not _is_int(end) or start < 0 or start > end or end > kvLen):
+            raise ValueError(
+                f"sdpa: keyBias keys [{_js(start)}, {_js(end)}) must lie within the {kvLen} keys")
+        if not math.isfinite(value):
+            raise ValueError(f"sdpa: keyBias value {_js(value)} must be finite")
+        if qLen == 1:
+            raise ValueError("sdpa: keyBias needs qLen > 1 (decode has no key bias route)")
+        bias_attrs = [1, int(start), int(end), value]
+    inputs = [q, k, v] + ([sinks] if sinks is not None else []) + (
+        [segments] if segments is not None else [])
+    attrs = [qHeads, kvHeads, headDim, wl, wr, qPosOffset, 1 if sinks is not None else 0,
+             1 if segments is not None else 0, int(maxSegment), 0, *bias_attrs]
+    return pending(ValueMeta(qLen * qw, dtype, (qLen, qw)), "attn", inputs, None, attrs)
+
+
+def sdpaPacked(qkv: Value, opts: dict) -> Value:
+    """sdpa over one fused qkv tensor read in place, q, k and v as column
+    blocks.  Self-attention only, no qLen = 1 route, no key bias."""
+    qHeads, kvHeads, headDim = opts["qHeads"], opts["kvHeads"], opts["headDim"]
+    sinks: Optional[Value] = opts.get("sinks")
+    segments: Optional[Value] = opts.get("segments")
+    qPosOffset = opts.get("qPosOffset")
+    qPosOffset = 0 if qPosOffset is None else qPosOffset
+    t, w, dtype = want2d("sdpaPacked", qkv, FLOAT_DTYPES)
+    qw = qHeads * headDim
+    packedW = (qHeads + 2 * kvHeads) * headDim
+    if w != packedW:
+        raise ValueError(f"sdpaPacked: qkv cols {w} != (qHeads + 2*kvHeads)*headDim = {packedW}")
+    if kvHeads <= 0 or qHeads % kvHeads != 0:
+        raise ValueError(f"sdpaPacked: qHeads {qHeads} not divisible by kvHeads {kvHeads}")
+    if headDim > 128:
+        raise ValueError(f"sdpaPacked: headDim {headDim} exceeds the kernel's max (128)")
+    if t == 1:
+        raise ValueError("sdpaPacked: qLen must be > 1 (decode has no packed route)")
+    wl = _lower_window("sdpaPacked", "windowLeft", opts["windowLeft"])
+    wr = _lower_window("sdpaPacked", "windowRight", opts["windowRight"])
+    if not _is_int(qPosOffset) or qPosOffset < 0:
+        raise ValueError(f"sdpaPacked: qPosOffset {_js(qPosOffset)} must be a non-negative integer")
+    qPosOffset = int(qPosOffset)
+    if wr != WINDOW_INF and qPosOffset + t > t:
+        raise ValueError(f"sdpaPacked: qPosOffset+qLen {qPosOffset + t} exceeds key rows kvLen {t}")
+    if sinks is not None and (sinks.shape.dtype != "f32" or sinks.shape.elems != qHeads):
+        raise ValueError(
+            f"sdpaPacked: sinks must be f32 with {qHeads} elems, got {sinks.shape.elems}")
+    if segments is not None and (segments.shape.dtype != "f32" or segments.shape.elems != 2 * t):
+        raise ValueError(
+            f"sdpaPacked: segments must be f32 [qLen, 2] = {2 * t} elems, got "
+            f"({segments.shape.elems},{segments.shape.dtype})")
+    maxSegment = opts.get("maxSegment")
+    maxSegment = 0 if maxSegment is None else maxSegment
+    if maxSegment != 0:
+        if segments is None:
+            raise ValueError("sdpaPacked: maxSegment needs segments")
+        if not _is_int(maxSegment) or maxSegment < 1:
+            raise ValueError(f"sdpaPacked: maxSegment {_js(maxSegment)} must be a positive integer")
+    inputs = [qkv] + ([sinks] if sinks is not None else []) + (
+        [segments] if segments is not None else [])
+    attrs = [qHeads, kvHeads, headDim, wl, wr, qPosOffset, 1 if sinks is not None else 0,
+             1 if segments is not None else 0, int(maxSegment), 1]
+    return pending(ValueMeta(t * qw, dtype, (t, qw)), "attn", inputs, None, attrs)
+
+
+def writeRows(dst: Value, src: Value, startRow) -> Value:
+    """In-place row write: copies src into rows [startRow, startRow + r) of the
+    caller-owned buffer behind dst and returns a [startRow + r, cols] view of
+    that same buffer.  Built for KV-cache appends: rows past the view keep
+    whatever they held."""
+    dstRows, dstCols, dtype = want2d("writeRows.dst", dst, FLOAT_DTYPES)
+    srcRows, srcCols, srcDtype = want2d("writeRows.src", src, FLOAT_DTYPES)
+    if srcDtype != dtype:
+        raise ValueError(f"writeRows: dtype mismatch — dst is {dtype}, src is {srcDtype}")
+    if dst.state != "materialized":
+        raise ValueError("writeRows: dst must be a materialized (caller-owned) buffer")
+    if srcCols != dstCols:
+        raise ValueError(f"writeRows: col mismatch — dst has {dstCols}, src has {srcCols}")
+    if not _is_int(startRow) or startRow < 0 or startRow + srcRows > dstRows:
+        end = startRow + srcRows if isinstance(startRow, (int, float)) else "NaN"
+        raise ValueError(
+            f"writeRows: rows [{_js(startRow)}, {_js(end)}) exceed dst capacity {dstRows}")
+    viewRows = int(startRow) + srcRows
+    return pending(ValueMeta(viewRows * dstCols, dtype, (viewRows, dstCols)), "writeRows",
+                   [dst, src], None, [int(startRow)])

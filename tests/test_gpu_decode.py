@@ -1,0 +1,210 @@
+"""Decode parity on the GPU: the reference's decode suite
+(packages/runntime/test/core/kernels/attention/attnDecode.gpu.test.ts:38-115),
+the fused KV-cache append, batched caches, partials + merge."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+import cases
+import oracle
+from gpu_harness import check_sdpa, ex  # noqa: F401
+from oracle import SdpaCase, make_inputs, sdpa_ref
+
+pytestmark = pytest.mark.gpu
+
+INF = math.inf
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+@pytest.mark.parametrize("name,c", cases.DECODE_CASES, ids=[n for n, _ in cases.DECODE_CASES])
+def test_decode_cases(ex, dtype, name, c):
+    check_sdpa(ex, c, dtype, route="decode")
+
+
+@pytest.mark.parametrize("name,dtype,c", [z for z in cases.ZOO_SHAPES if z[2].qLen == 1],
+                         ids=[z[0] for z in cases.ZOO_SHAPES if z[2].qLen == 1])
+def test_zoo_decode_shapes(ex, name, dtype, c):
+    check_sdpa(ex, c, dtype, route="decode")
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+@pytest.mark.parametrize("hd,heads", [(36, 8), (52, 8), (64, 4), (128, 2), (16, 4), (37, 3)])
+def test_model_head_sizes_long_cache(ex, dtype, hd, heads):
+    for kv in (1, 33, 448, 3000):
+        check_sdpa(ex, cases.decode(kv, qHeads=heads, kvHeads=heads, headDim=hd), dtype,
+                   route="decode")
+
+
+def test_two_chained_calls_share_the_split_scratch(ex):
+    import runntime_b200 as rt
+    opts = dict(qHeads=4, kvHeads=4, headDim=16, windowLeft=INF, windowRight=0, qPosOffset=599)
+    q = oracle.random_f32(64, 1)
+    k = oracle.random_f32(600 * 64, 2).reshape(600, 64)
+    v = oracle.random_f32(600 * 64, 3).reshape(600, 64)
+    ku, vu = ex.upload(k, [600, 64]), ex.upload(v, [600, 64])
+    first = rt.sdpa(ex.upload(q, [1, 64]), ku, vu, opts)
+    got = rt.toArray(rt.sdpa(first, vu, ku, opts), ex)
+    kw = dict(qHeads=4, kvHeads=4, headDim=16, windowRight=0, qPosOffset=599)
+    first_want = sdpa_ref(q.reshape(1, 64), k, v, **kw).astype(np.float32)
+    oracle.assert_close(got, sdpa_ref(first_want, v, k, **kw), "f32")
+
+
+def _decode_step_through_ops(ex, dtype, t, hd=36, heads=8, cacheRows=194):
+    """The decoder's step: writeRows K and V at t, causal sdpa with qPosOffset t."""
+    import runntime_b200 as rt
+    w = heads * hd
+    rnd = oracle.round_f16 if dtype == "f16" else (lambda a: a)
+    kc = rnd(oracle.random_f32(cacheRows * w, 5)).reshape(cacheRows, w)
+    vc = rnd(oracle.random_f32(cacheRows * w, 6)).reshape(cacheRows, w)
+    kn = rnd(oracle.random_f32(w, 7)).reshape(1, w)
+    vn = rnd(oracle.random_f32(w, 8)).reshape(1, w)
+    q = rnd(oracle.random_f32(w, 9) * np.float32(2 / math.sqrt(hd))).reshape(1, w)
+    kcache, vcache = ex.upload(kc, [cacheRows, w], dtype), ex.upload(vc, [cacheRows, w], dtype)
+    k = rt.writeRows(kcache, ex.upload(kn, [1, w], dtype), t)
+    v = rt.writeRows(vcache, ex.upload(vn, [1, w], dtype), t)
+    mha = rt.MultiHeadAttention(dict(qHeads=heads, kvHeads=heads, headDim=hd, windowLeft=INF,
+                                     windowRight=0))
+    before = len(ex.dispatches)
+    out = rt.toArray(mha.forward(ex.upload(q, [1, w], dtype), k, v, dict(qPosOffset=t)), ex)
+    routes = ex.dispatches[before:]
+    kc2, vc2 = kc.copy(), vc.copy()
+    kc2[t], vc2[t] = kn[0], vn[0]
+    want = sdpa_ref(q, kc2[: t + 1], vc2[: t + 1], qHeads=heads, kvHeads=heads, headDim=hd,
+                    windowRight=0, qPosOffset=t)
+    oracle.assert_close(out, want, dtype, f"decode step t={t}")
+    # the cache holds the new row exactly, the rest is untouched
+    assert np.array_equal(ex.readback(kcache.buffer, kcache.shape).reshape(cacheRows, w), kc2)
+    assert np.array_equal(ex.readback(vcache.buffer, vcache.shape).reshape(cacheRows, w), vc2)
+    return routes
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+@pytest.mark.parametrize("t", [0, 1, 31, 32, 100, 193])
+def test_decoder_step_append_then_attend(ex, dtype, t):
+    assert _decode_step_through_ops(ex, dtype, t) == ["decode+append"]
+
+
+def test_decoder_step_generic_head_size(ex):
+    assert _decode_step_through_ops(ex, "f16", 50, hd=37, heads=3, cacheRows=64) == ["decode+append"]
+    assert _decode_step_through_ops(ex, "f32", 50, hd=20, heads=5, cacheRows=64) == ["decode+append"]
+
+
+def _batched_inputs(batch, cacheRows, heads, kvHeads, hd, dtype, lens, seed=11):
+    torch = pytest.importorskip("torch")
+    g = torch.Generator().manual_seed(seed)
+    tdt = torch.float16 if dtype == "f16" else torch.float32
+    w, qw = kvHeads * hd, heads * hd
+    kc = torch.randn(batch, cacheRows, w, generator=g).to(tdt)
+    vc = torch.randn(batch, cacheRows, w, generator=g).to(tdt)
+    kn = torch.randn(batch, w, generator=g).to(tdt)
+    vn = torch.randn(batch, w, generator=g).to(tdt)
+    q = (torch.randn(batch, qw, generator=g) / math.sqrt(hd)).to(tdt)
+    return q, kc, vc, kn, vn, torch.tensor(lens, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("heads,kvHeads,hd", [(8, 8, 36), (8, 8, 52), (6, 2, 64), (4, 4, 20)])
+def test_batched_decode_with_append_matches_per_sequence_oracle(ex, dtype, heads, kvHeads, hd):
+    import torch
+    from runntime_b200.engine import decode_batched
+    batch, cacheRows = 9, 448
+    lens = [1, 2, 31, 32, 33, 200, 257, 447, 448]
+    q, kc, vc, kn, vn, lt = _batched_inputs(batch, cacheRows, heads, kvHeads, hd, dtype, lens)
+    dev = torch.device("cuda", 0)
+    qd, kcd, vcd, knd, vnd, ld = (t.to(dev) for t in (q, kc, vc, kn, vn, lt))
+    out = torch.full((batch, heads * hd), 7.0, dtype=qd.dtype, device=dev)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        for splits in (0, 1, 3):
+            kcd.copy_(kc)
+            vcd.copy_(vc)
+            decode_batched(ex, qd, out, kcd, vcd, dtype=dtype, batch=batch, cacheRows=cacheRows,
+                           qHeads=heads, kvHeads=kvHeads, headDim=hd, kvLen=max(lens), kvLens=ld,
+                           kNew=knd, vNew=vnd, splits=splits)
+            ex.sync()
+            got = out.float().cpu().numpy()
+            kc2, vc2 = kc.clone(), vc.clone()
+            for b, L in enumerate(lens):
+                kc2[b, L - 1], vc2[b, L - 1] = kn[b], vn[b]
+                want = sdpa_ref(q[b:b + 1].float().numpy(), kc2[b, :L].float().numpy(),
+                                vc2[b, :L].float().numpy(), qHeads=heads, kvHeads=kvHeads,
+                                headDim=hd, windowRight=0, qPosOffset=L - 1)
+                oracle.assert_close(got[b], want, dtype, f"seq {b} len {L} splits {splits}")
+            assert torch.equal(kcd.cpu(), kc2) and torch.equal(vcd.cpu(), vc2)
+    finally:
+        ex.setStream(None)
+
+
+def test_batched_cross_attention_and_window(ex):
+    import torch
+    from runntime_b200.engine import decode_batched
+    batch, rows, heads, hd = 5, 200, 8, 36
+    q, kc, vc, _, _, _ = _batched_inputs(batch, rows, heads, heads, hd, "f16", [rows] * batch)
+    dev = torch.device("cuda", 0)
+    qd, kcd, vcd = q.to(dev), kc.to(dev), vc.to(dev)
+    out = torch.empty_like(qd)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        for wl in (None, 10):
+            decode_batched(ex, qd, out, kcd, vcd, dtype="f16", batch=batch, cacheRows=rows,
+                           qHeads=heads, kvHeads=heads, headDim=hd, kvLen=rows, windowLeft=wl)
+            ex.sync()
+            for b in range(batch):
+                want = sdpa_ref(q[b:b + 1].float().numpy(), kc[b].float().numpy(),
+                                vc[b].float().numpy(), qHeads=heads, kvHeads=heads, headDim=hd,
+                                windowLeft=INF if wl is None else wl, windowRight=0,
+                                qPosOffset=rows - 1)
+                oracle.assert_close(out[b].float().cpu().numpy(), want, "f16")
+    finally:
+        ex.setStream(None)
+
+
+@pytest.mark.parametrize("parts", [1, 2, 4, 8])
+def test_sharded_partials_merge_equals_unsharded(ex, parts):
+    """KV sequence cut into `parts` shards: per-shard partials + merge == whole."""
+    import torch
+    from runntime_b200.engine import decode_batched, merge_partials, shard_rows
+    batch, rows, heads, hd = 6, 1000, 8, 52
+    q, kc, vc, _, _, _ = _batched_inputs(batch, rows, heads, heads, hd, "f16", [rows] * batch)
+    dev = torch.device("cuda", 0)
+    qd = q.to(dev)
+    partials = torch.zeros(parts, batch, heads, 2 + hd, dtype=torch.float32, device=dev)
+    out = torch.empty_like(qd)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        for r in range(parts):
+            s, e = shard_rows(rows, parts, r)
+            ks = kc[:, s:e].contiguous().to(dev)
+            vs = vc[:, s:e].contiguous().to(dev)
+            decode_batched(ex, qd, None, ks, vs, dtype="f16", batch=batch, cacheRows=e - s,
+                           qHeads=heads, kvHeads=heads, headDim=hd, kvLen=e - s,
+                           partialsOut=partials[r], splits=0 if r % 2 else 2)
+            ex.sync()
+        merge_partials(ex, partials, parts, batch * heads, hd, out, "f16")
+        ex.sync()
+    finally:
+        ex.setStream(None)
+    # GPU merge == oracle merge of the same partials == unsharded attention
+    host = partials.cpu().numpy().reshape(parts, batch * heads, 2 + hd)
+    oracle.assert_close(out.float().cpu().numpy(), oracle.merge_partials(host), "f16")
+    for b in range(batch):
+        want = sdpa_ref(q[b:b + 1].float().numpy(), kc[b].float().numpy(), vc[b].float().numpy(),
+                        qHeads=heads, kvHeads=heads, headDim=hd)
+        oracle.assert_close(out[b].float().cpu().numpy(), want, "f16")
+
+
+def test_write_rows_standalone(ex):
+    import runntime_b200 as rt
+    dst = np.arange(8 * 6, dtype=np.float32).reshape(8, 6)
+    src = -np.arange(2 * 6, dtype=np.float32).reshape(2, 6) - 1
+    for dtype in ("f32", "f16"):
+        d = ex.upload(dst, [8, 6], dtype)
+        view = rt.writeRows(d, ex.upload(src, [2, 6], dtype), 3)
+        got = rt.toArray(view, ex).reshape(5, 6)
+        want = dst.copy()
+        oracle.write_rows(want, src, 3)
+        assert np.array_equal(got, want[:5])
+        assert np.array_equal(ex.readback(d.buffer, d.shape).reshape(8, 6), want)
+        assert view.buffer is d.buffer

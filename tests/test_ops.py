@@ -1,0 +1,216 @@
+"""The operator boundary: shapes, attrs layout and every refusal of ``sdpa``,
+``sdpaPacked`` and ``writeRows``.  The cases and error texts are the ones the
+reference pins (packages/runntime/test/core/graph/ops/attention.test.ts:23-231,
+packages/runntime/test/core/graph/ops/shape.test.ts:232-280,
+packages/runntime/test/core/nn/layers.test.ts:1112-1131)."""
+import math
+import re
+
+import pytest
+
+from runntime_b200 import MultiHeadAttention, sdpa, sdpaPacked, writeRows
+from runntime_b200.value import DeviceBuffer, ValueMeta, materialized, pending
+
+INF = math.inf
+QH, KVH, HD = 4, 2, 8
+heads = dict(qHeads=QH, kvHeads=KVH, headDim=HD)
+causal = dict(heads, windowLeft=INF, windowRight=0)
+full = dict(heads, windowLeft=INF, windowRight=INF)
+
+
+def meta(dims, dtype="f32"):
+    n = 1
+    for d in dims:
+        n *= d
+    return ValueMeta(n, dtype, tuple(dims))
+
+
+def input_(dims, dtype="f32"):
+    """A pending value of the given shape (an op input not yet computed)."""
+    return pending(meta(dims, dtype), "reshape", [])
+
+
+def materialized_input(dims, dtype="f32"):
+    m = meta(dims, dtype)
+    return materialized(m, DeviceBuffer(0xDEAD0000, m.elems * 4, owned=False))
+
+
+def qkv(qLen, kvLen):
+    return input_([qLen, QH * HD]), input_([kvLen, KVH * HD]), input_([kvLen, KVH * HD])
+
+
+def test_sdpa_gives_one_output_row_per_query_row():
+    q, k, v = qkv(5, 7)
+    c = sdpa(q, k, v, causal)
+    assert c.shape == meta([5, QH * HD])
+    assert c.pending.op == "attn"
+    assert list(c.pending.attrs[:3]) == [QH, KVH, HD]
+
+
+def test_unbounded_window_is_a_large_finite_number():
+    q, k, v = qkv(5, 7)
+    attrs = sdpa(q, k, v, causal).pending.attrs
+    assert math.isfinite(attrs[3]) and attrs[3] > 1e9 and attrs[4] == 0
+
+
+@pytest.mark.parametrize("qLen,kvLen,opts", [
+    (1, 7, dict(causal, qPosOffset=6)),
+    (5, 3, full),
+    (5, 5, dict(heads, windowLeft=2, windowRight=0)),
+    (5, 5, dict(causal, kvHeads=1)),
+])
+def test_sdpa_accepts(qLen, kvLen, opts):
+    q = input_([qLen, QH * HD])
+    kv = input_([kvLen, opts["kvHeads"] * HD])
+    assert sdpa(q, kv, kv, opts).shape == meta([qLen, QH * HD])
+
+
+def test_sinks_and_segments_are_extra_inputs():
+    q, k, v = qkv(5, 5)
+    sinks, segments = input_([QH]), input_([5, 2])
+    c = sdpa(q, k, v, dict(causal, sinks=sinks, segments=segments, maxSegment=3))
+    assert list(c.pending.inputs) == [q, k, v, sinks, segments]
+    assert list(c.pending.attrs[6:10]) == [1, 1, 3, 0]
+
+
+def test_key_bias_is_attrs_not_an_input():
+    q, k, v = qkv(5, 7)
+    c = sdpa(q, k, v, dict(causal, keyBias=dict(start=2, end=7, value=-1.5)))
+    assert list(c.pending.inputs) == [q, k, v]
+    assert list(c.pending.attrs[10:]) == [1, 2, 7, -1.5]
+
+
+@pytest.mark.parametrize("repl,error", [
+    (dict(q=[5, 30]), r"q cols 30 != qHeads\*headDim 32"),
+    (dict(k=[7, 8]), r"k cols 8 != kvHeads\*headDim 16"),
+    (dict(v=[6, 16]), r"v rows 6 != k rows 7"),
+    (dict(v=[7, 8]), r"v cols 8 != kvHeads\*headDim 16"),
+    (dict(v=([7, 16], "f16")), r"must share a dtype, got f32/f32/f16"),
+])
+def test_sdpa_rejects_shapes(repl, error):
+    base = dict(zip("qkv", qkv(5, 7)))
+    for name, spec in repl.items():
+        base[name] = input_(*spec) if isinstance(spec, tuple) else input_(spec)
+    with pytest.raises(ValueError, match=error):
+        sdpa(base["q"], base["k"], base["v"], causal)
+
+
+@pytest.mark.parametrize("opts,error", [
+    (dict(causal, kvHeads=3), r"qHeads 4 not divisible by kvHeads 3"),
+    (dict(causal, kvHeads=0), r"not divisible by kvHeads 0"),
+    (dict(causal, windowLeft=-1), r"windowLeft -1 must be a non-negative integer"),
+    (dict(causal, windowRight=0.5), r"windowRight 0.5 must be"),
+    (dict(causal, windowLeft=1.5), r"windowLeft 1.5 must be a non-negative integer or Infinity"),
+    (dict(causal, qPosOffset=-1), r"qPosOffset -1 must be a non-negative integer"),
+    (dict(causal, qPosOffset=3), r"qPosOffset\+qLen 8 exceeds key rows kvLen 7"),
+    (dict(causal, sinks=input_([2])), r"sinks must be f32 with 4 elems"),
+    (dict(causal, segments=input_([5])), r"segments must be f32 \[qLen, 2\] = 10 elems"),
+    (dict(causal, maxSegment=3), r"maxSegment needs segments"),
+    (dict(causal, segments=input_([5, 2]), maxSegment=1.5),
+     r"maxSegment 1.5 must be a positive integer"),
+    (dict(causal, keyBias=dict(start=3, end=8, value=1)),
+     r"keyBias keys \[3, 8\) must lie within the 7 keys"),
+    (dict(causal, keyBias=dict(start=4, end=2, value=1)), r"keyBias keys \[4, 2\)"),
+    (dict(causal, keyBias=dict(start=0.5, end=2, value=1)), r"keyBias keys \[0.5, 2\)"),
+    (dict(causal, keyBias=dict(start=0, end=2, value=math.nan)),
+     r"keyBias value NaN must be finite"),
+])
+def test_sdpa_rejects_options(opts, error):
+    q, k, v = qkv(5, 7)
+    if opts["kvHeads"] not in (KVH,):
+        pass
+    with pytest.raises(ValueError, match=error):
+        sdpa(q, k, v, opts)
+
+
+def test_sdpa_rejects_segments_and_key_bias_on_decode():
+    q, k, v = qkv(1, 7)
+    with pytest.raises(ValueError, match=r"segments need qLen > 1"):
+        sdpa(q, k, v, dict(causal, qPosOffset=6, segments=input_([1, 2])))
+    with pytest.raises(ValueError, match=r"keyBias needs qLen > 1"):
+        sdpa(q, k, v, dict(causal, qPosOffset=6, keyBias=dict(start=0, end=2, value=1)))
+
+
+def test_head_size_limits():
+    x = input_([2, 512])
+    assert sdpa(x, x, x, dict(full, qHeads=1, kvHeads=1, headDim=512)).shape == meta([2, 512])
+    for qLen, hd, mx in ((1, 160, 128), (2, 640, 512)):
+        x = input_([qLen, hd])
+        with pytest.raises(ValueError, match=re.escape(f"headDim {hd} exceeds the kernel's max ({mx})")):
+            sdpa(x, x, x, dict(full, qHeads=1, kvHeads=1, headDim=hd))
+
+
+def test_queries_past_keys_under_bounded_right_window():
+    q = input_([4, 16])
+    kv = input_([3, 8])
+    with pytest.raises(ValueError, match=r"qPosOffset\+qLen 4 exceeds key rows kvLen 3"):
+        sdpa(q, kv, kv, dict(qHeads=2, kvHeads=1, headDim=8, windowLeft=INF, windowRight=0))
+
+
+def test_want2d_message():
+    with pytest.raises(ValueError, match=r"sdpa: expected a 2D f32 or f16 tensor, got dims=\[5\] dtype=f32"):
+        sdpa(input_([5]), input_([5, 16]), input_([5, 16]), causal)
+
+
+def packed(t):
+    return input_([t, (QH + 2 * KVH) * HD])
+
+
+def test_sdpa_packed_reads_one_tensor():
+    c = sdpaPacked(packed(5), causal)
+    assert c.shape == meta([5, QH * HD])
+    assert c.pending.attrs[-1] == 1 and len(c.pending.attrs) == 10
+    assert len(c.pending.inputs) == 1
+
+
+@pytest.mark.parametrize("x,opts,error", [
+    (input_([5, 60]), causal, r"qkv cols 60 != \(qHeads \+ 2\*kvHeads\)\*headDim = 64"),
+    (packed(1), causal, r"qLen must be > 1"),
+    (packed(5), dict(causal, qPosOffset=1), r"exceeds key rows"),
+    (input_([5, 3 * 130]), dict(qHeads=1, kvHeads=1, headDim=130, windowLeft=INF, windowRight=0),
+     r"headDim 130 exceeds the kernel's max \(128\)"),
+])
+def test_sdpa_packed_rejects(x, opts, error):
+    with pytest.raises(ValueError, match=error):
+        sdpaPacked(x, opts)
+
+
+def test_sdpa_packed_allows_offset_with_unbounded_right():
+    assert sdpaPacked(packed(5), dict(full, qPosOffset=1)).shape == meta([5, QH * HD])
+
+
+cache = materialized_input([8, 4])
+
+
+def test_write_rows_returns_view_up_to_last_written_row():
+    c = writeRows(cache, input_([2, 4]), 3)
+    assert c.shape == meta([5, 4]) and list(c.pending.attrs) == [3]
+    assert c.pending.op == "writeRows"
+    assert writeRows(cache, input_([2, 4]), 6).shape == meta([8, 4])
+
+
+@pytest.mark.parametrize("dst,src,start,error", [
+    (input_([8, 4]), input_([2, 4]), 0, r"dst must be a materialized"),
+    (cache, input_([2, 4]), 7, r"rows \[7, 9\) exceed dst capacity 8"),
+    (cache, input_([2, 4]), -1, r"exceed dst capacity"),
+    (cache, input_([2, 5]), 0, r"col mismatch"),
+    (cache, input_([2, 4], "f16"), 0, r"dtype mismatch"),
+])
+def test_write_rows_rejects(dst, src, start, error):
+    with pytest.raises(ValueError, match=error):
+        writeRows(dst, src, start)
+
+
+def test_multi_head_attention_module():
+    mha = MultiHeadAttention(dict(causal, sinks=True))
+    assert list(mha.parameters()) == ["sinks"]
+    assert mha.sinks.shape == ValueMeta(QH, "f32", (QH,)) and mha.sinks.pinned
+    with pytest.raises(RuntimeError):
+        mha.forward(*qkv(5, 5))
+    mha.sinks.set(input_([QH]))
+    q, k, v = qkv(5, 7)
+    c = mha.forward(q, k, v, dict(qPosOffset=2))
+    assert c.pending.attrs[5] == 2 and c.pending.attrs[6] == 1
+    assert MultiHeadAttention(causal).parameters() == {}
+    c = MultiHeadAttention(causal).forwardPacked(packed(5))
+    assert c.pending.attrs[9] == 1

@@ -1,0 +1,89 @@
+"""Host side of KV-sequence-sharded decode on CPU ranks (gloo, world size 2 and
+3): the shard plan covers the sequence, the exchange is one all-gather of
+(m, l, acc) partials, and merging them equals unsharded attention.  The
+per-shard partials here come from plain numpy: only the plumbing is under
+test, the kernels have their own GPU suite."""
+import math
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import oracle
+from runntime_b200.engine import shard_rows
+
+
+def test_shard_rows_partition_the_sequence():
+    for total in (1, 7, 8192, 8193):
+        for world in (1, 2, 3, 8):
+            spans = [shard_rows(total, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == total
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [e - s for s, e in spans]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def _partials(q, k, v, heads, hd):
+    """(m, l, acc) per head over the given rows, natural-log domain."""
+    out = np.zeros((heads, 2 + hd), np.float32)
+    for h in range(heads):
+        if k.shape[0] == 0:
+            out[h, 0] = -1e30
+            continue
+        s = k[:, h * hd:(h + 1) * hd].astype(np.float64) @ q[h * hd:(h + 1) * hd].astype(np.float64)
+        m = s.max()
+        p = np.exp(s - m)
+        out[h, 0], out[h, 1] = m, p.sum()
+        out[h, 2:] = p @ v[:, h * hd:(h + 1) * hd].astype(np.float64)
+    return out
+
+
+def _worker(rank, world, port, rows, result):
+    import torch
+    import torch.distributed as dist
+    from runntime_b200.engine import ShardedDecode
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        batch, heads, hd = 3, 4, 8
+        rng = np.random.default_rng(0)
+        q = rng.standard_normal((batch, heads * hd)).astype(np.float32)
+        k = rng.standard_normal((batch, rows, heads * hd)).astype(np.float32)
+        v = rng.standard_normal((batch, rows, heads * hd)).astype(np.float32)
+        sd = ShardedDecode()
+        assert (sd.world, sd.rank) == (world, rank)
+        s, e = shard_rows(rows, world, rank)
+        mine = np.stack([_partials(q[b], k[b, s:e], v[b, s:e], heads, hd) for b in range(batch)])
+        gathered = sd.gather(torch.from_numpy(mine.reshape(batch * heads, 2 + hd)))
+        assert tuple(gathered.shape) == (world, batch * heads, 2 + hd)
+        assert np.array_equal(gathered[rank].numpy(), mine.reshape(batch * heads, 2 + hd))
+        got = oracle.merge_partials(gathered.numpy())
+        for b in range(batch):
+            want = oracle.sdpa_ref(q[b:b + 1], k[b], v[b], qHeads=heads, kvHeads=heads, headDim=hd)
+            assert np.allclose(got.reshape(batch, -1)[b], want.reshape(-1), rtol=1e-5, atol=1e-6)
+        result[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("world,rows", [(2, 64), (3, 2)])
+def test_sharded_decode_exchange_on_cpu_ranks(world, rows):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    result = ctx.Array("i", world)
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, rows, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert list(result) == [1] * world
