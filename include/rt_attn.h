@@ -65,6 +65,11 @@ RT_API int rt_ctx_destroy(rt_ctx* ctx);
  * the library's kernels order with the caller's other work.  external == 0
  * restores the context's stream. */
 RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
+/* Context options.  RT_OPT_PREFILL_TC (default 1): route eligible f16 prefill
+ * shapes to the tensor-core kernel; 0 sends every prefill to the FP32-pipe
+ * kernel (both compute the same op; the switch exists for testing). */
+#define RT_OPT_PREFILL_TC 1
+RT_API int rt_ctx_set_option(rt_ctx* ctx, int option, int value);
 /* Message of the last failure on this context (or, with ctx == NULL, of the
  * last failed call on this thread that had no context to record it in). */
 RT_API const char* rt_last_error(const rt_ctx* ctx);

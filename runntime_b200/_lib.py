@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "librt_attn.so")
 
 RT_F32, RT_F16 = 0, 1
 WINDOW_INF = 0x3FFFFFFF
+OPT_PREFILL_TC = 1
 DTYPE_CODE = {"f32": RT_F32, "f16": RT_F16}
 
 
@@ -50,6 +51,7 @@ SYMBOLS = {
     "rt_ctx_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
     "rt_ctx_destroy": (C.c_int, [C.c_void_p]),
     "rt_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
+    "rt_ctx_set_option": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "rt_last_error": (C.c_char_p, [C.c_void_p]),
     "rt_sync": (C.c_int, [C.c_void_p]),
     "rt_launch_count": (C.c_int64, [C.c_void_p]),

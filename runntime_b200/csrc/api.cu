@@ -20,6 +20,7 @@ struct rt_ctx {
   size_t counterCount;
   int* statusDev;
   int64_t launches;
+  int useTc;
   std::string err;
 };
 
@@ -262,6 +263,7 @@ int rt_ctx_create(int device, rt_ctx** out) {
   ctx->counters = nullptr;
   ctx->counterCount = 0;
   ctx->launches = 0;
+  ctx->useTc = 1;
   if ((e = cudaSetDevice(device)) != cudaSuccess ||
       (e = cudaStreamCreateWithFlags(&ctx->own, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaMalloc(&ctx->statusDev, sizeof(int))) != cudaSuccess ||
@@ -294,6 +296,15 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
   RT_ENTER(ctx);
   ctx->stream = external ? static_cast<cudaStream_t>(cuda_stream) : ctx->own;
   return RT_OK;
+}
+
+int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
+  RT_ENTER(ctx);
+  if (option == RT_OPT_PREFILL_TC) {
+    ctx->useTc = value != 0;
+    return RT_OK;
+  }
+  return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: unknown option %d", option);
 }
 
 const char* rt_last_error(const rt_ctx* ctx) {
@@ -353,9 +364,10 @@ int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* ho
   return rt_sync(ctx);
 }
 
-static const char* route_of(const rt_attn_args* a) {
+static const char* route_of(const rt_ctx* ctx, const rt_attn_args* a) {
   if (a->qLen == 1) return "decode";
-  return rt::prefill_tc_supported(to_params(a), a->dtype) ? "prefill_tc" : "prefill_simt";
+  return (ctx->useTc && rt::prefill_tc_supported(to_params(a), a->dtype)) ? "prefill_tc"
+                                                                          : "prefill_simt";
 }
 
 int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
@@ -363,7 +375,7 @@ int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
   if (!args || !route) return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_route: NULL argument");
   int s = validate_attn(ctx, args);
   if (s != RT_OK) return s;
-  *route = route_of(args);
+  *route = route_of(ctx, args);
   return RT_OK;
 }
 
@@ -393,7 +405,7 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
     return run_decode(ctx, p, a->dtype);
   }
   const rt::AttnParams p = to_params(a);
-  if (rt::prefill_tc_supported(p, a->dtype)) {
+  if (ctx->useTc && rt::prefill_tc_supported(p, a->dtype)) {
     std::string err;
     cudaError_t e = rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
     if (e != cudaSuccess)

@@ -1,14 +1,460 @@
-// Tensor-core prefill (placeholder until the tcgen05 kernel lands): no shape is
-// routed here yet, so every prefill takes the FP32-pipe kernel.
+// Tensor-core prefill attention for f16 storage: a flash-style fused kernel on
+// the 5th-generation tensor cores (tcgen05) with accumulators in tensor memory.
+//
+// One CTA owns 128 query rows of one query head.  Roles:
+//   warps 0-3  softmax: one thread per query row (= one TMEM lane).  Reads the
+//              scores S from TMEM, applies the band/segment mask, keeps the
+//              online-softmax state in fp32, writes the probabilities P back to
+//              TMEM as f16 (over the S columns it has just read), rescales the
+//              output accumulator only when a row's max has grown by more than
+//              2^8, and runs the epilogue (O / l -> f16 -> global).
+//   warp 4     TMA producer: Q once, then K and V tiles of BK keys into a
+//              shared-memory ring (128-byte swizzle), one mbarrier per tile.
+//   warp 5     MMA issuer: S = Q K^T (A, B from shared memory) into one of two
+//              S buffers, and O += P V (A = P from TMEM, B = V tile, MN-major).
+//              S of tile j+1 is issued before P V of tile j so that the tensor
+//              pipe works while the softmax warps are busy.
+//
+// Semantics are the 'attn' op's (window, segments / per-sequence lengths, GQA,
+// sinks, key bias, no score scale, empty rows -> zeros); see rt_attn.h.  It
+// replaces attnFlash (packages/runntime/src/core/kernels/attention/
+// attnFlash.ts:93-276), which has no tensor-core path.
+//
+// Every wait is bounded (sm100.cuh); a wait that runs out sets the status word
+// and the CTA winds down through the common exit that frees its tensor memory.
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace rt {
+namespace {
 
-bool prefill_tc_supported(const AttnParams&, int) { return false; }
+using namespace sm100;
 
-cudaError_t launch_prefill_tc(const AttnParams&, int, int*, cudaStream_t, std::string* err) {
-  *err = "tensor-core prefill is not built";
-  return cudaErrorNotSupported;
+constexpr int BM = 128;             // query rows per CTA
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = 192;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+template <int HD>
+struct Cfg {
+  static constexpr int BK = HD <= 128 ? 128 : 64;          // keys per tile
+  static constexpr int CHUNKS = HD / 64;                   // 64-column (128-byte) chunks of a row
+  static constexpr int Q_BYTES = BM * HD * 2;
+  static constexpr int KV_BYTES = BK * HD * 2;             // one K (or V) tile
+  static constexpr int STAGES = (220 * 1024 - Q_BYTES) / (2 * KV_BYTES) > 4
+                                    ? 4
+                                    : (220 * 1024 - Q_BYTES) / (2 * KV_BYTES);
+  static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + 1024;  // + alignment slack
+  static constexpr int S_COLS = BK;                        // f32 score columns per buffer
+  static constexpr int O_COL = 2 * S_COLS;                 // O accumulator after the two S buffers
+  static constexpr int TMEM_COLS = 512;
+  static_assert(O_COL + HD <= TMEM_COLS, "tensor memory budget");
+  static_assert(STAGES >= 2, "need a double-buffered ring");
+};
+
+struct Barriers {
+  uint64_t fullQ;
+  uint64_t fullK[4], fullV[4], empty[4];
+  uint64_t sFull[2], pReady[2], pvDone[2];
+};
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version bit set.
+// Offsets are in bytes; the hardware fields drop the 4 low bits.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lboBytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sboBytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: f16 A and B, f32 D, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool bMnMajor) {
+  return (1u << 4)                       // D format f32
+         | (0u << 7) | (0u << 10)        // A, B format f16
+         | (0u << 15)                    // A K-major
+         | ((bMnMajor ? 1u : 0u) << 16)  // B major
+         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                  const __grid_constant__ CUtensorMap mapV, const AttnParams p, int* status) {
+  using C = Cfg<HD>;
+  constexpr int BK = C::BK;
+  extern __shared__ unsigned char smemRaw[];
+  __shared__ Barriers bars;
+  __shared__ uint32_t sTmemBase;
+  __shared__ int sAbort;
+  __shared__ int sLoMin[4], sEndMax[4];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Long rows first: under a causal mask the last row tile has the most keys.
+  const int qTile = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y;
+  const int kvh = h / (p.qHeads / p.kvHeads);
+  const int64_t row0 = (int64_t)qTile * BM;
+
+  // 1024-byte aligned carve-up: swizzle atoms must start on 1024-byte lines.
+  const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;
+  const uint32_t sQ = smemBase;
+  const uint32_t sKV = sQ + C::Q_BYTES;  // stage s: K at sKV + s*2*KV_BYTES, V right after
+
+  if (tid == 0) {
+    sAbort = 0;
+    mbar_init(smem_u32(&bars.fullQ), 1);
+    for (int s = 0; s < C::STAGES; s++) {
+      mbar_init(smem_u32(&bars.fullK[s]), 1);
+      mbar_init(smem_u32(&bars.fullV[s]), 1);
+      mbar_init(smem_u32(&bars.empty[s]), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(smem_u32(&bars.sFull[b]), 1);
+      mbar_init(smem_u32(&bars.pReady[b]), kSoftmaxThreads);
+      mbar_init(smem_u32(&bars.pvDone[b]), 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sTmemBase), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+
+  // Band of this thread's row (softmax threads) and of the whole row tile.
+  int lo = 1, end = 0;  // empty
+  if (tid < kSoftmaxThreads) {
+    const int64_t row = row0 + tid;
+    if (row < p.qLen) {
+      int64_t l64, e64;
+      row_band(p, row, l64, e64);
+      if (l64 <= e64) {
+        lo = (int)l64;
+        end = (int)e64;
+      }
+    }
+    int wl = lo <= end ? lo : INT_MAX, we = lo <= end ? end : -1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      wl = min(wl, __shfl_xor_sync(0xffffffffu, wl, o));
+      we = max(we, __shfl_xor_sync(0xffffffffu, we, o));
+    }
+    if (lane == 0) {
+      sLoMin[warp] = wl;
+      sEndMax[warp] = we;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sTmemBase;
+  const int tileLo = min(min(sLoMin[0], sLoMin[1]), min(sLoMin[2], sLoMin[3]));
+  const int tileEnd = max(max(sEndMax[0], sEndMax[1]), max(sEndMax[2], sEndMax[3]));
+  const int kt0 = tileEnd >= 0 ? tileLo / BK : 0;
+  const int nTiles = tileEnd >= 0 ? tileEnd / BK - kt0 + 1 : 0;
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && nTiles > 0) {
+      prefetch_tensormap(&mapQ);
+      prefetch_tensormap(&mapK);
+      prefetch_tensormap(&mapV);
+      mbar_expect_tx(smem_u32(&bars.fullQ), C::Q_BYTES);
+      for (int c = 0; c < C::CHUNKS; c++)
+        tma_load_2d(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
+      for (int j = 0; j < nTiles; j++) {
+        const int s = j % C::STAGES;
+        if (j >= C::STAGES &&
+            !mbar_wait(smem_u32(&bars.empty[s]), ((j / C::STAGES) - 1) & 1, &sAbort))
+          break;
+        const int key0 = (kt0 + j) * BK;
+        const uint32_t dK = sKV + s * 2 * C::KV_BYTES, dV = dK + C::KV_BYTES;
+        mbar_expect_tx(smem_u32(&bars.fullK[s]), C::KV_BYTES);
+        for (int c = 0; c < C::CHUNKS; c++)
+          tma_load_2d(dK + c * (BK * 128), &mapK, kvh * HD + c * 64, key0, smem_u32(&bars.fullK[s]));
+        mbar_expect_tx(smem_u32(&bars.fullV[s]), C::KV_BYTES);
+        for (int c = 0; c < C::CHUNKS; c++)
+          tma_load_2d(dV + c * (BK * 128), &mapV, kvh * HD + c * 64, key0, smem_u32(&bars.fullV[s]));
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0 && nTiles > 0) {
+      constexpr uint32_t idescS = instr_desc(BK, false);
+      constexpr uint32_t idescO = instr_desc(HD, true);
+      bool ok = mbar_wait(smem_u32(&bars.fullQ), 0, &sAbort);
+      for (int j = 0; ok && j <= nTiles; j++) {
+        if (j < nTiles) {
+          const int s = j % C::STAGES, b = j & 1;
+          ok = mbar_wait(smem_u32(&bars.fullK[s]), (j / C::STAGES) & 1, &sAbort);
+          if (ok && j >= 2) ok = mbar_wait(smem_u32(&bars.pvDone[b]), ((j - 2) >> 1) & 1, &sAbort);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t dK = sKV + s * 2 * C::KV_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; kk++) {
+            // K-major operands: 16 elements (32 bytes) further along the swizzled row per step
+            const uint64_t aDesc = smem_desc(sQ + (kk >> 2) * (BM * 128) + (kk & 3) * 32, 16, 1024);
+            const uint64_t bDesc = smem_desc(dK + (kk >> 2) * (BK * 128) + (kk & 3) * 32, 16, 1024);
+            mma_f16_ss(tmem + b * C::S_COLS, aDesc, bDesc, idescS, kk > 0);
+          }
+          tc_commit(smem_u32(&bars.sFull[b]));
+        }
+        if (j >= 1) {
+          const int t = j - 1, s = t % C::STAGES, b = t & 1;
+          ok = mbar_wait(smem_u32(&bars.pReady[b]), (t >> 1) & 1, &sAbort);
+          if (ok) ok = mbar_wait(smem_u32(&bars.fullV[s]), (t / C::STAGES) & 1, &sAbort);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t dV = sKV + s * 2 * C::KV_BYTES + C::KV_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; kk++) {
+            // V is [keys][hd] (MN-major B): 16 keys = 2048 bytes further per step;
+            // LBO = next 64 columns of hd, SBO = next 8 keys.
+            const uint64_t bDesc = smem_desc(dV + kk * 2048, BK * 128, 1024);
+            // P: f16 pairs, 8 columns of TMEM per 16 keys
+            mma_f16_ts(tmem + C::O_COL, tmem + b * C::S_COLS + kk * 8, bDesc, idescO,
+                       (t > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bars.empty[s]));
+          tc_commit(smem_u32(&bars.pvDone[b]));
+        }
+      }
+    }
+  } else {
+    // ------------------------------ softmax + epilogue ------------------------
+    const uint32_t laneBase = (uint32_t)(warp * 32) << 16;
+    float mref = kNegSeed, l = 0.f;
+    if (p.sinks) {
+      mref = p.sinks[h];  // log2 domain: sink * ln2 * log2e
+      l = 1.f;
+    }
+    bool ok = true;
+    for (int j = 0; j < nTiles && ok; j++) {
+      const int b = j & 1;
+      const int key0 = (kt0 + j) * BK;
+      ok = mbar_wait(smem_u32(&bars.sFull[b]), (j >> 1) & 1, &sAbort);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t sv[BK];
+#pragma unroll
+      for (int c = 0; c < BK; c += 32)
+        tmem_ld32(tmem + laneBase + b * C::S_COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
+      tmem_wait_ld();
+      const bool fullTile = lo <= key0 && end >= key0 + BK - 1;
+      if (!fullTile || p.hasKeyBias) {
+#pragma unroll
+        for (int c = 0; c < BK; c++) {
+          const int jj = key0 + c;
+          float s = __uint_as_float(sv[c]);
+          if (p.hasKeyBias && jj >= p.biasStart && jj < p.biasEnd) s += p.biasValue;
+          sv[c] = __float_as_uint((jj >= lo && jj <= end) ? s : -INFINITY);
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BK; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
+      mx *= kLog2e;
+      // Lazy rescale: only when some row's max grew by more than 2^8 (whole warp
+      // together, because TMEM loads/stores are warp-collective).
+      const bool grow = mx > mref + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float mnew = fmaxf(mref, mx);
+        const float f = fast_exp2(mref - mnew);
+        mref = mnew;
+        l *= f;
+        if (j > 0) {
+          // O holds the tiles up to j-1: wait for the last P V to land, then scale.
+          ok = mbar_wait(smem_u32(&bars.pvDone[(j - 1) & 1]), ((j - 1) >> 1) & 1, &sAbort);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tmem + laneBase + C::O_COL + c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
+            tmem_st32(tmem + laneBase + C::O_COL + c, o);
+          }
+        }
+      }
+      // p = 2^(s*log2e - mref), packed to f16 pairs over the S columns just read
+      float sum = 0.f;
+      uint32_t pk[BK / 2];
+#pragma unroll
+      for (int c = 0; c < BK; c += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), kLog2e, -mref));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), kLog2e, -mref));
+        sum += p0 + p1;
+        const __half2 hp = __floats2half2_rn(p0, p1);
+        pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+      }
+      l += sum;
+#pragma unroll
+      for (int c = 0; c < BK / 2; c += 32)
+        tmem_st32(tmem + laneBase + b * C::S_COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&pk[c]));
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars.pReady[b]));
+    }
+
+    // Epilogue: O / l -> f16 -> global.  Rows that saw no key are zeros.
+    const int64_t row = row0 + tid;
+    __half* out = static_cast<__half*>(p.out) + row * ((int64_t)p.qHeads * HD) + (int64_t)h * HD;
+    if (nTiles > 0 && ok) {
+      ok = mbar_wait(smem_u32(&bars.pvDone[(nTiles - 1) & 1]), ((nTiles - 1) >> 1) & 1, &sAbort);
+      if (ok) {
+        tc_fence_after_sync();
+        const float invL = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tmem + laneBase + C::O_COL + c, o);
+          tmem_wait_ld();
+          if (row < p.qLen) {
+            uint4 pkd[4];
+            uint32_t* w = reinterpret_cast<uint32_t*>(pkd);
+#pragma unroll
+            for (int x = 0; x < 32; x += 2) {
+              // a row with an empty band has l = 0 (or only the sink): force zeros
+              const float a = lo <= end ? __uint_as_float(o[x]) * invL : 0.f;
+              const float bb = lo <= end ? __uint_as_float(o[x + 1]) * invL : 0.f;
+              const __half2 hp = __floats2half2_rn(a, bb);
+              w[x / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+            }
+#pragma unroll
+            for (int v = 0; v < 4; v++) reinterpret_cast<uint4*>(out + c)[v] = pkd[v];
+          }
+        }
+      }
+    } else if (nTiles == 0 && row < p.qLen) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int c = 0; c < HD; c += 8) *reinterpret_cast<uint4*>(out + c) = z;
+    }
+  }
+
+  // Common exit: every role arrives here, then the allocating warp frees TMEM.
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && sAbort) atomicOr(status, kStatusWaitTimeout);
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// [rows, cols] f16 row-major with `strideElems` between rows; box = 64 columns x boxRows.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t strideElems,
+              int boxRows, std::string* err) {
+  auto fn = encode_fn();
+  if (!fn) {
+    *err = "cuTensorMapEncodeTiled is not available from the driver";
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)strideElems * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)boxRows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *err = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r);
+    return false;
+  }
+  return true;
+}
+
+template <int HD>
+cudaError_t launch(const AttnParams& p, int* status, cudaStream_t s, std::string* err) {
+  using C = Cfg<HD>;
+  CUtensorMap mq, mk, mv;
+  if (!make_map(&mq, p.q, p.qLen, (int64_t)p.qHeads * HD, p.qStride, BM, err) ||
+      !make_map(&mk, p.k, p.kvLen, (int64_t)p.kvHeads * HD, p.kvStride, C::BK, err) ||
+      !make_map(&mv, p.v, p.kvLen, (int64_t)p.kvHeads * HD, p.kvStride, C::BK, err))
+    return cudaErrorInvalidValue;
+  auto kern = prefill_tc_kernel<HD>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+  if (e != cudaSuccess) return e;
+  dim3 grid((unsigned)((p.qLen + BM - 1) / BM), (unsigned)p.qHeads);
+  kern<<<grid, kThreads, C::SMEM, s>>>(mq, mk, mv, p, status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool prefill_tc_supported(const AttnParams& p, int dtype) {
+  if (dtype != RT_F16) return false;
+  if (p.hd != 64 && p.hd != 128 && p.hd != 256) return false;
+  if (p.qLen < 2 || p.qLen >= (1ll << 31) - BM || p.kvLen >= (1ll << 31) - 256) return false;
+  // TMA: 16-byte aligned bases and row pitches
+  auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  if (!al(p.q) || !al(p.k) || !al(p.v) || !al(p.out)) return false;
+  if ((p.qStride * 2) % 16 || (p.kvStride * 2) % 16) return false;
+  if (!encode_fn()) return false;
+  return true;
+}
+
+cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaStream_t s,
+                              std::string* err) {
+  (void)dtype;
+  switch (p.hd) {
+    case 64: return launch<64>(p, status, s, err);
+    case 128: return launch<128>(p, status, s, err);
+    case 256: return launch<256>(p, status, s, err);
+  }
+  *err = "unsupported head size";
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace rt

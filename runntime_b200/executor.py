@@ -56,6 +56,9 @@ class CudaExecutor:
         check(self._lib.rt_ctx_set_stream(self.ctx, C.c_void_p(cuda_stream or 0),
                                           0 if cuda_stream is None else 1), self.ctx)
 
+    def setOption(self, option: int, value: int) -> None:
+        check(self._lib.rt_ctx_set_option(self.ctx, option, value), self.ctx)
+
     def sync(self) -> None:
         check(self._lib.rt_sync(self.ctx), self.ctx)
 

@@ -1,0 +1,119 @@
+"""The tensor-core prefill kernel (f16, head sizes 64/128/256): multi-tile
+shapes, every mask family, GQA, sinks, key bias, packed qkv and the padded-batch
+form, against the f64 oracle (f16 tolerance: atol 2e-3 + rtol 4e-3) and against
+the FP32-pipe kernel on the same inputs."""
+import math
+
+import numpy as np
+import pytest
+
+import cases
+import oracle
+from gpu_harness import check_sdpa, ex, run_sdpa  # noqa: F401
+from oracle import SdpaCase, make_inputs
+
+pytestmark = pytest.mark.gpu
+INF = math.inf
+
+
+def _c(**kw):
+    return SdpaCase(**kw)
+
+
+TC_CASES = [
+    ("one_tile_exact", _c(qLen=128, kvLen=128, qHeads=2, kvHeads=2, headDim=128)),
+    ("two_rows", _c(qLen=2, kvLen=2, qHeads=1, kvHeads=1, headDim=64)),
+    ("causal_1000", _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=1, headDim=128, windowRight=0)),
+    ("causal_1000_hd64", _c(qLen=1000, kvLen=1000, qHeads=4, kvHeads=2, headDim=64,
+                            windowRight=0)),
+    ("causal_700_hd256", _c(qLen=700, kvLen=700, qHeads=3, kvHeads=1, headDim=256,
+                            windowRight=0)),
+    ("sliding_both_hd256", _c(qLen=900, kvLen=900, qHeads=3, kvHeads=1, headDim=256,
+                              windowLeft=200, windowRight=200)),
+    ("sliding_left_300", _c(qLen=1500, kvLen=1500, qHeads=2, kvHeads=2, headDim=128,
+                            windowLeft=300, windowRight=0)),
+    ("cross_300x2000", _c(qLen=300, kvLen=2000, qHeads=2, kvHeads=1, headDim=128)),
+    ("qposoffset_into_cache", _c(qLen=200, kvLen=900, qHeads=2, kvHeads=1, headDim=64,
+                                 windowRight=0, qPosOffset=700)),
+    ("segments_two_halves", _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=2, headDim=128,
+                               segments=True)),
+    ("segments_causal_sinks", _c(qLen=777, kvLen=777, qHeads=4, kvHeads=2, headDim=64,
+                                 segments=True, windowRight=0, sinks=True)),
+    ("packed_causal", _c(qLen=600, kvLen=600, qHeads=4, kvHeads=2, headDim=64, packed=True,
+                         windowRight=0)),
+    ("packed_segments_sinks_hd128", _c(qLen=520, kvLen=520, qHeads=2, kvHeads=1, headDim=128,
+                                       packed=True, segments=True, sinks=True)),
+    ("keybias_reverb", _c(qLen=335, kvLen=640, qHeads=12, kvHeads=6, headDim=128, keyBias=True)),
+    ("keybias_sinks_segments", _c(qLen=400, kvLen=400, qHeads=2, kvHeads=1, headDim=64,
+                                  keyBias=True, sinks=True, segments=True)),
+    ("rows_see_no_key", _c(qLen=300, kvLen=150, qHeads=2, kvHeads=1, headDim=64, windowLeft=0,
+                           sinks=True)),
+    ("long_keys_many_tiles", _c(qLen=130, kvLen=5000, qHeads=1, kvHeads=1, headDim=128)),
+    ("window_narrower_than_tile", _c(qLen=1024, kvLen=1024, qHeads=1, kvHeads=1, headDim=128,
+                                     windowLeft=5, windowRight=3)),
+]
+
+
+@pytest.mark.parametrize("name,c", TC_CASES, ids=[n for n, _ in TC_CASES])
+def test_tensor_core_prefill_against_oracle(ex, name, c):
+    check_sdpa(ex, c, "f16", route="prefill_tc")
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+def test_every_option_takes_the_tensor_core_route(ex, hd):
+    for name, c in cases.option_cases(300, hd):
+        if c.packed and hd > 128:
+            continue
+        check_sdpa(ex, c, "f16", route="prefill_tc")
+
+
+def test_matches_the_fp32_pipe_kernel(ex):
+    from runntime_b200._lib import OPT_PREFILL_TC
+    c = _c(qLen=900, kvLen=900, qHeads=4, kvHeads=2, headDim=128, windowLeft=400, windowRight=0,
+           sinks=True)
+    x = make_inputs(c, "f16")
+    tc = run_sdpa(ex, x)
+    assert ex.dispatches[-1] == "prefill_tc"
+    ex.setOption(OPT_PREFILL_TC, 0)
+    try:
+        simt = run_sdpa(ex, x)
+        assert ex.dispatches[-1] == "prefill_simt"
+    finally:
+        ex.setOption(OPT_PREFILL_TC, 1)
+    assert np.abs(tc - simt).max() < 2e-3
+
+
+def test_large_scores_need_the_rescale_path(ex):
+    """Scores that keep growing along the keys force repeated accumulator rescales."""
+    import runntime_b200 as rt
+    T, hd = 640, 64
+    rng = np.random.default_rng(1)
+    q = np.ones((T, hd), np.float32) * 0.25
+    k = (np.arange(T, dtype=np.float32)[:, None] / 16.0 * np.ones((1, hd), np.float32)) / 4
+    k = oracle.round_f16(k.astype(np.float32))
+    v = oracle.round_f16(rng.standard_normal((T, hd)).astype(np.float32))
+    opts = dict(qHeads=1, kvHeads=1, headDim=hd, windowLeft=INF, windowRight=INF)
+    out = rt.toArray(rt.sdpa(ex.upload(q, [T, hd], "f16"), ex.upload(k, [T, hd], "f16"),
+                             ex.upload(v, [T, hd], "f16"), opts), ex)
+    assert ex.dispatches[-1] == "prefill_tc"
+    want = oracle.sdpa_ref(q, k, v, qHeads=1, kvHeads=1, headDim=hd)
+    oracle.assert_close(out, want, "f16")
+
+
+def test_n_of_1_inputs_at_long_sequence_keep_the_tolerance(ex):
+    """N(0,1) values at head size 128 over 4096 keys: P rounded to f16 for the
+    second product must still meet 2e-3 absolute."""
+    import runntime_b200 as rt
+    T, hd = 4096, 128
+    rng = np.random.default_rng(2)
+    f = hd ** -0.25
+    q = oracle.round_f16((rng.standard_normal((256, hd)) * f).astype(np.float32))
+    k = oracle.round_f16((rng.standard_normal((T, hd)) * f).astype(np.float32))
+    v = oracle.round_f16(rng.standard_normal((T, hd)).astype(np.float32))
+    opts = dict(qHeads=1, kvHeads=1, headDim=hd, windowLeft=INF, windowRight=0,
+                qPosOffset=T - 256)
+    out = rt.toArray(rt.sdpa(ex.upload(q, [256, hd], "f16"), ex.upload(k, [T, hd], "f16"),
+                             ex.upload(v, [T, hd], "f16"), opts), ex)
+    want = oracle.sdpa_ref(q, k, v, qHeads=1, kvHeads=1, headDim=hd, windowRight=0,
+                           qPosOffset=T - 256)
+    assert np.abs(out.reshape(want.shape) - want).max() <= 2e-3
