@@ -193,6 +193,33 @@ typedef struct {
 
 RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);
 
+/* rt_attn_decode for callers that may not allocate.  It has no counterpart in
+ * the reference.  Who needs it: a host that fixed its device-memory budget
+ * before the model started (a real-time transcription loop, an embedded
+ * player), code running inside another framework's memory pool, or a caller
+ * that holds the allocator lock — for them cudaMalloc is off limits, and
+ * rt_attn_decode needs a context, which allocates a stream, a status word and
+ * a split scratch that grows on demand.  This call takes no context and calls
+ * no allocating routine: the split-KV scratch, the arrival counters and the
+ * status word sit in one fixed device array inside the library (about 4 MiB,
+ * held by every GPU that loads the library until the process exits).
+ *
+ * Same arguments and results as rt_attn_decode, enqueued on `cuda_stream` (a
+ * cudaStream_t; NULL is the legacy default stream) of the CURRENT device.
+ * Limits: batch*splits*qHeads*(2+headDim) <= 1,048,576 floats and
+ * batch*headBlocks <= 4096 when more than one split is used (the library picks
+ * the split count when args->splits is 0; pass splits = 1 to need no scratch at
+ * all); larger requests are refused with RT_INVALID_ARGUMENT and a message
+ * that names the two figures.  The first call on each device looks up the
+ * array's device address; make that first call outside any stream capture.
+ * All calls on a device share the one array, which keeps the previous call's
+ * contents (the counters are cleared on the stream before each launch): two
+ * calls whose kernels may overlap on the GPU — different streams, or the same
+ * call from two threads — race on it, so serialise them.  Errors are reported
+ * through the return code and rt_last_error(NULL); a device-side wait that
+ * runs out is recorded in the array's status word only. */
+RT_API int rt_attn_decode_noalloc(const rt_decode_args* args, void* cuda_stream);
+
 /* Merges `parts` sets of partials (m, l, acc) — the algebra of attnDecodeMerge
  * (packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422) lifted
  * across devices.  partials: f32 [parts, units, 2+headDim]; out:

@@ -235,6 +235,8 @@ int run_decode(rt_ctx* ctx, rt::DecodeParams& p, int dtype) {
 
 }  // namespace
 
+void rt::set_thread_error(const char* msg) { tlsError = msg; }
+
 extern "C" {
 
 int rt_ctx_create(int device, rt_ctx** out) {

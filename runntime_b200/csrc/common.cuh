@@ -105,6 +105,9 @@ cudaError_t launch_merge_partials(const float* partials, int parts, int64_t unit
 cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes, int64_t bytes,
                               cudaStream_t s);
 
+// Records `msg` as the calling thread's last error (what rt_last_error(NULL) returns).
+void set_thread_error(const char* msg);
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);
 template <>

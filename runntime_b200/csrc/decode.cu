@@ -16,6 +16,8 @@
 // Replaces packages/runntime/src/core/kernels/attention/attnDecode.ts:81-187
 // (decode), :263-424 (decodeSplit + merge) and the writeRows dispatches that
 // precede them (packages/runntime/src/core/kernels/shape/rows.ts:143-162).
+#include <mutex>
+
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -522,3 +524,141 @@ cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s) {
 }
 
 }  // namespace rt
+
+// ---- decode without any allocation ---------------------------------------------
+//
+// Some hosts of this library must not allocate device memory when they call it:
+// a real-time audio or serving loop that has pinned its memory budget up front,
+// a plugin that runs inside another framework's memory pool, or code that runs
+// while the device allocator is locked.  rt_attn_decode needs a context, and a
+// context allocates (its stream, its status word, and the split scratch that
+// grows on demand).  This entry point runs the same decode kernel with no
+// context: the split scratch, the arrival counters and the status word live in
+// the fixed-size device array below, which every GPU that loads the library
+// holds until the process exits.
+namespace rt {
+namespace {
+
+constexpr size_t kStaticScratchFloats = 1u << 20;   // 4 MiB of (m, l, acc) partials
+constexpr size_t kStaticCounters = 4096;            // one per (sequence, head block)
+
+struct StaticDecodeArea {
+  float partials[kStaticScratchFloats];
+  unsigned counters[kStaticCounters];
+  int status;
+};
+
+static __device__ __align__(256) StaticDecodeArea gStaticDecodeArea;
+
+constexpr int kMaxDevices = 64;
+std::mutex gStaticMutex;
+StaticDecodeArea* gStaticAddr[kMaxDevices];  // device address of the area, per device
+int gStaticSmCount[kMaxDevices];
+
+// Recorded where rt_last_error(NULL) finds it: this entry point has no context.
+int static_fail(int code, const std::string& msg) {
+  set_thread_error(msg.c_str());
+  return code;
+}
+
+}  // namespace
+}  // namespace rt
+
+extern "C" {
+
+int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
+  using namespace rt;
+  if (!a) return static_fail(RT_INVALID_ARGUMENT, "rt_attn_decode_noalloc: args is NULL");
+  if (!a->q || !a->kCache || !a->vCache || (!a->out && !a->partialsOut))
+    return static_fail(RT_INVALID_ARGUMENT,
+                       "rt_attn_decode_noalloc: q, kCache, vCache and out (or partialsOut) must be "
+                       "device pointers");
+  if (a->dtype != RT_F32 && a->dtype != RT_F16)
+    return static_fail(RT_INVALID_ARGUMENT, "rt_attn_decode_noalloc: dtype is neither f32 nor f16");
+  if (a->batch < 1 || a->batch > 65535 || a->cacheRows < 1 || a->qHeads < 1 || a->headDim < 1 ||
+      a->headDim > 128 || a->kvHeads < 1 || a->qHeads % a->kvHeads != 0 || a->kvLen < 0 ||
+      a->kvLen > a->cacheRows || (!a->kvLens && a->kvLen < 1) || a->windowLeft < 0 ||
+      a->splits < 0 || a->splits > 64 || (a->kNew == nullptr) != (a->vNew == nullptr) ||
+      a->cacheSeqStride < 0 ||
+      (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim))
+    return static_fail(RT_INVALID_ARGUMENT,
+                       "rt_attn_decode_noalloc: a size or option is out of range (same rules as "
+                       "rt_attn_decode)");
+
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return static_fail(RT_EXECUTION_FAILED, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  StaticDecodeArea* area;
+  int smCount;
+  {
+    // Set-up, once per device, with that device current: in host code the
+    // array's name is only a handle, the kernel needs its device address.
+    std::lock_guard<std::mutex> lock(gStaticMutex);
+    if (!gStaticAddr[device]) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, gStaticDecodeArea);
+      if (e != cudaSuccess || !ptr)
+        return static_fail(RT_EXECUTION_FAILED,
+                           std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+      int sms = 0;
+      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+      if (e != cudaSuccess || sms < 1)
+        return static_fail(RT_EXECUTION_FAILED,
+                           std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+      gStaticSmCount[device] = sms;
+      gStaticAddr[device] = static_cast<StaticDecodeArea*>(ptr);
+    }
+    area = gStaticAddr[device];
+    smCount = gStaticSmCount[device];
+  }
+
+  DecodeParams p{};
+  p.q = a->q;
+  p.out = a->out;
+  p.kCache = a->kCache;
+  p.vCache = a->vCache;
+  p.kNew = a->kNew;
+  p.vNew = a->vNew;
+  p.kvLens = a->kvLens;
+  p.sinks = a->sinks;
+  p.partialsOut = a->partialsOut;
+  p.cacheSeqStride = a->cacheSeqStride;
+  p.batch = a->batch;
+  p.kvLen = a->kvLens ? (a->kvLen > 0 ? a->kvLen : a->cacheRows) : a->kvLen;
+  p.qHeads = a->qHeads;
+  p.kvHeads = a->kvHeads;
+  p.hd = a->headDim;
+  p.wl = a->windowLeft;
+  p.splits = a->splits;
+  std::string err;
+  if (!plan_decode(p, a->dtype, smCount, &err)) return static_fail(RT_INVALID_ARGUMENT, err);
+  const size_t zBlocks = (size_t)(p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
+  const size_t needFloats = p.splits > 1 ? (size_t)p.batch * p.splits * p.qHeads * (2 + p.hd) : 0;
+  const size_t needCounters = p.splits > 1 ? (size_t)p.batch * zBlocks : 0;
+  if (needFloats > kStaticScratchFloats || needCounters > kStaticCounters)
+    return static_fail(
+        RT_INVALID_ARGUMENT,
+        "rt_attn_decode_noalloc: batch*splits*qHeads*(2+headDim) = " + std::to_string(needFloats) +
+            " floats (limit " + std::to_string(kStaticScratchFloats) + ") or batch*headBlocks = " +
+            std::to_string(needCounters) + " counters (limit " + std::to_string(kStaticCounters) +
+            ") exceeds the fixed scratch; pass fewer splits or a smaller batch");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // The area keeps the last call's contents.  Partials are fully rewritten
+  // before they are read; the arrival counters must start at zero.
+  if (needCounters) {
+    e = cudaMemsetAsync(area->counters, 0, needCounters * sizeof(unsigned), stream);
+    if (e != cudaSuccess)
+      return static_fail(RT_EXECUTION_FAILED,
+                         std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+  }
+  p.scratch = area->partials;
+  p.counters = area->counters;
+  p.status = &area->status;
+  e = launch_decode(p, a->dtype, stream);
+  if (e != cudaSuccess)
+    return static_fail(RT_EXECUTION_FAILED, std::string("decode launch: ") + cudaGetErrorString(e));
+  return RT_OK;
+}
+
+}  // extern "C"
