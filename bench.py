@@ -473,7 +473,10 @@ def run_gpu(args):
     traffic = load_traffic()
 
     def measure(key, steps, warmup, with_e2e):
-        cfg = CONFIGS[key]
+        cfg = dict(CONFIGS[key])
+        if args.batch and key == args.workload:
+            cfg["batch"] = args.batch
+            cfg["name"] += f"_batch{args.batch}"
         wl = (Prefill if cfg["kind"] == "prefill" else Decode)(cfg, rank, world, ex)
         layers = cfg.get("layers", 1)
         small = key in ("c1", "c2")
@@ -485,6 +488,21 @@ def run_gpu(args):
             sampler.start()
         ms = timed(torch, dist, world, lambda i: wl.step(i % layers), steps, warmup, flush)
         clocks = sampler.stop() if sampler else None
+        if world == 1 and clocks is not None and (clocks.get("samples") or 0) < 3:
+            # The timed region was shorter than the sampler's period: repeat the same
+            # steps untimed for about 1.5 s with the sampler on and report that.
+            sampler = ClockSampler(local)
+            sampler.start()
+            t_end = time.perf_counter() + 1.5
+            i = 0
+            while time.perf_counter() < t_end:
+                wl.step(i % layers)
+                i += 1
+                if i % 8 == 0:
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            clocks = sampler.stop()
+            clocks["sampled"] = "1.5 s untimed repeat of the timed loop (timed region < sampler period)"
         ex.sync()
         launches = (ex.launchCount() - n0) * steps // (steps + warmup)
         if cfg["kind"] == "prefill":
@@ -509,7 +527,7 @@ def run_gpu(args):
             "clocks": clocks, "gpu_launches": launches,
             "l2": "256 MB flush between timed steps" if small else "inputs larger than L2",
         }
-        if with_e2e:
+        if with_e2e and not args.no_e2e:
             wl.make_host()
             h2d, d2h = wl.io_bytes()
             e_steps = max(2, min(steps, 3)) if not small else steps
@@ -528,6 +546,7 @@ def run_gpu(args):
     key = args.workload
     cfg = CONFIGS[key]
     main = measure(key, args.steps, args.warmup, True)
+    cfg = dict(cfg, name=main["workload"])
     extra = None
     if key == "c5" and not args.no_decode:
         extra = measure("c4", max(args.steps, 5), max(args.warmup, 3), True)
@@ -544,16 +563,16 @@ def run_gpu(args):
                                        "KV rows sharded over ranks, one all-gather of partials"
                                        if cfg.get("lens") is None else "sequences sharded over ranks")},
             "roofline": main["roofline"], "clocks": main["clocks"],
-            "e2e": main["e2e"], "gpu_launches": main["gpu_launches"],
+            "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
         }
         if world == 1 and not args.no_cpu:
             v, cores, desc, _ = cpu_sample(key)
             line["cpu_baseline"] = {"value": v, "unit": main["unit"], "cores": cores,
                                     "kind": "port", "sample": desc}
         if extra:
-            line["decode"] = {k: extra[k] for k in ("metric", "value", "unit", "ms_per_step",
-                                                    "workload", "roofline", "e2e", "gpu_launches",
-                                                    "clocks")}
+            line["decode"] = {k: extra.get(k) for k in ("metric", "value", "unit", "ms_per_step",
+                                                        "workload", "roofline", "e2e",
+                                                        "gpu_launches", "clocks")}
             if world == 1 and not args.no_cpu:
                 v, cores, desc, _ = cpu_sample("c4", budget_s=6.0)
                 line["decode"]["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores,
@@ -573,6 +592,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode rider of c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the workload's batch (small cases for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
