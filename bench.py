@@ -482,7 +482,7 @@ def run_gpu(args):
         small = key in ("c1", "c2")
         flushbuf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if small else None
         flush = (lambda: flushbuf.fill_(1)) if small else None
-        sampler = ClockSampler(local) if rank == 0 else None
+        sampler = ClockSampler(local) if (rank == 0 and not args.no_clocks) else None
         n0 = ex.launchCount()
         if sampler:
             sampler.start()
@@ -593,6 +593,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the decode rider of c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
+    ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi clocks")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the workload's batch (small cases for profiler captures)")
     args = ap.parse_args()

@@ -22,22 +22,18 @@
 //
 // Every wait is bounded (sm100.cuh); a wait that runs out sets the status word
 // and the CTA winds down through the common exit that frees its tensor memory.
-#include <cudaTypedefs.h>
-
-#include <mutex>
-
 #include "common.cuh"
 #include "sm100.cuh"
+#include "tc_common.cuh"
 
 namespace rt {
 namespace {
 
 using namespace sm100;
+using namespace tc;
 
-constexpr int BM = 128;             // query rows per CTA
 constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = 192;
-constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 template <int HD>
 struct Cfg {
@@ -45,9 +41,9 @@ struct Cfg {
   static constexpr int CHUNKS = HD / 64;                   // 64-column (128-byte) chunks of a row
   static constexpr int Q_BYTES = BM * HD * 2;
   static constexpr int KV_BYTES = BK * HD * 2;             // one K (or V) tile
-  static constexpr int STAGES = (220 * 1024 - Q_BYTES) / (2 * KV_BYTES) > 4
+  static constexpr int STAGES = (226 * 1024 - Q_BYTES) / (2 * KV_BYTES) > 4
                                     ? 4
-                                    : (220 * 1024 - Q_BYTES) / (2 * KV_BYTES);
+                                    : (226 * 1024 - Q_BYTES) / (2 * KV_BYTES);
   static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + 1024;  // + alignment slack
   static constexpr int S_COLS = BK;                        // f32 score columns per buffer
   static constexpr int O_COL = 2 * S_COLS;                 // O accumulator after the two S buffers
@@ -61,53 +57,6 @@ struct Barriers {
   uint64_t fullK[4], fullV[4], empty[4];
   uint64_t sFull[2], pReady[2], pvDone[2];
 };
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};" ::"r"(r[0]),
-      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
-      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
-      "r"(r[30]), "r"(r[31]), "r"(taddr)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version bit set.
-// Offsets are in bytes; the hardware fields drop the 4 low bits.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3fff);
-  d |= (uint64_t)((lboBytes >> 4) & 0x3fff) << 16;
-  d |= (uint64_t)((sboBytes >> 4) & 0x3fff) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor, kind::f16: f16 A and B, f32 D, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(int n, bool bMnMajor) {
-  return (1u << 4)                       // D format f32
-         | (0u << 7) | (0u << 10)        // A, B format f16
-         | (0u << 15)                    // A K-major
-         | ((bMnMajor ? 1u : 0u) << 16)  // B major
-         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -283,10 +232,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           sv[c] = __float_as_uint((jj >= lo && jj <= end) ? s : -INFINITY);
         }
       }
-      float mx = -INFINITY;
+      // Row max with four independent chains of 3-input max.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < BK; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
-      mx *= kLog2e;
+      for (int c = 0; c < BK; c += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          mx4[u] = max3(mx4[u], __uint_as_float(sv[c + 2 * u]), __uint_as_float(sv[c + 2 * u + 1]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
       // Lazy rescale: only when some row's max grew by more than 2^8 (whole warp
       // together, because TMEM loads/stores are warp-collective).
       const bool grow = mx > mref + kRescaleThreshold;
@@ -311,18 +265,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           }
         }
       }
-      // p = 2^(s*log2e - mref), packed to f16 pairs over the S columns just read
-      float sum = 0.f;
+      // p = 2^(s*log2e - mref): one packed FFMA per two scores, one MUFU each, four
+      // independent packed sums; packed to f16 pairs over the S columns just read.
+      const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mref, -mref);
+      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
+                        make_float2(0.f, 0.f)};
       uint32_t pk[BK / 2];
 #pragma unroll
       for (int c = 0; c < BK; c += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), kLog2e, -mref));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), kLog2e, -mref));
-        sum += p0 + p1;
-        const __half2 hp = __floats2half2_rn(p0, p1);
+        const float2 t = fma2(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])),
+                              scale2, shift2);
+        const float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+        sum2[(c >> 1) & 3] = add2(sum2[(c >> 1) & 3], pe);
+        const __half2 hp = __floats2half2_rn(pe.x, pe.y);
         pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
       }
-      l += sum;
+      const float2 s01 = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+      l += s01.x + s01.y;
 #pragma unroll
       for (int c = 0; c < BK / 2; c += 32)
         tmem_st32(tmem + laneBase + b * C::S_COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&pk[c]));
@@ -379,42 +338,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 
 // ---- host side ------------------------------------------------------------------
 
-PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
-            cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
-  });
-  return fn;
-}
-
-// [rows, cols] f16 row-major with `strideElems` between rows; box = 64 columns x boxRows.
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t strideElems,
-              int boxRows, std::string* err) {
-  auto fn = encode_fn();
-  if (!fn) {
-    *err = "cuTensorMapEncodeTiled is not available from the driver";
-    return false;
-  }
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)strideElems * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)boxRows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    *err = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r);
-    return false;
-  }
-  return true;
-}
-
 template <int HD>
 cudaError_t launch(const AttnParams& p, int* status, cudaStream_t s, std::string* err) {
   using C = Cfg<HD>;
@@ -448,6 +371,7 @@ bool prefill_tc_supported(const AttnParams& p, int dtype) {
 cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaStream_t s,
                               std::string* err) {
   (void)dtype;
+  if (p.tcMode == 3 && prefill_tc2_supported(p)) return launch_prefill_tc2(p, status, s, err);
   switch (p.hd) {
     case 64: return launch<64>(p, status, s, err);
     case 128: return launch<128>(p, status, s, err);

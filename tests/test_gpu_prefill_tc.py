@@ -59,6 +59,19 @@ def test_tensor_core_prefill_against_oracle(ex, name, c):
     check_sdpa(ex, c, "f16", route="prefill_tc")
 
 
+@pytest.mark.parametrize("name,c", [t for t in TC_CASES if t[1].headDim <= 128],
+                         ids=[n for n, c in TC_CASES if c.headDim <= 128])
+def test_two_query_tile_kernel_against_oracle(ex, name, c):
+    from runntime_b200._lib import OPT_PREFILL_TC
+    ex.setOption(OPT_PREFILL_TC, 3)
+    try:
+        check_sdpa(ex, c, "f16", route="prefill_tc")
+        for _, o in cases.option_cases(300, 64)[:11]:
+            check_sdpa(ex, o, "f16", route="prefill_tc")
+    finally:
+        ex.setOption(OPT_PREFILL_TC, 1)
+
+
 @pytest.mark.parametrize("hd", [64, 128, 256])
 def test_every_option_takes_the_tensor_core_route(ex, hd):
     for name, c in cases.option_cases(300, hd):
