@@ -469,6 +469,9 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = rt.CudaExecutor(local)
     ex.setStream(torch.cuda.current_stream().cuda_stream)
+    if args.tc_mode is not None:
+        from runntime_b200._lib import OPT_PREFILL_TC
+        ex.setOption(OPT_PREFILL_TC, args.tc_mode)
     peaks = load_peaks()
     traffic = load_traffic()
 
@@ -594,6 +597,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi clocks")
+    ap.add_argument("--tc-mode", type=int, default=None,
+                    help="RT_OPT_PREFILL_TC value (tuning: 0 FP32 pipes, 1 default, 3 two-tile)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the workload's batch (small cases for profiler captures)")
     args = ap.parse_args()

@@ -35,34 +35,42 @@ using namespace tc;
 constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = 192;
 
-template <int HD>
+template <int HD, bool PSMEM>
 struct Cfg {
   static constexpr int BK = HD <= 128 ? 128 : 64;          // keys per tile
   static constexpr int CHUNKS = HD / 64;                   // 64-column (128-byte) chunks of a row
   static constexpr int Q_BYTES = BM * HD * 2;
   static constexpr int KV_BYTES = BK * HD * 2;             // one K (or V) tile
-  static constexpr int STAGES = (226 * 1024 - Q_BYTES) / (2 * KV_BYTES) > 4
-                                    ? 4
-                                    : (226 * 1024 - Q_BYTES) / (2 * KV_BYTES);
-  static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + 1024;  // + alignment slack
+  // Where P lives.  In tensor memory (over the S columns) P V is a TS MMA; in
+  // shared memory (two buffers of 128 x BK f16) it is an SS MMA.  Measured rates
+  // per K = 16 step at M = 128: SS 64 cycles at N = 128; TS 113 cycles at
+  // N = 128 and 137 at N = 256.
+  static constexpr bool P_SMEM = PSMEM;
+  static constexpr int P_BYTES = P_SMEM ? BM * BK * 2 : 0;  // one P buffer
+  // K and V tiles sit in separate rings: a K slot is free as soon as S(j) has been
+  // computed, a V slot only after P V(j), so K can be fetched further ahead.
+  static constexpr int TILE_SLOTS = (226 * 1024 - Q_BYTES - 2 * P_BYTES) / KV_BYTES;
+  static constexpr int K_SLOTS = (TILE_SLOTS + 1) / 2 > 4 ? 4 : (TILE_SLOTS + 1) / 2;
+  static constexpr int V_SLOTS = TILE_SLOTS / 2 > 4 ? 4 : TILE_SLOTS / 2;
+  static constexpr int SMEM = Q_BYTES + 2 * P_BYTES + (K_SLOTS + V_SLOTS) * KV_BYTES + 1024;
   static constexpr int S_COLS = BK;                        // f32 score columns per buffer
   static constexpr int O_COL = 2 * S_COLS;                 // O accumulator after the two S buffers
   static constexpr int TMEM_COLS = 512;
   static_assert(O_COL + HD <= TMEM_COLS, "tensor memory budget");
-  static_assert(STAGES >= 2, "need a double-buffered ring");
+  static_assert(K_SLOTS >= 2 && V_SLOTS >= 2, "need double-buffered rings");
 };
 
 struct Barriers {
   uint64_t fullQ;
-  uint64_t fullK[4], fullV[4], empty[4];
+  uint64_t fullK[4], fullV[4], emptyK[4], emptyV[4];
   uint64_t sFull[2], pReady[2], pvDone[2];
 };
 
-template <int HD>
+template <int HD, bool PSMEM>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const AttnParams p, int* status) {
-  using C = Cfg<HD>;
+  using C = Cfg<HD, PSMEM>;
   constexpr int BK = C::BK;
   extern __shared__ unsigned char smemRaw[];
   __shared__ Barriers bars;
@@ -71,6 +79,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   __shared__ int sLoMin[4], sEndMax[4];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  TC_TRACE_DECL
   // Long rows first: under a causal mask the last row tile has the most keys.
   const int qTile = (int)gridDim.x - 1 - (int)blockIdx.x;
   const int h = blockIdx.y;
@@ -80,15 +89,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   // 1024-byte aligned carve-up: swizzle atoms must start on 1024-byte lines.
   const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;
   const uint32_t sQ = smemBase;
-  const uint32_t sKV = sQ + C::Q_BYTES;  // stage s: K at sKV + s*2*KV_BYTES, V right after
+  const uint32_t sP = sQ + C::Q_BYTES;            // two P buffers (head sizes up to 128)
+  const uint32_t sK = sP + 2 * C::P_BYTES;        // K ring
+  const uint32_t sV = sK + C::K_SLOTS * C::KV_BYTES;  // V ring
 
   if (tid == 0) {
     sAbort = 0;
     mbar_init(smem_u32(&bars.fullQ), 1);
-    for (int s = 0; s < C::STAGES; s++) {
+    for (int s = 0; s < 4; s++) {
       mbar_init(smem_u32(&bars.fullK[s]), 1);
       mbar_init(smem_u32(&bars.fullV[s]), 1);
-      mbar_init(smem_u32(&bars.empty[s]), 1);
+      mbar_init(smem_u32(&bars.emptyK[s]), 1);
+      mbar_init(smem_u32(&bars.emptyV[s]), 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(smem_u32(&bars.sFull[b]), 1);
@@ -136,26 +148,34 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 
   if (warp == 4) {
     // ------------------------------ TMA producer ------------------------------
+    // lane 0: Q, then the K ring; lane 1: the V ring (each runs ahead on its own).
     if (lane == 0 && nTiles > 0) {
       prefetch_tensormap(&mapQ);
       prefetch_tensormap(&mapK);
-      prefetch_tensormap(&mapV);
       mbar_expect_tx(smem_u32(&bars.fullQ), C::Q_BYTES);
       for (int c = 0; c < C::CHUNKS; c++)
         tma_load_2d(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
       for (int j = 0; j < nTiles; j++) {
-        const int s = j % C::STAGES;
-        if (j >= C::STAGES &&
-            !mbar_wait(smem_u32(&bars.empty[s]), ((j / C::STAGES) - 1) & 1, &sAbort))
+        const int s = j % C::K_SLOTS;
+        if (j >= C::K_SLOTS &&
+            !mbar_wait(smem_u32(&bars.emptyK[s]), ((j / C::K_SLOTS) - 1) & 1, &sAbort))
           break;
-        const int key0 = (kt0 + j) * BK;
-        const uint32_t dK = sKV + s * 2 * C::KV_BYTES, dV = dK + C::KV_BYTES;
         mbar_expect_tx(smem_u32(&bars.fullK[s]), C::KV_BYTES);
         for (int c = 0; c < C::CHUNKS; c++)
-          tma_load_2d(dK + c * (BK * 128), &mapK, kvh * HD + c * 64, key0, smem_u32(&bars.fullK[s]));
+          tma_load_2d(sK + s * C::KV_BYTES + c * (BK * 128), &mapK, kvh * HD + c * 64,
+                      (kt0 + j) * BK, smem_u32(&bars.fullK[s]));
+      }
+    } else if (lane == 1 && nTiles > 0) {
+      prefetch_tensormap(&mapV);
+      for (int j = 0; j < nTiles; j++) {
+        const int s = j % C::V_SLOTS;
+        if (j >= C::V_SLOTS &&
+            !mbar_wait(smem_u32(&bars.emptyV[s]), ((j / C::V_SLOTS) - 1) & 1, &sAbort))
+          break;
         mbar_expect_tx(smem_u32(&bars.fullV[s]), C::KV_BYTES);
         for (int c = 0; c < C::CHUNKS; c++)
-          tma_load_2d(dV + c * (BK * 128), &mapV, kvh * HD + c * 64, key0, smem_u32(&bars.fullV[s]));
+          tma_load_2d(sV + s * C::KV_BYTES + c * (BK * 128), &mapV, kvh * HD + c * 64,
+                      (kt0 + j) * BK, smem_u32(&bars.fullV[s]));
       }
     }
   } else if (warp == 5) {
@@ -166,12 +186,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       bool ok = mbar_wait(smem_u32(&bars.fullQ), 0, &sAbort);
       for (int j = 0; ok && j <= nTiles; j++) {
         if (j < nTiles) {
-          const int s = j % C::STAGES, b = j & 1;
-          ok = mbar_wait(smem_u32(&bars.fullK[s]), (j / C::STAGES) & 1, &sAbort);
-          if (ok && j >= 2) ok = mbar_wait(smem_u32(&bars.pvDone[b]), ((j - 2) >> 1) & 1, &sAbort);
+          const int s = j % C::K_SLOTS, b = j & 1;
+          ok = mbar_wait(smem_u32(&bars.fullK[s]), (j / C::K_SLOTS) & 1, &sAbort);
+          // With P in tensor memory over the S columns, S(j) must not land before
+          // P V(j-2) has read them.  With P in shared memory the S buffer is free as
+          // soon as the softmax warps have loaded it, which P-ready(j-2) implies.
+          if (!C::P_SMEM && ok && j >= 2)
+            ok = mbar_wait(smem_u32(&bars.pvDone[b]), ((j - 2) >> 1) & 1, &sAbort);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t dK = sKV + s * 2 * C::KV_BYTES;
+          const uint32_t dK = sK + s * C::KV_BYTES;
 #pragma unroll
           for (int kk = 0; kk < HD / 16; kk++) {
             // K-major operands: 16 elements (32 bytes) further along the swizzled row per step
@@ -180,24 +204,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mma_f16_ss(tmem + b * C::S_COLS, aDesc, bDesc, idescS, kk > 0);
           }
           tc_commit(smem_u32(&bars.sFull[b]));
+          tc_commit(smem_u32(&bars.emptyK[s]));
         }
         if (j >= 1) {
-          const int t = j - 1, s = t % C::STAGES, b = t & 1;
+          const int t = j - 1, s = t % C::V_SLOTS, b = t & 1;
           ok = mbar_wait(smem_u32(&bars.pReady[b]), (t >> 1) & 1, &sAbort);
-          if (ok) ok = mbar_wait(smem_u32(&bars.fullV[s]), (t / C::STAGES) & 1, &sAbort);
+          if (ok) ok = mbar_wait(smem_u32(&bars.fullV[s]), (t / C::V_SLOTS) & 1, &sAbort);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t dV = sKV + s * 2 * C::KV_BYTES + C::KV_BYTES;
+          const uint32_t dV = sV + s * C::KV_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; kk++) {
             // V is [keys][hd] (MN-major B): 16 keys = 2048 bytes further per step;
             // LBO = next 64 columns of hd, SBO = next 8 keys.
             const uint64_t bDesc = smem_desc(dV + kk * 2048, BK * 128, 1024);
             // P: f16 pairs, 8 columns of TMEM per 16 keys
-            mma_f16_ts(tmem + C::O_COL, tmem + b * C::S_COLS + kk * 8, bDesc, idescO,
-                       (t > 0 || kk > 0) ? 1u : 0u);
+            if (C::P_SMEM) {
+              // P: [128 rows][BK keys] f16, K-major, 64-key chunks of 128-byte rows
+              const uint64_t aDesc =
+                  smem_desc(sP + b * C::P_BYTES + (kk >> 2) * (BM * 128) + (kk & 3) * 32, 16, 1024);
+              mma_f16_ss(tmem + C::O_COL, aDesc, bDesc, idescO, (t > 0 || kk > 0) ? 1u : 0u);
+            } else {
+              mma_f16_ts(tmem + C::O_COL, tmem + b * C::S_COLS + kk * 8, bDesc, idescO,
+                         (t > 0 || kk > 0) ? 1u : 0u);
+            }
           }
-          tc_commit(smem_u32(&bars.empty[s]));
+          tc_commit(smem_u32(&bars.emptyV[s]));
           tc_commit(smem_u32(&bars.pvDone[b]));
         }
       }
@@ -214,14 +246,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     for (int j = 0; j < nTiles && ok; j++) {
       const int b = j & 1;
       const int key0 = (kt0 + j) * BK;
+      TC_TRACE(0, j);
       ok = mbar_wait(smem_u32(&bars.sFull[b]), (j >> 1) & 1, &sAbort);
       if (!ok) break;
       tc_fence_after_sync();
+      TC_TRACE(1, j);
       uint32_t sv[BK];
 #pragma unroll
       for (int c = 0; c < BK; c += 32)
         tmem_ld32(tmem + laneBase + b * C::S_COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
       tmem_wait_ld();
+      TC_TRACE(2, j);
       const bool fullTile = lo <= key0 && end >= key0 + BK - 1;
       if (!fullTile || p.hasKeyBias) {
 #pragma unroll
@@ -267,6 +302,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       }
       // p = 2^(s*log2e - mref): one packed FFMA per two scores, one MUFU each, four
       // independent packed sums; packed to f16 pairs over the S columns just read.
+      TC_TRACE(3, j);
       const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mref, -mref);
       float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
                         make_float2(0.f, 0.f)};
@@ -275,19 +311,39 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       for (int c = 0; c < BK; c += 2) {
         const float2 t = fma2(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])),
                               scale2, shift2);
-        const float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+        const float2 pe = exp2_pair(t, c >> 1);
         sum2[(c >> 1) & 3] = add2(sum2[(c >> 1) & 3], pe);
         const __half2 hp = __floats2half2_rn(pe.x, pe.y);
         pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
       }
       const float2 s01 = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
       l += s01.x + s01.y;
+      if (C::P_SMEM) {
+        // The buffer was last read by P V(j-2).
+        if (j >= 2) {
+          ok = mbar_wait(smem_u32(&bars.pvDone[b]), ((j - 2) >> 1) & 1, &sAbort);
+          if (!ok) break;
+        }
+        // Row `tid` of the A operand: 16-byte units (8 keys) swizzled by row & 7.
+        const uint32_t rowBase = sP + b * C::P_BYTES + tid * 128;
 #pragma unroll
-      for (int c = 0; c < BK / 2; c += 32)
-        tmem_st32(tmem + laneBase + b * C::S_COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&pk[c]));
+        for (int u = 0; u < BK / 8; u++) {
+          const uint32_t addr = rowBase + (u >> 3) * (BM * 128) + (((u & 7) ^ (tid & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * u]),
+                       "r"(pk[4 * u + 1]), "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
+                       : "memory");
+        }
+        fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
+      } else {
+#pragma unroll
+        for (int c = 0; c < BK / 2; c += 32)
+          tmem_st32(tmem + laneBase + b * C::S_COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&pk[c]));
+      }
+      TC_TRACE(4, j);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bars.pReady[b]));
+      TC_TRACE(5, j);
     }
 
     // Epilogue: O / l -> f16 -> global.  Rows that saw no key are zeros.
@@ -338,15 +394,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 
 // ---- host side ------------------------------------------------------------------
 
-template <int HD>
+template <int HD, bool PSMEM>
 cudaError_t launch(const AttnParams& p, int* status, cudaStream_t s, std::string* err) {
-  using C = Cfg<HD>;
+  using C = Cfg<HD, PSMEM>;
   CUtensorMap mq, mk, mv;
   if (!make_map(&mq, p.q, p.qLen, (int64_t)p.qHeads * HD, p.qStride, BM, err) ||
       !make_map(&mk, p.k, p.kvLen, (int64_t)p.kvHeads * HD, p.kvStride, C::BK, err) ||
       !make_map(&mv, p.v, p.kvLen, (int64_t)p.kvHeads * HD, p.kvStride, C::BK, err))
     return cudaErrorInvalidValue;
-  auto kern = prefill_tc_kernel<HD>;
+  auto kern = prefill_tc_kernel<HD, PSMEM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)((p.qLen + BM - 1) / BM), (unsigned)p.qHeads);
@@ -373,9 +429,11 @@ cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaS
   (void)dtype;
   if (p.tcMode == 3 && prefill_tc2_supported(p)) return launch_prefill_tc2(p, status, s, err);
   switch (p.hd) {
-    case 64: return launch<64>(p, status, s, err);
-    case 128: return launch<128>(p, status, s, err);
-    case 256: return launch<256>(p, status, s, err);
+    case 64: return p.tcMode == 4 ? launch<64, true>(p, status, s, err)
+                                  : launch<64, false>(p, status, s, err);
+    case 128: return p.tcMode == 4 ? launch<128, true>(p, status, s, err)
+                                   : launch<128, false>(p, status, s, err);
+    case 256: return launch<256, false>(p, status, s, err);
   }
   *err = "unsupported head size";
   return cudaErrorInvalidValue;

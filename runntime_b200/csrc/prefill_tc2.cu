@@ -312,7 +312,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           const int cc = half * 64 + c;
           const float2 t = fma2(make_float2(__uint_as_float(sv[cc]), __uint_as_float(sv[cc + 1])),
                                 scale2, shift2);
-          const float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          const float2 pe = exp2_pair(t, c >> 1);
           sum2[(c >> 1) & 3] = add2(sum2[(c >> 1) & 3], pe);
           const __half2 hp = __floats2half2_rn(pe.x, pe.y);
           pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);

@@ -88,6 +88,35 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return *reinterpret_cast<float2*>(&d);
 }
 
+// 2^x for a pair of values on the FMA pipe, no MUFU: split x into its nearest
+// integer n (magic-number rounding) and f in [-0.5, 0.5], evaluate a degree-3
+// polynomial for 2^f (max relative error 7.5e-5, below f16 resolution) and add n
+// to the exponent field.  Inputs below -126 (masked scores are -inf) give 2^-126.
+// The MUFU unit delivers 16 ex2 per clock per SM, which is exactly the tensor
+// core's appetite for a 128-wide head; moving part of the exponentials here
+// takes the special-function unit off the critical path.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 xr = add2(x, make_float2(kMagic, kMagic));
+  const float2 n = add2(xr, make_float2(-kMagic, -kMagic));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+  float2 r = fma2(make_float2(0.055171649903059006f, 0.055171649903059006f), f,
+                  make_float2(0.2426111251115799f, 0.2426111251115799f));
+  r = fma2(r, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  r = fma2(r, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(xr.x) << 23));
+  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(xr.y) << 23));
+  return r;
+}
+// Of every kPolyDen consecutive score pairs, kPolyNum take the polynomial path.
+constexpr int kPolyNum = 3, kPolyDen = 8;
+__device__ __forceinline__ float2 exp2_pair(float2 t, int pairIndex) {
+  if (pairIndex % kPolyDen < kPolyNum) return exp2_poly2(t);
+  return make_float2(sm100::fast_exp2(t.x), sm100::fast_exp2(t.y));
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version bit set.
 // Offsets are in bytes; the hardware fields drop the 4 low bits.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes) {
