@@ -303,7 +303,7 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
 int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
   RT_ENTER(ctx);
   if (option == RT_OPT_PREFILL_TC) {
-    ctx->useTc = value < 0 ? 0 : value > 4 ? 4 : value;
+    ctx->useTc = value < 0 ? 0 : value > 6 ? 6 : value;
     return RT_OK;
   }
   return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: unknown option %d", option);

@@ -38,7 +38,7 @@ struct AttnParams {
   float biasValue;
   int32_t seqStride;
   int32_t maxSegment;
-  int32_t tcMode;  // 1, 2: one-query-tile kernel; 3: two-query-tile kernel where it applies
+  int32_t tcMode;  // tensor-core kernel variant, see launch_prefill_tc
 };
 
 // Visible key range [lo, end] (inclusive) of query row `row`; empty when lo > end.

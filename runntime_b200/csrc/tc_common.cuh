@@ -111,7 +111,10 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   return r;
 }
 // Of every kPolyDen consecutive score pairs, kPolyNum take the polynomial path.
-constexpr int kPolyNum = 3, kPolyDen = 8;
+#ifndef RT_POLY_NUM
+#define RT_POLY_NUM 2
+#endif
+constexpr int kPolyNum = RT_POLY_NUM, kPolyDen = 8;
 __device__ __forceinline__ float2 exp2_pair(float2 t, int pairIndex) {
   if (pairIndex % kPolyDen < kPolyNum) return exp2_poly2(t);
   return make_float2(sm100::fast_exp2(t.x), sm100::fast_exp2(t.y));

@@ -59,11 +59,11 @@ def test_tensor_core_prefill_against_oracle(ex, name, c):
     check_sdpa(ex, c, "f16", route="prefill_tc")
 
 
-@pytest.mark.parametrize("mode", [3, 4])
+@pytest.mark.parametrize("mode", [3, 4, 5, 6])
 @pytest.mark.parametrize("name,c", [t for t in TC_CASES if t[1].headDim <= 128],
                          ids=[n for n, c in TC_CASES if c.headDim <= 128])
 def test_kernel_variants_against_oracle(ex, name, c, mode):
-    """Option 3: two query tiles per CTA; option 4: P through shared memory."""
+    """Kernel variants behind RT_OPT_PREFILL_TC (see launch_prefill_tc)."""
     from runntime_b200._lib import OPT_PREFILL_TC
     ex.setOption(OPT_PREFILL_TC, mode)
     try:
