@@ -466,6 +466,9 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL's version banner goes to stdout; this program's stdout is one JSON line.
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = rt.CudaExecutor(local)
     ex.setStream(torch.cuda.current_stream().cuda_stream)
@@ -491,6 +494,8 @@ def run_gpu(args):
             sampler.start()
         ms = timed(torch, dist, world, lambda i: wl.step(i % layers), steps, warmup, flush)
         clocks = sampler.stop() if sampler else None
+        ex.sync()
+        launches = (ex.launchCount() - n0) * steps // (steps + warmup)
         if world == 1 and clocks is not None and (clocks.get("samples") or 0) < 3:
             # The timed region was shorter than the sampler's period: repeat the same
             # steps untimed for about 1.5 s with the sampler on and report that.
@@ -507,7 +512,6 @@ def run_gpu(args):
             clocks = sampler.stop()
             clocks["sampled"] = "1.5 s untimed repeat of the timed loop (timed region < sampler period)"
         ex.sync()
-        launches = (ex.launchCount() - n0) * steps // (steps + warmup)
         if cfg["kind"] == "prefill":
             work = sum(wl.flops(i % layers) for i in range(steps))
             value, unit = work / (ms * 1e-3) / 1e12, "TFLOP/s"
