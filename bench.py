@@ -602,7 +602,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi clocks")
     ap.add_argument("--tc-mode", type=int, default=None,
-                    help="RT_OPT_PREFILL_TC value (tuning: 0 FP32 pipes, 1 default, 3 two-tile)")
+                    help="RT_OPT_PREFILL_TC value (0: FP32-pipe kernel, 1: tensor-core kernel)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the workload's batch (small cases for profiler captures)")
     args = ap.parse_args()

@@ -67,9 +67,7 @@ RT_API int rt_ctx_destroy(rt_ctx* ctx);
 RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
 /* Context options.  RT_OPT_PREFILL_TC (default 1): route eligible f16 prefill
  * shapes to the tensor-core kernel; 0 sends every prefill to the FP32-pipe
- * kernel; 2..6 pick other builds of the tensor-core kernel (different thread
- * layouts and placements of the probabilities; all compute the same op — the
- * switch exists for testing and tuning). */
+ * kernel (both compute the same op; the switch exists for testing). */
 #define RT_OPT_PREFILL_TC 1
 RT_API int rt_ctx_set_option(rt_ctx* ctx, int option, int value);
 /* Message of the last failure on this context (or, with ctx == NULL, of the

@@ -303,7 +303,7 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
 int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
   RT_ENTER(ctx);
   if (option == RT_OPT_PREFILL_TC) {
-    ctx->useTc = value < 0 ? 0 : value > 6 ? 6 : value;
+    ctx->useTc = value != 0;
     return RT_OK;
   }
   return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: unknown option %d", option);
@@ -406,8 +406,7 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
     p.splits = 0;
     return run_decode(ctx, p, a->dtype);
   }
-  rt::AttnParams p = to_params(a);
-  p.tcMode = ctx->useTc;
+  const rt::AttnParams p = to_params(a);
   if (ctx->useTc && rt::prefill_tc_supported(p, a->dtype)) {
     std::string err;
     cudaError_t e = rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);

@@ -38,7 +38,6 @@ struct AttnParams {
   float biasValue;
   int32_t seqStride;
   int32_t maxSegment;
-  int32_t tcMode;  // tensor-core kernel variant, see launch_prefill_tc
 };
 
 // Visible key range [lo, end] (inclusive) of query row `row`; empty when lo > end.
@@ -98,8 +97,6 @@ cudaError_t launch_prefill_simt(const AttnParams& p, int dtype, cudaStream_t s);
 bool prefill_tc_supported(const AttnParams& p, int dtype);
 cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaStream_t s,
                               std::string* err);
-bool prefill_tc2_supported(const AttnParams& p);  // two query tiles per CTA
-cudaError_t launch_prefill_tc2(const AttnParams& p, int* status, cudaStream_t s, std::string* err);
 // Fills kvPerCta/keySlots/stages/splits; returns false with a message when the shape cannot run.
 bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);

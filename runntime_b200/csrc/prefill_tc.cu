@@ -25,6 +25,17 @@
 // replaces attnFlash (packages/runntime/src/core/kernels/attention/
 // attnFlash.ts:93-276), which has no tensor-core path.
 //
+// The kernel is a template over where P lives (tensor memory or shared memory)
+// and over one or two softmax threads per row; the launcher uses one thread per
+// row with P in tensor memory, the fastest measured on B200 (head size 128,
+// causal 8192: 880-940 TFLOP/s).  Measured and not faster: P through shared
+// memory for an SS-form P V (the stores and the proxy fence cost more than the
+// faster MMA gains); two threads per row (the special-function unit, 16 ex2 per
+// clock per SM, is the shared limit and the per-tile exchange of row maxima keeps
+// both halves' ex2 phases in lockstep); two query tiles per CTA; evaluating part
+// of the exponentials by polynomial on the FMA pipe (more issue slots than the
+// MUFU cycles it frees; RT_POLY_NUM in tc_common.cuh, default 0).
+//
 // Every wait is bounded (sm100.cuh); a wait that runs out sets the status word
 // and the CTA winds down through the common exit that frees its tensor memory.
 #include "common.cuh"
@@ -68,6 +79,12 @@ struct Cfg {
   static constexpr int SMEM = Q_BYTES + P_BUFS * P_BYTES + (K_SLOTS + V_SLOTS) * KV_BYTES + 1024;
   static constexpr int S_COLS = BK;                        // f32 score columns per buffer
   static constexpr int O_COL = 2 * S_COLS;                 // O accumulator after the two S buffers
+  // P in tensor memory gets columns of its own (two buffers of BK/2 packed f16
+  // pairs) when they fit, so that the next S never waits for a P V to finish
+  // reading; otherwise P overwrites the S columns it came from.
+  static constexpr bool P_OWN_COLS = !PSMEM && (2 * S_COLS + HD + S_COLS <= 512);
+  static constexpr int P_COL = P_OWN_COLS ? O_COL + HD : 0;
+  static constexpr int P_STRIDE = P_OWN_COLS ? S_COLS / 2 : S_COLS;  // between the two P buffers
   static constexpr int OW = HD / SPLIT;                    // O columns per softmax thread
   static constexpr int TMEM_COLS = 512;
   static_assert(O_COL + HD <= TMEM_COLS, "tensor memory budget");
@@ -206,11 +223,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const int s = j % C::K_SLOTS, b = j & 1;
         TC_TRACE(10, j);
         ok = mbar_wait(smem_u32(&bars.fullK[s]), (j / C::K_SLOTS) & 1, &sAbort);
-        // The S buffer is free once its previous contents are dead: with P in tensor
-        // memory over the S columns, after P V(j-2) has read them; with P in shared
-        // memory, as soon as the softmax warps have loaded S(j-2) into registers.
+        // The S buffer is free once its previous contents are dead: with P written
+        // over the S columns, after P V(j-2) has read them; with P elsewhere (shared
+        // memory or its own TMEM columns), as soon as the softmax warps have loaded
+        // S(j-2) into registers.
         if (ok && j >= 2)
-          ok = mbar_wait(smem_u32(C::P_SMEM ? &bars.sFree[b] : &bars.pvDone[b]),
+          ok = mbar_wait(smem_u32((C::P_SMEM || C::P_OWN_COLS) ? &bars.sFree[b] : &bars.pvDone[b]),
                          ((j - 2) >> 1) & 1, &sAbort);
         if (!ok) break;
         TC_TRACE(11, j);
@@ -255,7 +273,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mma_f16_ss(tmem + C::O_COL, aDesc, bDesc, idescO, (t > 0 || kk > 0) ? 1u : 0u);
           } else {
             // P: f16 pairs, 8 columns of TMEM per 16 keys
-            mma_f16_ts(tmem + C::O_COL, tmem + b * C::S_COLS + kk * 8, bDesc, idescO,
+            mma_f16_ts(tmem + C::O_COL, tmem + C::P_COL + b * C::P_STRIDE + kk * 8, bDesc, idescO,
                        (t > 0 || kk > 0) ? 1u : 0u);
           }
         }
@@ -292,7 +310,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           tmem_ld32(tmem + laneBase + b * C::S_COLS + col0 + c,
                     *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
         tmem_wait_ld();
-        if (C::P_SMEM) {  // S(j) is in registers: its buffer may take S(j+2)
+        if (C::P_SMEM || C::P_OWN_COLS) {  // S(j) is in registers: its buffer may take S(j+2)
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bars.sFree[b]));
@@ -395,9 +413,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           }
         } else {
           static_assert(PSMEM || (CW / 2) % 32 == 0, "P part must be whole 32-column stores");
+          // P's own columns were last read by P V(j-2).
+          if (C::P_OWN_COLS && j >= 2)
+            ok = mbar_wait(smem_u32(&bars.pvDone[b]), ((j - 2) >> 1) & 1, &sAbort);
 #pragma unroll
           for (int c = 0; c < CW / 2; c += 32)
-            tmem_st32(tmem + laneBase + b * C::S_COLS + part * (CW / 2) + c,
+            tmem_st32(tmem + laneBase + C::P_COL + b * C::P_STRIDE + part * (CW / 2) + c,
                       *reinterpret_cast<uint32_t(*)[32]>(&pk[c & ~31]));
           tmem_wait_st();
         }
@@ -494,27 +515,13 @@ bool prefill_tc_supported(const AttnParams& p, int dtype) {
   return true;
 }
 
-// tcMode selects the variant (tuning and tests).  1 (default) and 2: one softmax
-// thread per row, P in tensor memory — the fastest measured; 3: two query tiles per
-// CTA; 4: one thread per row, P through shared memory; 5: two threads per row, P in
-// tensor memory; 6: two threads per row, P through shared memory.
 cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaStream_t s,
                               std::string* err) {
   (void)dtype;
-  if (p.tcMode == 3 && prefill_tc2_supported(p)) return launch_prefill_tc2(p, status, s, err);
-  if (p.hd == 256) return launch<256, false, 1>(p, status, s, err);
-  const int mode = p.tcMode;
-  if (p.hd == 64) {
-    if (mode == 4) return launch<64, true, 1>(p, status, s, err);
-    if (mode == 5) return launch<64, false, 2>(p, status, s, err);
-    if (mode == 6) return launch<64, true, 2>(p, status, s, err);
-    return launch<64, false, 1>(p, status, s, err);
-  }
-  if (p.hd == 128) {
-    if (mode == 4) return launch<128, true, 1>(p, status, s, err);
-    if (mode == 5) return launch<128, false, 2>(p, status, s, err);
-    if (mode == 6) return launch<128, true, 2>(p, status, s, err);
-    return launch<128, false, 1>(p, status, s, err);
+  switch (p.hd) {
+    case 64: return launch<64, false, 1>(p, status, s, err);
+    case 128: return launch<128, false, 1>(p, status, s, err);
+    case 256: return launch<256, false, 1>(p, status, s, err);
   }
   *err = "unsupported head size";
   return cudaErrorInvalidValue;

@@ -66,6 +66,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -112,7 +121,7 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 }
 // Of every kPolyDen consecutive score pairs, kPolyNum take the polynomial path.
 #ifndef RT_POLY_NUM
-#define RT_POLY_NUM 2
+#define RT_POLY_NUM 0
 #endif
 constexpr int kPolyNum = RT_POLY_NUM, kPolyDen = 8;
 __device__ __forceinline__ float2 exp2_pair(float2 t, int pairIndex) {

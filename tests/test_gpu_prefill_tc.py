@@ -59,21 +59,6 @@ def test_tensor_core_prefill_against_oracle(ex, name, c):
     check_sdpa(ex, c, "f16", route="prefill_tc")
 
 
-@pytest.mark.parametrize("mode", [3, 4, 5, 6])
-@pytest.mark.parametrize("name,c", [t for t in TC_CASES if t[1].headDim <= 128],
-                         ids=[n for n, c in TC_CASES if c.headDim <= 128])
-def test_kernel_variants_against_oracle(ex, name, c, mode):
-    """Kernel variants behind RT_OPT_PREFILL_TC (see launch_prefill_tc)."""
-    from runntime_b200._lib import OPT_PREFILL_TC
-    ex.setOption(OPT_PREFILL_TC, mode)
-    try:
-        check_sdpa(ex, c, "f16", route="prefill_tc")
-        for _, o in cases.option_cases(300, 64)[:11]:
-            check_sdpa(ex, o, "f16", route="prefill_tc")
-    finally:
-        ex.setOption(OPT_PREFILL_TC, 1)
-
-
 @pytest.mark.parametrize("hd", [64, 128, 256])
 def test_every_option_takes_the_tensor_core_route(ex, hd):
     for name, c in cases.option_cases(300, hd):
