@@ -489,13 +489,31 @@ def run_gpu(args):
         flushbuf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if small else None
         flush = (lambda: flushbuf.fill_(1)) if small else None
         sampler = ClockSampler(local) if (rank == 0 and not args.no_clocks) else None
+        step_fn = lambda i: wl.step(i % layers)
+        graphed = False
+        if cfg["kind"] == "decode" and not args.no_graph:
+            # A decode step is a few short launches (kernel, all-gather, merge): capture
+            # it once in a CUDA graph so that the device is not left waiting for the host.
+            n1 = ex.launchCount()
+            for i in range(3):
+                wl.step(0)
+            per_step = (ex.launchCount() - n1) // 3
+            torch.cuda.synchronize()
+            graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.graph(graph, stream=side):
+                ex.setStream(torch.cuda.current_stream().cuda_stream)
+                wl.step(0)
+            ex.setStream(torch.cuda.current_stream().cuda_stream)
+            step_fn = lambda i: graph.replay()
+            graphed = True
         n0 = ex.launchCount()
         if sampler:
             sampler.start()
-        ms = timed(torch, dist, world, lambda i: wl.step(i % layers), steps, warmup, flush)
+        ms = timed(torch, dist, world, step_fn, steps, warmup, flush)
         clocks = sampler.stop() if sampler else None
         ex.sync()
-        launches = (ex.launchCount() - n0) * steps // (steps + warmup)
+        launches = (per_step * steps) if graphed else \
+            (ex.launchCount() - n0) * steps // (steps + warmup)
         if world == 1 and clocks is not None and (clocks.get("samples") or 0) < 3:
             # The timed region was shorter than the sampler's period: repeat the same
             # steps untimed for about 1.5 s with the sampler on and report that.
@@ -504,7 +522,7 @@ def run_gpu(args):
             t_end = time.perf_counter() + 1.5
             i = 0
             while time.perf_counter() < t_end:
-                wl.step(i % layers)
+                step_fn(i)
                 i += 1
                 if i % 8 == 0:
                     torch.cuda.synchronize()
@@ -533,6 +551,7 @@ def run_gpu(args):
                          "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else "")},
             "clocks": clocks, "gpu_launches": launches,
             "l2": "256 MB flush between timed steps" if small else "inputs larger than L2",
+            "launch": "CUDA graph replay of one step" if graphed else "direct launches",
         }
         if with_e2e and not args.no_e2e:
             wl.make_host()
@@ -564,7 +583,7 @@ def run_gpu(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": main["dtype"], "data": "synthetic",
-            "config": {"workload": cfg["name"], "l2": main["l2"],
+            "config": {"workload": cfg["name"], "l2": main["l2"], "launch": main["launch"],
                        "parallelism": ("sequences sharded over ranks, no collective"
                                        if cfg["kind"] == "prefill" else
                                        "KV rows sharded over ranks, one all-gather of partials"
@@ -579,7 +598,7 @@ def run_gpu(args):
         if extra:
             line["decode"] = {k: extra.get(k) for k in ("metric", "value", "unit", "ms_per_step",
                                                         "workload", "roofline", "e2e",
-                                                        "gpu_launches", "clocks")}
+                                                        "gpu_launches", "clocks", "launch")}
             if world == 1 and not args.no_cpu:
                 v, cores, desc, _ = cpu_sample("c4", budget_s=6.0)
                 line["decode"]["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores,
@@ -601,6 +620,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi clocks")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch decode steps directly instead of replaying a CUDA graph")
     ap.add_argument("--tc-mode", type=int, default=None,
                     help="RT_OPT_PREFILL_TC value (0: FP32-pipe kernel, 1: tensor-core kernel)")
     ap.add_argument("--batch", type=int, default=0,
