@@ -233,7 +233,8 @@ class Decode:
             return
         decode_batched(self.ex, self.q, self.out, self.k, self.v, cacheRows=self.rows,
                        kvLen=max(self.lens_all) if self.lens is not None else self.rows,
-                       kvLens=self.lens, kNew=self.kNew, vNew=self.vNew, **common)
+                       kvLens=self.lens, kNew=self.kNew, vNew=self.vNew,
+                       splits=int(os.environ.get("RT_BENCH_SPLITS", "0")), **common)
         if c["cross"]:
             decode_batched(self.ex, self.q, self.out2, self.ck, self.cv, cacheRows=c["cross"],
                            kvLen=c["cross"], **common)
@@ -483,6 +484,9 @@ def run_gpu(args):
         if args.batch and key == args.workload:
             cfg["batch"] = args.batch
             cfg["name"] += f"_batch{args.batch}"
+        if args.rows and key == args.workload:
+            cfg["cacheRows" if cfg["kind"] == "decode" else "seq"] = args.rows
+            cfg["name"] += f"_rows{args.rows}"
         wl = (Prefill if cfg["kind"] == "prefill" else Decode)(cfg, rank, world, ex)
         layers = cfg.get("layers", 1)
         small = key in ("c1", "c2")
@@ -624,6 +628,8 @@ def main():
                     help="launch decode steps directly instead of replaying a CUDA graph")
     ap.add_argument("--tc-mode", type=int, default=None,
                     help="RT_OPT_PREFILL_TC value (0: FP32-pipe kernel, 1: tensor-core kernel)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="override the workload's sequence / cache length (small cases)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the workload's batch (small cases for profiler captures)")
     args = ap.parse_args()

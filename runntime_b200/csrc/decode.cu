@@ -29,7 +29,11 @@ using namespace sm100;
 constexpr int kConsumers = 256;
 constexpr int kConsumerWarps = kConsumers / 32;
 constexpr int kMaxStages = 8;
+// Heads up to 64 wide fit two CTAs per SM (registers and shared memory), so that one
+// CTA's set-up, pipeline fill and merge overlap the other's streaming; wider heads get
+// the whole SM.
 constexpr size_t kSmemBudget = 200 * 1024;
+constexpr size_t kSmemBudgetTwoPerSm = 108 * 1024;
 
 __host__ __device__ constexpr int q_stride(int hdp) { return ((hdp / 4) & 1) ? hdp : hdp + 4; }
 
@@ -115,9 +119,9 @@ __device__ __forceinline__ void process_key(const T* kp, const T* vp, const floa
 }
 
 template <typename T, int HDP, bool EXACT, int VEC, bool BULK>
-__global__ void __launch_bounds__(BULK ? kConsumers + 32 : kConsumers)
+__global__ void __launch_bounds__(BULK ? kConsumers + 32 : kConsumers, HDP <= 64 ? 2 : 1)
 decode_kernel(const DecodeParams p) {
-  constexpr bool QSMEM = HDP > 64;
+  constexpr bool QSMEM = true;
   constexpr int QS = q_stride(HDP);
   extern __shared__ __align__(128) unsigned char smemRaw[];
   __shared__ int sAbort;
@@ -395,7 +399,7 @@ decode_kernel(const DecodeParams p) {
 size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
   const int group = p.qHeads / p.kvHeads;
   const int hqMax = p.kvPerCta * group;
-  const size_t qBytes = hdp > 64 ? (((size_t)hqMax * q_stride(hdp) * 4 + 127) / 128) * 128 : 0;
+  const size_t qBytes = (((size_t)hqMax * q_stride(hdp) * 4 + 127) / 128) * 128;
   const size_t tileBytes = (((size_t)p.keySlots * p.kvPerCta * p.hd * esize + 127) / 128) * 128;
   const size_t ringBytes = (size_t)(bulk ? p.stages : 1) * 2 * tileBytes;
   const size_t mergeBytes = (size_t)p.keySlots * hqMax * (2 + hdp) * 4;
@@ -462,8 +466,8 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
   int kvPerCta = p.kvHeads;
   while (kvPerCta * group > kConsumers) kvPerCta = (kvPerCta + 1) / 2;
   const int hdp = padded_hd(p.hd);
-  const size_t qBytes = hdp > 64 ? (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128 : 0;
-  const size_t budget = kSmemBudget - qBytes;
+  const size_t qBytes = (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128;
+  const size_t budget = (hdp <= 64 ? kSmemBudgetTwoPerSm : kSmemBudget) - qBytes;
   int keySlots;
   for (;;) {
     keySlots = kConsumers / (kvPerCta * group);
@@ -500,18 +504,20 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     int64_t maxS = nmax / (4ll * keySlots);  // at least four tiles per split
     if (maxS > 32) maxS = 32;
     if (maxS < 1) maxS = 1;
+    // Cost in units of one tile's streaming time: every CTA pays a fixed set-up,
+    // pipeline-fill and merge cost (about three tiles' worth, measured), CTAs run in
+    // waves of `resident` at a time, and splitting adds the partials pass.  Measured
+    // on B200: with at least one wave of sequences, not splitting is fastest.
+    const int64_t resident = (int64_t)smCount * (hdp <= 64 ? 2 : 1);
     int best = 1;
-    if (ctas * maxS <= smCount) {
-      best = (int)maxS;
-    } else {
-      double bestEff = 0.0;
-      for (int s = 1; s <= maxS; s++) {
-        const double waves = (double)(ctas * s) / smCount;
-        const double eff = waves / (double)((ctas * s + smCount - 1) / smCount);
-        if (eff > bestEff + 0.02) {
-          bestEff = eff;
-          best = s;
-        }
+    int64_t bestCost = INT64_MAX;
+    for (int s = 1; s <= maxS; s++) {
+      const int64_t tilesPerCta = (nmax + (int64_t)s * keySlots - 1) / ((int64_t)s * keySlots);
+      const int64_t waves = (ctas * s + resident - 1) / resident;
+      const int64_t cost = waves * (3 + tilesPerCta) + (s > 1 ? 3 : 0);
+      if (cost < bestCost) {
+        bestCost = cost;
+        best = s;
       }
     }
     p.splits = best;
