@@ -227,6 +227,16 @@ RT_API int rt_attn_decode_noalloc(const rt_decode_args* args, void* cuda_stream)
 RT_API int rt_attn_merge_partials(rt_ctx* ctx, const float* partials, int32_t parts, int64_t units,
                            int32_t headDim, void* out, int32_t dtype);
 
+/* ---- rope: the rotary embedding applied to q and k just before attention ------
+ * out [rows, width] = interleaved-pair rotation of columns [srcStart,
+ * srcStart+width) of x [rows, cols] by the pair-duplicated f32 tables cos, sin
+ * [rows, headDim] (any scale pre-folded): (x0, x1) -> (x0 c - x1 s, x1 c + x0 s).
+ * Replaces the 'rope' op and kernel (packages/runntime/src/core/graph/ops/
+ * attention.ts:214-252; packages/runntime/src/core/kernels/attention/rope.ts:36-112). */
+RT_API int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, void* out,
+                   int64_t rows, int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
+                   int32_t dtype);
+
 /* ---- writeRows: the KV-cache append as its own op ----------------------------
  * dst rows [startRow, startRow+rows) = src (packages/runntime/src/core/graph/
  * ops/shape.ts:236-259; kernel packages/runntime/src/core/kernels/shape/

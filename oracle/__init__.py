@@ -37,8 +37,10 @@ class _Dims(C.Structure):
 
 
 def build(force: bool = False) -> str:
-    """Compile liboracle.so if it is missing (or ``force``)."""
-    if force or not os.path.exists(_LIB_PATH):
+    """Compile liboracle.so if it is missing or older than its source (or ``force``)."""
+    src = os.path.join(_HERE, "sdpa_oracle.c")
+    stale = not os.path.exists(_LIB_PATH) or os.path.getmtime(src) > os.path.getmtime(_LIB_PATH)
+    if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "-B" if force else "-s", "liboracle.so"])
     return _LIB_PATH
 
@@ -221,6 +223,19 @@ def merge_partials(partials: np.ndarray) -> np.ndarray:
     out = np.empty((units, w - 2), dtype=np.float64)
     lib().oracle_merge_partials(_p(partials), C.c_int32(parts), C.c_int64(units),
                                 C.c_int32(w - 2), _p(out))
+    return out
+
+
+def rope_ref(x, cos, sin, *, headDim, srcStart=0, width=None) -> np.ndarray:
+    """f64 rotary embedding of a column window of x [rows, cols] (f32 values)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    cos = np.ascontiguousarray(cos, dtype=np.float32)
+    sin = np.ascontiguousarray(sin, dtype=np.float32)
+    rows, cols = x.shape
+    width = cols if width is None else width
+    out = np.empty((rows, width), dtype=np.float64)
+    lib().oracle_rope_f64(_p(x), _p(cos), _p(sin), C.c_int64(rows), C.c_int64(cols),
+                          C.c_int32(headDim), C.c_int64(srcStart), C.c_int64(width), _p(out))
     return out
 
 

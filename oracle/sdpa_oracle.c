@@ -21,6 +21,8 @@
  *     (packages/runntime/src/core/kernels/shape/rows.ts:143-162).
  *   - oracle_merge_partials: (m, l, acc) merge algebra of
  *     packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422.
+ *   - oracle_rope_f64: the rotary embedding that precedes attention in a decoder
+ *     layer (packages/runntime/src/core/kernels/attention/rope.ts:36-70).
  *   - oracle_random_f32 / oracle_round_f16: the reference tests' input
  *     generator (packages/runntime/test/gpu.ts:114-130).
  *
@@ -193,6 +195,26 @@ void oracle_sdpa_rows_f16(const _Float16* q, const _Float16* k, const _Float16* 
 void oracle_write_rows(void* dst, const void* src, int64_t startRow, int64_t rows, int64_t cols,
                        int32_t elemBytes) {
   memcpy((char*)dst + (size_t)startRow * cols * elemBytes, src, (size_t)rows * cols * elemBytes);
+}
+
+/* ---- rotary embedding ------------------------------------------------------ */
+
+/* Interleaved-pair rotation of columns [srcStart, srcStart+width) of x
+ * [rows, cols] by pair-duplicated f32 tables cos/sin [rows, headDim]; f64.
+ * Semantics: packages/runntime/test/core/kernels/attention/rope.gpu.test.ts:27-49
+ * (kernel: packages/runntime/src/core/kernels/attention/rope.ts:36-70). */
+void oracle_rope_f64(const float* x, const float* cosT, const float* sinT, int64_t rows,
+                     int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
+                     double* out) {
+  for (int64_t t = 0; t < rows; t++) {
+    for (int64_t col = 0; col < width; col += 2) {
+      const double c = cosT[t * headDim + (col % headDim)];
+      const double s = sinT[t * headDim + (col % headDim)];
+      const double x0 = x[t * cols + srcStart + col], x1 = x[t * cols + srcStart + col + 1];
+      out[t * width + col] = x0 * c - x1 * s;
+      out[t * width + col + 1] = x1 * c + x0 * s;
+    }
+  }
 }
 
 /* ---- (m, l, acc) merge ---------------------------------------------------- */

@@ -11,11 +11,11 @@ there is no CPU path.
 from .errors import RUNNTIME_ERROR_CODES, RunntimeError
 from .executor import CudaExecutor, evalValues, gpuExecutor, toArray
 from .nn import MultiHeadAttention, Parameter
-from .ops import sdpa, sdpaPacked, writeRows
+from .ops import rope, sdpa, sdpaPacked, writeRows
 from .value import DeviceBuffer, Value, ValueMeta, materialized, matrix, pending
 
 __all__ = [
     "RUNNTIME_ERROR_CODES", "RunntimeError", "CudaExecutor", "gpuExecutor", "evalValues",
-    "toArray", "MultiHeadAttention", "Parameter", "sdpa", "sdpaPacked", "writeRows",
+    "toArray", "MultiHeadAttention", "Parameter", "rope", "sdpa", "sdpaPacked", "writeRows",
     "DeviceBuffer", "Value", "ValueMeta", "materialized", "matrix", "pending",
 ]

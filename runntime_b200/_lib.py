@@ -65,6 +65,8 @@ SYMBOLS = {
     "rt_attn_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "rt_attn_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                          C.c_void_p, C.c_int32]),
+    "rt_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                          C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int32]),
     "rt_kv_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                C.c_int64, C.c_int64, C.c_int32]),
 }

@@ -498,6 +498,34 @@ int rt_attn_merge_partials(rt_ctx* ctx, const float* partials, int32_t parts, in
   return RT_OK;
 }
 
+int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, void* out,
+            int64_t rows, int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
+            int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!x || !cosT || !sinT || !out) return fail(ctx, RT_INVALID_ARGUMENT, "rope: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rope: bad dtype %d", dtype);
+  if (rows < 1 || cols < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rope: empty tensor (%lld x %lld)", (long long)rows,
+                (long long)cols);
+  if (headDim <= 0 || headDim % 2 != 0)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rope: headDim %d must be a positive even integer",
+                headDim);
+  if (srcStart < 0 || srcStart % 2 != 0)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rope: srcStart %lld must be a non-negative even integer",
+                (long long)srcStart);
+  if (width <= 0 || srcStart + width > cols)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rope: window [%lld, %lld) exceeds %lld input cols",
+                (long long)srcStart, (long long)(srcStart + width), (long long)cols);
+  if (width % headDim != 0)
+    return fail(ctx, RT_INVALID_ARGUMENT, "rope: width %lld must be a multiple of headDim %d",
+                (long long)width, headDim);
+  RT_CUDA(ctx, rt::launch_rope(x, cosT, sinT, out, rows, cols, headDim, srcStart, width, dtype,
+                               ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
 int rt_kv_append(rt_ctx* ctx, void* dst, const void* src, int64_t startRow, int64_t rows,
                  int64_t cols, int64_t dstRows, int32_t dtype) {
   RT_ENTER(ctx);

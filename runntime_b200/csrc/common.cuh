@@ -102,6 +102,9 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_merge_partials(const float* partials, int parts, int64_t units, int hd,
                                   void* out, int dtype, cudaStream_t s);
+cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
+                        int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
+                        int dtype, cudaStream_t s);
 cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes, int64_t bytes,
                               cudaStream_t s);
 

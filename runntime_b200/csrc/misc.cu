@@ -1,5 +1,6 @@
-// Small kernels beside attention: the standalone KV-cache append (writeRows)
-// and the cross-device merge of (m, l, acc) partials.
+// Small kernels beside attention: the standalone KV-cache append (writeRows),
+// the rotary embedding that precedes it, and the cross-device merge of
+// (m, l, acc) partials.
 #include "common.cuh"
 
 namespace rt {
@@ -44,7 +45,76 @@ __global__ void merge_partials_kernel(const float* __restrict__ partials, int pa
   }
 }
 
+// Rotary embedding, one thread per interleaved pair of a column window of x:
+// (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) with pair-duplicated f32 tables
+// [rows, headDim]; packages/runntime/src/core/kernels/attention/rope.ts:36-70.
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; };
+template <> struct Pair<__half> { using type = __half2; };
+
+// PAIRED: every pair of x and out sits on a pair-sized boundary (even row strides,
+// aligned bases), so a pair moves as one 8- or 4-byte access.
+template <typename T, bool PAIRED>
+__global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ cosT,
+                            const float* __restrict__ sinT, T* __restrict__ out, int64_t rows,
+                            int64_t srcCols, int hd, int64_t srcStart, int64_t width) {
+  using P = typename Pair<T>::type;
+  const int64_t pairs = width / 2, total = rows * pairs;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t row = i / pairs, col0 = (i - row * pairs) * 2;
+    const int dcol = (int)(col0 % hd);
+    const float c = cosT[row * hd + dcol], s = sinT[row * hd + dcol];
+    const T* src = x + row * srcCols + srcStart + col0;
+    T* dst = out + row * width + col0;
+    T a, b;
+    if (PAIRED) {
+      const P v = *reinterpret_cast<const P*>(src);
+      a = v.x, b = v.y;
+    } else {
+      a = src[0], b = src[1];
+    }
+    const float x0 = to_f32<T>(a), x1 = to_f32<T>(b);
+    const T r0 = from_f32<T>(x0 * c - x1 * s), r1 = from_f32<T>(x1 * c + x0 * s);
+    if (PAIRED) {
+      P v;
+      v.x = r0, v.y = r1;
+      *reinterpret_cast<P*>(dst) = v;
+    } else {
+      dst[0] = r0, dst[1] = r1;
+    }
+  }
+}
+
+template <typename T>
+void rope_launch(const void* x, const float* cosT, const float* sinT, void* out, int64_t rows,
+                 int64_t srcCols, int hd, int64_t srcStart, int64_t width, unsigned blocks,
+                 cudaStream_t s) {
+  const uintptr_t pairBytes = 2 * sizeof(T);
+  const bool paired = (srcCols % 2 == 0) && (reinterpret_cast<uintptr_t>(x) % pairBytes == 0) &&
+                      (reinterpret_cast<uintptr_t>(out) % pairBytes == 0);
+  auto* xi = static_cast<const T*>(x);
+  auto* oi = static_cast<T*>(out);
+  if (paired)
+    rope_kernel<T, true><<<blocks, 256, 0, s>>>(xi, cosT, sinT, oi, rows, srcCols, hd, srcStart, width);
+  else
+    rope_kernel<T, false><<<blocks, 256, 0, s>>>(xi, cosT, sinT, oi, rows, srcCols, hd, srcStart, width);
+}
+
 }  // namespace
+
+cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
+                        int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
+                        int dtype, cudaStream_t s) {
+  const int64_t total = rows * (width / 2);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == RT_F16)
+    rope_launch<__half>(x, cosT, sinT, out, rows, srcCols, hd, srcStart, width, (unsigned)blocks, s);
+  else
+    rope_launch<float>(x, cosT, sinT, out, rows, srcCols, hd, srcStart, width, (unsigned)blocks, s);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes, int64_t bytes,
                               cudaStream_t s) {

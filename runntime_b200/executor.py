@@ -159,6 +159,8 @@ class CudaExecutor:
             self._dispatch_attn(node, inputs, out, extras)
         elif op == "writeRows":
             self._dispatch_write_rows(node, inputs)
+        elif op == "rope":
+            self._dispatch_rope(node, inputs, out)
         else:
             raise RunntimeError("INVALID_ARGUMENT", f"dispatch: no kernel for op '{op}'")
 
@@ -232,6 +234,15 @@ class CudaExecutor:
         check(self._lib.rt_attn_route(self.ctx, C.byref(args), C.byref(route)), self.ctx)
         check(self._lib.rt_attn(self.ctx, C.byref(args)), self.ctx)
         self.dispatches.append(route.value.decode())
+
+    def _dispatch_rope(self, node, inputs, out):
+        xV = node.pending.inputs[0]
+        headDim, srcStart, width = (int(a) for a in node.pending.attrs)
+        rows, cols = xV.shape.dims
+        check(self._lib.rt_rope(self.ctx, C.c_void_p(inputs[0].ptr), C.c_void_p(inputs[1].ptr),
+                                C.c_void_p(inputs[2].ptr), C.c_void_p(out.ptr), rows, cols,
+                                headDim, srcStart, width, DTYPE_CODE[xV.shape.dtype]), self.ctx)
+        self.dispatches.append("rope")
 
     def _dispatch_write_rows(self, node, inputs):
         dstV, srcV = node.pending.inputs

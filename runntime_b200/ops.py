@@ -1,4 +1,4 @@
-"""Operator constructors of the attention path: ``sdpa``, ``sdpaPacked`` and
+"""Operator constructors of the attention path: ``sdpa``, ``sdpaPacked``, ``rope`` and
 ``writeRows`` with the reference's names, option names, defaults, synchronous
 validation and error texts
 (packages/runntime/src/core/graph/ops/attention.ts:28-212,
@@ -178,6 +178,36 @@ def sdpaPacked(qkv: Value, opts: dict) -> Value:
     attrs = [qHeads, kvHeads, headDim, wl, wr, qPosOffset, 1 if sinks is not None else 0,
              1 if segments is not None else 0, int(maxSegment), 1]
     return pending(ValueMeta(t * qw, dtype, (t, qw)), "attn", inputs, None, attrs)
+
+
+def rope(x: Value, cos: Value, sin: Value, opts: dict) -> Value:
+    """Rotary position embedding over every head section of x [T, W] in one
+    kernel.  Rotation is interleaved-pair, and cos/sin are pair-duplicated f32
+    tables [T, headDim] with any scale pre-folded.  ``srcStart`` and ``width``
+    optionally read a slice of a wider slab — the q or k section of a fused qkv —
+    and rope it in the same dispatch
+    (packages/runntime/src/core/graph/ops/attention.ts:214-252)."""
+    headDim = opts["headDim"]
+    t, xw, dtype = want2d("rope", x, FLOAT_DTYPES)
+    srcStart = opts.get("srcStart")
+    srcStart = 0 if srcStart is None else srcStart
+    w = opts.get("width")
+    w = xw if w is None else w
+    if not _is_int(headDim) or headDim <= 0 or headDim % 2 != 0:
+        raise ValueError(f"rope: headDim {_js(headDim)} must be a positive even integer")
+    if not _is_int(srcStart) or srcStart < 0 or srcStart % 2 != 0:
+        raise ValueError(f"rope: srcStart {_js(srcStart)} must be a non-negative even integer")
+    if not _is_int(w) or w <= 0 or srcStart + w > xw:
+        raise ValueError(
+            f"rope: window [{_js(srcStart)}, {_js(srcStart + w)}) exceeds {xw} input cols")
+    if w % headDim != 0:
+        raise ValueError(f"rope: width {_js(w)} must be a multiple of headDim {headDim}")
+    for name, v in (("cos", cos), ("sin", sin)):
+        if v.shape.dtype != "f32" or v.shape.elems != t * headDim:
+            raise ValueError(
+                f"rope: {name} must be f32 [T,headDim] = {t * headDim} elems, got {v.shape.elems}")
+    return pending(ValueMeta(t * int(w), dtype, (t, int(w))), "rope", [x, cos, sin], None,
+                   [int(headDim), int(srcStart), int(w)])
 
 
 def writeRows(dst: Value, src: Value, startRow) -> Value:

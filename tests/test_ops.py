@@ -214,3 +214,40 @@ def test_multi_head_attention_module():
     assert MultiHeadAttention(causal).parameters() == {}
     c = MultiHeadAttention(causal).forwardPacked(packed(5))
     assert c.pending.attrs[9] == 1
+
+
+# ---- rope (packages/runntime/test/core/graph/ops/attention.test.ts:232-283) ----
+
+from runntime_b200 import rope  # noqa: E402
+
+
+def _tables(t, headDim=HD):
+    return input_([t, headDim]), input_([t, headDim])
+
+
+def test_rope_rotates_every_head_or_a_slice():
+    cos, sin = _tables(5)
+    c = rope(input_([5, 32], "f16"), cos, sin, dict(headDim=HD))
+    assert c.shape == meta([5, 32], "f16") and list(c.pending.attrs) == [HD, 0, 32]
+    assert c.pending.op == "rope"
+    c = rope(input_([5, 64]), cos, sin, dict(headDim=HD, srcStart=32, width=16))
+    assert c.shape == meta([5, 16]) and list(c.pending.attrs) == [HD, 32, 16]
+
+
+@pytest.mark.parametrize("opts,error", [
+    (dict(headDim=7), r"headDim 7 must be a positive even integer"),
+    (dict(headDim=HD, srcStart=3, width=8), r"srcStart 3 must be a non-negative even integer"),
+    (dict(headDim=HD, srcStart=24, width=16), r"window \[24, 40\) exceeds 32 input cols"),
+    (dict(headDim=HD, width=12), r"width 12 must be a multiple of headDim 8"),
+])
+def test_rope_rejects_options(opts, error):
+    cos, sin = _tables(5)
+    with pytest.raises(ValueError, match=error):
+        rope(input_([5, 32]), cos, sin, opts)
+
+
+def test_rope_rejects_tables():
+    with pytest.raises(ValueError, match=r"cos must be f32 \[T,headDim\] = 40 elems, got 32"):
+        rope(input_([5, 32]), input_([4, HD]), input_([5, HD]), dict(headDim=HD))
+    with pytest.raises(ValueError, match=r"cos must be f32"):
+        rope(input_([5, 32]), input_([5, HD], "f16"), input_([5, HD]), dict(headDim=HD))

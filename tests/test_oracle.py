@@ -158,3 +158,32 @@ def test_write_rows_appends_in_place():
     view = oracle.write_rows(dst, src, 3)
     assert view.shape == (5, 4) and np.array_equal(dst[3:5], src) and (dst[:3] == 0).all()
     assert (dst[5] == 0).all()
+
+
+# ---- rope -------------------------------------------------------------------------
+
+def test_rope_hand_worked_vector():
+    # packages/runntime/test/core/kernels/attention/rope.gpu.test.ts:110-116: position 1,
+    # headDim 2, angle 1 turns (1, 0) to (cos 1, sin 1) and (0, 1) to (-sin 1, cos 1).
+    x = np.array([[1, 0], [0, 1]], np.float32)
+    cos = np.array([[1, 1], [math.cos(1)] * 2], np.float32)
+    sin = np.array([[0, 0], [math.sin(1)] * 2], np.float32)
+    got = oracle.rope_ref(x, cos, sin, headDim=2)
+    want = np.array([[1, 0], [-np.float32(math.sin(1)), np.float32(math.cos(1))]], np.float64)
+    assert np.allclose(got, want, rtol=0, atol=1e-12)
+
+
+@pytest.mark.parametrize("rows,cols,hd,start,width", [
+    (7, 60, 10, 0, None), (9, 128, 16, 64, 32), (3, 48, 16, 32, 16), (3, 136, 34, 0, None)])
+def test_rope_against_numpy(rows, cols, hd, start, width):
+    x = oracle.random_f32(rows * cols, 5).reshape(rows, cols)
+    cos = oracle.random_f32(rows * hd, 6).reshape(rows, hd)
+    sin = oracle.random_f32(rows * hd, 7).reshape(rows, hd)
+    w = cols if width is None else width  # tables need not be pair-duplicated: entry 2p is read
+    xs = x[:, start:start + w].astype(np.float64).reshape(rows, w // hd, hd // 2, 2)
+    c = cos.astype(np.float64).reshape(rows, 1, hd // 2, 2)
+    s = sin.astype(np.float64).reshape(rows, 1, hd // 2, 2)
+    want = np.stack([xs[..., 0] * c[..., 0] - xs[..., 1] * s[..., 0],
+                     xs[..., 1] * c[..., 0] + xs[..., 0] * s[..., 0]], -1).reshape(rows, w)
+    got = oracle.rope_ref(x, cos, sin, headDim=hd, srcStart=start, width=width)
+    assert np.allclose(got, want, rtol=1e-14, atol=1e-14)
