@@ -165,6 +165,17 @@ RT_API int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** rou
  * writeRows(cache, new, L_b-1) does (ops/shape.ts:230-259), rows past the view
  * keep their contents — and attends to them.
  *
+ * Fused rope: when ropeCos and ropeSin are given (pair-duplicated f32 tables,
+ * any scale folded in, as for rt_rope) q[b] and kNew[b] are the UN-rotated
+ * rows and the kernel rotates them itself — rounding the result to `dtype`
+ * exactly as the separate rope dispatch stores it — before the append and the
+ * scores.  Table row: L_b-1 when ropeByPosition is set (one table
+ * [positions, headDim] for the whole model), else b (tables [batch, headDim]
+ * gathered by the caller; with batch 1 that is the reference's cosRow/sinRow).
+ * Together with the row strides this lets q, kNew and vNew point into the one
+ * fused qkv row the projection wrote, so a decoder layer's rope x 2, slice,
+ * writeRows x 2 and attention (decoder.ts:58-76) become one launch.
+ *
  * partialsOut != NULL: instead of `out`, writes un-normalised partials
  * f32 [batch, qHeads, 2+headDim] = (m, l, acc) per head for a later
  * rt_attn_merge_partials (KV-sequence sharding across GPUs); keyOffset is
@@ -189,6 +200,12 @@ typedef struct {
   int32_t headDim;
   int32_t windowLeft;
   int32_t splits;         /* key splits per sequence; 0 = let the library choose */
+  int32_t ropeByPosition; /* rope table row: 0 = b, 1 = L_b-1 */
+  const float* ropeCos;   /* device f32 [batch or positions, headDim] or NULL */
+  const float* ropeSin;   /* device or NULL (both or neither) */
+  int64_t qRowStride;     /* elements between q rows; 0 = qHeads*headDim (dense) */
+  int64_t kNewRowStride;  /* elements between kNew rows; 0 = kvHeads*headDim */
+  int64_t vNewRowStride;  /* elements between vNew rows; 0 = kvHeads*headDim */
 } rt_decode_args;
 
 RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);
@@ -236,6 +253,15 @@ RT_API int rt_attn_merge_partials(rt_ctx* ctx, const float* partials, int32_t pa
 RT_API int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, void* out,
                    int64_t rows, int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
                    int32_t dtype);
+
+/* ---- slice: a row or column block of a 2-D tensor as its own tensor ------------
+ * out [rowEnd-rowStart, colEnd-colStart] = x[rowStart:rowEnd, colStart:colEnd] of
+ * x [rows, cols].  Replaces the 'sliceRows' / 'sliceCols' ops that cut v out of
+ * the fused qkv row and k | v out of the fused cross projection
+ * (packages/runntime/src/core/graph/ops/shape.ts:69-135; decoder.ts:55,72,93-97). */
+RT_API int rt_slice(rt_ctx* ctx, const void* x, void* out, int64_t rows, int64_t cols,
+                    int64_t rowStart, int64_t rowEnd, int64_t colStart, int64_t colEnd,
+                    int32_t dtype);
 
 /* ---- writeRows: the KV-cache append as its own op ----------------------------
  * dst rows [startRow, startRow+rows) = src (packages/runntime/src/core/graph/

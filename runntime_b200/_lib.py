@@ -43,6 +43,8 @@ class DecodeArgs(C.Structure):
         ("dtype", C.c_int32), ("batch", C.c_int32), ("cacheRows", C.c_int32),
         ("kvLen", C.c_int32), ("qHeads", C.c_int32), ("kvHeads", C.c_int32),
         ("headDim", C.c_int32), ("windowLeft", C.c_int32), ("splits", C.c_int32),
+        ("ropeByPosition", C.c_int32), ("ropeCos", C.c_void_p), ("ropeSin", C.c_void_p),
+        ("qRowStride", C.c_int64), ("kNewRowStride", C.c_int64), ("vNewRowStride", C.c_int64),
     ]
 
 
@@ -67,6 +69,8 @@ SYMBOLS = {
                                          C.c_void_p, C.c_int32]),
     "rt_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                           C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int32]),
+    "rt_slice": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                           C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     "rt_kv_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                C.c_int64, C.c_int64, C.c_int32]),
 }

@@ -461,24 +461,10 @@ int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
     return fail(ctx, RT_INVALID_ARGUMENT,
                 "rt_attn_decode: cacheSeqStride %lld is smaller than one cache",
                 (long long)a->cacheSeqStride);
+  if (const char* why = rt::decode_rope_args_error(*a))
+    return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: %s", why);
   rt::DecodeParams p{};
-  p.q = a->q;
-  p.out = a->out;
-  p.kCache = a->kCache;
-  p.vCache = a->vCache;
-  p.kNew = a->kNew;
-  p.vNew = a->vNew;
-  p.kvLens = a->kvLens;
-  p.sinks = a->sinks;
-  p.partialsOut = a->partialsOut;
-  p.cacheSeqStride = a->cacheSeqStride;
-  p.batch = a->batch;
-  p.kvLen = a->kvLens ? (a->kvLen > 0 ? a->kvLen : a->cacheRows) : a->kvLen;
-  p.qHeads = a->qHeads;
-  p.kvHeads = a->kvHeads;
-  p.hd = a->headDim;
-  p.wl = a->windowLeft;
-  p.splits = a->splits;
+  rt::decode_params_from_args(*a, p);
   return run_decode(ctx, p, a->dtype);
 }
 
@@ -522,6 +508,29 @@ int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, vo
                 (long long)width, headDim);
   RT_CUDA(ctx, rt::launch_rope(x, cosT, sinT, out, rows, cols, headDim, srcStart, width, dtype,
                                ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
+int rt_slice(rt_ctx* ctx, const void* x, void* out, int64_t rows, int64_t cols, int64_t rowStart,
+             int64_t rowEnd, int64_t colStart, int64_t colEnd, int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!x || !out) return fail(ctx, RT_INVALID_ARGUMENT, "slice: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "slice: bad dtype %d", dtype);
+  if (rows < 1 || cols < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "slice: empty tensor (%lld x %lld)", (long long)rows,
+                (long long)cols);
+  if (rowStart < 0 || rowEnd > rows || rowStart >= rowEnd)
+    return fail(ctx, RT_INVALID_ARGUMENT, "slice: bad range [%lld, %lld) for %lld rows",
+                (long long)rowStart, (long long)rowEnd, (long long)rows);
+  if (colStart < 0 || colEnd > cols || colStart >= colEnd)
+    return fail(ctx, RT_INVALID_ARGUMENT, "slice: bad range [%lld, %lld) for %lld cols",
+                (long long)colStart, (long long)colEnd, (long long)cols);
+  const int es = elem_size(dtype);
+  RT_CUDA(ctx, rt::launch_slice(x, out, rowEnd - rowStart, cols * es,
+                                (rowStart * cols + colStart) * es, (colEnd - colStart) * es,
+                                ctx->stream));
   ctx->launches++;
   return RT_OK;
 }

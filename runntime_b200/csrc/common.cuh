@@ -90,7 +90,64 @@ struct DecodeParams {
   int32_t kvPerCta;     // kv heads handled by one CTA
   int32_t keySlots;     // keys processed concurrently by one CTA
   int32_t stages;       // smem ring depth (bulk path)
+  // fused rope (null tables = off) and row strides of q / kNew / vNew, in elements
+  const float* ropeCos;
+  const float* ropeSin;
+  int32_t ropeByPos;
+  int64_t qRowStride, kNewRowStride, vNewRowStride;
 };
+
+// Copies the caller's decode arguments (already validated) into kernel parameters.
+inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
+  p.q = a.q;
+  p.out = a.out;
+  p.kCache = a.kCache;
+  p.vCache = a.vCache;
+  p.kNew = a.kNew;
+  p.vNew = a.vNew;
+  p.kvLens = a.kvLens;
+  p.sinks = a.sinks;
+  p.partialsOut = a.partialsOut;
+  p.cacheSeqStride = a.cacheSeqStride;
+  p.batch = a.batch;
+  p.kvLen = a.kvLens ? (a.kvLen > 0 ? a.kvLen : a.cacheRows) : a.kvLen;
+  p.qHeads = a.qHeads;
+  p.kvHeads = a.kvHeads;
+  p.hd = a.headDim;
+  p.wl = a.windowLeft;
+  p.splits = a.splits;
+  p.ropeCos = a.ropeCos;
+  p.ropeSin = a.ropeSin;
+  p.ropeByPos = a.ropeByPosition;
+  p.qRowStride = a.qRowStride ? a.qRowStride : (int64_t)a.qHeads * a.headDim;
+  p.kNewRowStride = a.kNewRowStride ? a.kNewRowStride : (int64_t)a.kvHeads * a.headDim;
+  p.vNewRowStride = a.vNewRowStride ? a.vNewRowStride : (int64_t)a.kvHeads * a.headDim;
+}
+
+// What is wrong with the rope / stride fields of decode arguments, or NULL.
+inline const char* decode_rope_args_error(const rt_decode_args& a) {
+  if ((a.ropeCos == nullptr) != (a.ropeSin == nullptr)) return "ropeCos and ropeSin go together";
+  if (a.ropeCos && a.headDim % 2 != 0) return "rope: headDim must be a positive even integer";
+  if (a.qRowStride < 0 || (a.qRowStride && a.qRowStride < (int64_t)a.qHeads * a.headDim))
+    return "qRowStride is smaller than one q row";
+  const int64_t kvw = (int64_t)a.kvHeads * a.headDim;
+  if (a.kNewRowStride < 0 || (a.kNewRowStride && a.kNewRowStride < kvw) ||
+      a.vNewRowStride < 0 || (a.vNewRowStride && a.vNewRowStride < kvw))
+    return "kNewRowStride / vNewRowStride is smaller than one kv row";
+  return nullptr;
+}
+
+#ifdef __CUDACC__
+// One interleaved pair of the rotary embedding:
+// packages/runntime/src/core/kernels/attention/rope.ts:60-68.  Spelled with
+// intrinsics so that every kernel using it rounds the same way (the compiler is
+// otherwise free to contract a*b - c*d differently from one kernel to the next).
+__device__ __forceinline__ void rope_pair(float x0, float x1, float c, float s, float& r0,
+                                          float& r1) {
+  r0 = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+  r1 = __fmaf_rn(x1, c, __fmul_rn(x0, s));
+}
+#endif
 
 // Launchers (defined one per .cu).  Each returns a cudaError_t from the launch.
 cudaError_t launch_prefill_simt(const AttnParams& p, int dtype, cudaStream_t s);
@@ -105,6 +162,8 @@ cudaError_t launch_merge_partials(const float* partials, int parts, int64_t unit
 cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
                         int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
                         int dtype, cudaStream_t s);
+cudaError_t launch_slice(const void* x, void* out, int64_t rows, int64_t srcColBytes,
+                         int64_t offsetBytes, int64_t widthBytes, cudaStream_t s);
 cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes, int64_t bytes,
                               cudaStream_t s);
 

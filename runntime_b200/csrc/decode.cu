@@ -142,12 +142,12 @@ decode_kernel(const DecodeParams p) {
   const bool hasNew = p.kNew != nullptr;
 
   // Key range of this sequence that lives in the cache.
-  int64_t lo, end;
+  int64_t lo, end, L = 0;
   if (p.useRange) {
     lo = p.lo;
     end = p.end;
   } else {
-    const int64_t L = p.kvLens ? p.kvLens[b] : p.kvLen;
+    L = p.kvLens ? p.kvLens[b] : p.kvLen;
     end = L - 1;
     lo = L - 1 - p.wl;
     if (lo < 0) lo = 0;
@@ -164,11 +164,14 @@ decode_kernel(const DecodeParams p) {
   const T* kBase = static_cast<const T*>(p.kCache) + (int64_t)b * p.cacheSeqStride + kvh0 * hd;
   const T* vBase = static_cast<const T*>(p.vCache) + (int64_t)b * p.cacheSeqStride + kvh0 * hd;
 
-  // Shared-memory carve-up: [q][ring: stages x (K tile, V tile)]; the ring is
-  // reused for the slot merge at the end.
+  // Shared-memory carve-up: [q][appended K, V slices][ring: stages x (K tile, V tile)];
+  // the ring is reused for the slot merge at the end.
   float* sQ = reinterpret_cast<float*>(smemRaw);
   const int qBytes = QSMEM ? ((hqMax * QS * 4 + 127) / 128) * 128 : 0;
-  unsigned char* ring = smemRaw + qBytes;
+  const int newBytes = hasNew ? ((p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128 : 0;
+  T* sKn = reinterpret_cast<T*>(smemRaw + qBytes);           // appended K slice
+  T* sVn = reinterpret_cast<T*>(smemRaw + qBytes + newBytes);  // appended V slice
+  unsigned char* ring = smemRaw + qBytes + 2 * newBytes;
   const int tileBytes = ((KS * p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128;
   const int stages = BULK ? p.stages : 1;
 
@@ -224,23 +227,62 @@ decode_kernel(const DecodeParams p) {
   const int h = kvh0 * group + hl;   // query head
   const int kvl = hl / group;        // kv head within the CTA's slice
 
-  float qreg[QSMEM ? 1 : HDP];
-  const float* qv;
+  // Stage q (f32) and, in split 0, the appended K/V slices; with rope tables q and
+  // the new K row are rotated here and rounded to T as the separate rope dispatch
+  // stores them.  The new row goes to the cache from the same threads (what
+  // writeRows would do) and is attended from shared memory after the cache keys.
+  const bool appendHere = hasNew && split == 0 && !p.useRange && L >= 1;
+  const float* qv = sQ + hl * QS;
   {
-    const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qHeads * hd;
-    if (QSMEM) {
+    const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qRowStride;
+    const bool roped = p.ropeCos != nullptr && !p.useRange;
+    const int64_t ropeRow = p.ropeByPos ? (L >= 1 ? L - 1 : 0) : b;
+    const float* rc = roped ? p.ropeCos + ropeRow * hd : nullptr;
+    const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
+    if (roped) {
+      const int hp = hd >> 1;
+      for (int idx = tid; idx < hq * hp; idx += kConsumers) {
+        const int hh = idx / hp, x = (idx - hh * hp) * 2;
+        const T* src = qg + (kvh0 * group + hh) * hd + x;
+        float r0, r1;
+        rope_pair(to_f32<T>(src[0]), to_f32<T>(src[1]), rc[x], rs[x], r0, r1);
+        sQ[hh * QS + x] = to_f32<T>(from_f32<T>(r0));
+        sQ[hh * QS + x + 1] = to_f32<T>(from_f32<T>(r1));
+      }
+    } else {
       for (int idx = tid; idx < hq * hd; idx += kConsumers) {
         const int hh = idx / hd, x = idx - hh * hd;
         sQ[hh * QS + x] = to_f32<T>(qg[(kvh0 * group + hh) * hd + x]);
       }
-      named_barrier_sync(1, kConsumers);
-      qv = sQ + hl * QS;
-    } else {
-#pragma unroll
-      for (int x = 0; x < HDP; x++)
-        qreg[x] = (active && (EXACT || x < hd)) ? to_f32<T>(qg[h * hd + x]) : 0.f;
-      qv = qreg;
     }
+    if (appendHere) {
+      const T* kn = static_cast<const T*>(p.kNew) + (int64_t)b * p.kNewRowStride + kvh0 * hd;
+      const T* vn = static_cast<const T*>(p.vNew) + (int64_t)b * p.vNewRowStride + kvh0 * hd;
+      T* kc = const_cast<T*>(kBase) + (L - 1) * rowElems;
+      T* vc = const_cast<T*>(vBase) + (L - 1) * rowElems;
+      if (roped) {
+        const int hp = hd >> 1;
+        for (int idx = tid; idx < nkv * hp; idx += kConsumers) {
+          const int hh = idx / hp, x = (idx - hh * hp) * 2;
+          float r0, r1;
+          rope_pair(to_f32<T>(kn[hh * hd + x]), to_f32<T>(kn[hh * hd + x + 1]), rc[x], rs[x], r0, r1);
+          const T t0 = from_f32<T>(r0), t1 = from_f32<T>(r1);
+          sKn[hh * hd + x] = t0, sKn[hh * hd + x + 1] = t1;
+          kc[hh * hd + x] = t0, kc[hh * hd + x + 1] = t1;
+        }
+      }
+      for (int x = tid; x < sliceElems; x += kConsumers) {
+        if (!roped) {
+          const T t = kn[x];
+          sKn[x] = t;
+          kc[x] = t;
+        }
+        const T u = vn[x];
+        sVn[x] = u;
+        vc[x] = u;
+      }
+    }
+    named_barrier_sync(1, kConsumers);
   }
 
   float m = kNegSeed, l = 0.f;
@@ -280,22 +322,9 @@ decode_kernel(const DecodeParams p) {
     }
   }
 
-  // Fused append: split 0 stores the new row into the cache and attends to it.
-  if (hasNew && split == 0 && !p.useRange) {
-    const int64_t L = p.kvLens ? p.kvLens[b] : p.kvLen;
-    if (L >= 1) {
-      const T* kn = static_cast<const T*>(p.kNew) + (int64_t)b * rowElems + kvh0 * hd;
-      const T* vn = static_cast<const T*>(p.vNew) + (int64_t)b * rowElems + kvh0 * hd;
-      T* kc = const_cast<T*>(kBase) + (L - 1) * rowElems;
-      T* vc = const_cast<T*>(vBase) + (L - 1) * rowElems;
-      for (int x = tid; x < sliceElems; x += kConsumers) {
-        kc[x] = kn[x];
-        vc[x] = vn[x];
-      }
-      if (active && slot == 0)
-        process_key<T, HDP, EXACT, VEC, QSMEM>(kn + kvl * hd, vn + kvl * hd, qv, hd, m, l, acc);
-    }
-  }
+  // Fused append: split 0 attends to the new row it staged (and stored) above.
+  if (appendHere && active && slot == 0)
+    process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + kvl * hd, sVn + kvl * hd, qv, hd, m, l, acc);
 
   if (!ok || sAbort) {
     // A wait ran out: record it, let copies in flight land, leave.
@@ -403,7 +432,8 @@ size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
   const size_t tileBytes = (((size_t)p.keySlots * p.kvPerCta * p.hd * esize + 127) / 128) * 128;
   const size_t ringBytes = (size_t)(bulk ? p.stages : 1) * 2 * tileBytes;
   const size_t mergeBytes = (size_t)p.keySlots * hqMax * (2 + hdp) * 4;
-  return qBytes + (ringBytes > mergeBytes ? ringBytes : mergeBytes);
+  const size_t newBytes = p.kNew ? 2 * ((((size_t)p.kvPerCta * p.hd * esize) + 127) / 128) * 128 : 0;
+  return qBytes + newBytes + (ringBytes > mergeBytes ? ringBytes : mergeBytes);
 }
 
 int padded_hd(int hd) { return hd <= 32 ? 32 : hd <= 64 ? 64 : 128; }
@@ -418,7 +448,6 @@ bool bulk_ok(const DecodeParams& p, int esize) {
   const int64_t sliceBytes = (int64_t)p.kvPerCta * p.hd * esize;
   if (rowBytes % 16 || sliceBytes % 16 || (p.cacheSeqStride * esize) % 16) return false;
   if (!aligned16(p.kCache) || !aligned16(p.vCache)) return false;
-  if (p.kNew && (!aligned16(p.kNew) || !aligned16(p.vNew))) return false;
   if (p.kvHeads % p.kvPerCta) return false;  // a ragged last block changes the slice size
   return true;
 }
@@ -466,7 +495,8 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
   int kvPerCta = p.kvHeads;
   while (kvPerCta * group > kConsumers) kvPerCta = (kvPerCta + 1) / 2;
   const int hdp = padded_hd(p.hd);
-  const size_t qBytes = (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128;
+  const size_t qBytes = (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128 +
+                        (p.kNew ? 2 * ((size_t)kvPerCta * p.hd * esize + 128) : 0);
   const size_t budget = (hdp <= 64 ? kSmemBudgetTwoPerSm : kSmemBudget) - qBytes;
   int keySlots;
   for (;;) {
@@ -586,7 +616,8 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
       a->kvLen > a->cacheRows || (!a->kvLens && a->kvLen < 1) || a->windowLeft < 0 ||
       a->splits < 0 || a->splits > 64 || (a->kNew == nullptr) != (a->vNew == nullptr) ||
       a->cacheSeqStride < 0 ||
-      (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim))
+      (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim) ||
+      decode_rope_args_error(*a) != nullptr)
     return static_fail(RT_INVALID_ARGUMENT,
                        "rt_attn_decode_noalloc: a size or option is out of range (same rules as "
                        "rt_attn_decode)");
@@ -620,23 +651,7 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
   }
 
   DecodeParams p{};
-  p.q = a->q;
-  p.out = a->out;
-  p.kCache = a->kCache;
-  p.vCache = a->vCache;
-  p.kNew = a->kNew;
-  p.vNew = a->vNew;
-  p.kvLens = a->kvLens;
-  p.sinks = a->sinks;
-  p.partialsOut = a->partialsOut;
-  p.cacheSeqStride = a->cacheSeqStride;
-  p.batch = a->batch;
-  p.kvLen = a->kvLens ? (a->kvLen > 0 ? a->kvLen : a->cacheRows) : a->kvLen;
-  p.qHeads = a->qHeads;
-  p.kvHeads = a->kvHeads;
-  p.hd = a->headDim;
-  p.wl = a->windowLeft;
-  p.splits = a->splits;
+  decode_params_from_args(*a, p);
   std::string err;
   if (!plan_decode(p, a->dtype, smCount, &err)) return static_fail(RT_INVALID_ARGUMENT, err);
   const size_t zBlocks = (size_t)(p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;

@@ -15,6 +15,19 @@ __global__ void write_rows_kernel(V* __restrict__ dst, const V* __restrict__ src
     dst[i] = src[i];
 }
 
+// out[r, c] = x[rowStart + r, colStart + c] in units of V (1 to 16 bytes):
+// packages/runntime/src/core/kernels/shape/columns.ts, rows.ts (sliceCols / sliceRows).
+template <typename V>
+__global__ void slice_kernel(V* __restrict__ out, const V* __restrict__ x, int64_t rows,
+                             int64_t width, int64_t srcCols, int64_t srcOffset) {
+  const int64_t total = rows * width;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / width, c = i - r * width;
+    out[i] = x[srcOffset + r * srcCols + c];
+  }
+}
+
 // One warp per unit (one query head of one sequence): M = max m_p,
 // L = sum l_p e^(m_p - M), o = sum acc_p e^(m_p - M) / L — the algebra of
 // packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422.
@@ -75,7 +88,9 @@ __global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ c
       a = src[0], b = src[1];
     }
     const float x0 = to_f32<T>(a), x1 = to_f32<T>(b);
-    const T r0 = from_f32<T>(x0 * c - x1 * s), r1 = from_f32<T>(x1 * c + x0 * s);
+    float f0, f1;
+    rope_pair(x0, x1, c, s, f0, f1);
+    const T r0 = from_f32<T>(f0), r1 = from_f32<T>(f1);
     if (PAIRED) {
       P v;
       v.x = r0, v.y = r1;
@@ -113,6 +128,25 @@ cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, voi
     rope_launch<__half>(x, cosT, sinT, out, rows, srcCols, hd, srcStart, width, (unsigned)blocks, s);
   else
     rope_launch<float>(x, cosT, sinT, out, rows, srcCols, hd, srcStart, width, (unsigned)blocks, s);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_slice(const void* x, void* out, int64_t rows, int64_t srcColBytes,
+                         int64_t offsetBytes, int64_t widthBytes, cudaStream_t s) {
+  const uintptr_t mis = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                        (uintptr_t)srcColBytes | (uintptr_t)offsetBytes | (uintptr_t)widthBytes;
+  auto run = [&](auto tag) {
+    using V = decltype(tag);
+    const int64_t u = sizeof(V), total = rows * (widthBytes / u);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    slice_kernel<V><<<(unsigned)blocks, 256, 0, s>>>(static_cast<V*>(out), static_cast<const V*>(x),
+                                                     rows, widthBytes / u, srcColBytes / u,
+                                                     offsetBytes / u);
+  };
+  if ((mis & 15) == 0) run(uint4{});
+  else if ((mis & 3) == 0) run(uint32_t{});
+  else run(uint16_t{});
   return cudaGetLastError();
 }
 

@@ -60,10 +60,14 @@ def prefill_batched(ex: CudaExecutor, q, k, v, out, *, dtype: str, batch: int, s
 def decode_batched(ex: CudaExecutor, q, out, kCache, vCache, *, dtype: str, batch: int,
                    cacheRows: int, qHeads: int, kvHeads: int, headDim: int, kvLen: int = 0,
                    kvLens=None, kNew=None, vNew=None, cacheSeqStride: Optional[int] = None,
-                   windowLeft=None, sinks=None, partialsOut=None, splits: int = 0) -> None:
+                   windowLeft=None, sinks=None, partialsOut=None, splits: int = 0,
+                   ropeCos=None, ropeSin=None, ropeByPosition: bool = False, qRowStride: int = 0,
+                   kNewRowStride: int = 0, vNewRowStride: int = 0) -> None:
     """One decode step for ``batch`` sequences; see rt_attn_decode in
     include/rt_attn.h.  ``kvLen`` is the (maximum) visible length including the
-    appended row; ``kvLens`` gives it per sequence."""
+    appended row; ``kvLens`` gives it per sequence.  With ``ropeCos``/``ropeSin``
+    q and kNew are un-rotated rows (for example windows of the fused qkv
+    projection, ``*RowStride`` apart) and the kernel rotates them."""
     d = DecodeArgs()
     d.q, d.out = _ptr(q), _ptr(out)
     d.kCache, d.vCache = _ptr(kCache), _ptr(vCache)
@@ -74,6 +78,8 @@ def decode_batched(ex: CudaExecutor, q, out, kCache, vCache, *, dtype: str, batc
     d.batch, d.cacheRows, d.kvLen = batch, cacheRows, kvLen
     d.qHeads, d.kvHeads, d.headDim = qHeads, kvHeads, headDim
     d.windowLeft, d.splits = _win(windowLeft), splits
+    d.ropeCos, d.ropeSin, d.ropeByPosition = _ptr(ropeCos), _ptr(ropeSin), int(ropeByPosition)
+    d.qRowStride, d.kNewRowStride, d.vNewRowStride = qRowStride, kNewRowStride, vNewRowStride
     check(ex._lib.rt_attn_decode(ex.ctx, C.byref(d)), ex.ctx)
 
 
@@ -103,19 +109,46 @@ class KvCacheEngine:
         self.lens = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.maxLen = 0
         self.cross: Optional[Tuple[object, object, int]] = None
+        self.rope = None
 
     def setCross(self, k, v, rows: int) -> None:
         """Precomputed cross-attention K/V [batch, rows, kvHeads*headDim]."""
         self.cross = (k, v, rows)
 
-    def step(self, q, kNew, vNew, out) -> None:
-        """Appends kNew/vNew at each sequence's end and attends causally."""
+    def setRope(self, cos, sin) -> None:
+        """Pair-duplicated f32 tables [maxPositions, headDim] (any scale folded in,
+        packages/runntime/src/zoo/moonshine/rope.ts:18-50); stepQkv then rotates."""
+        self.rope = (cos, sin)
+
+    def stepQkv(self, qkv, out) -> None:
+        """One decoder-layer step from the fused projection's rows
+        qkv [batch, (qHeads + 2*kvHeads)*headDim] (columns q|k|v, un-rotated): rope
+        on q and k at each sequence's position, append, causal attend — the six
+        dispatches of packages/runntime/src/zoo/moonshine/decoder.ts:66-76 in one launch."""
+        qw, kvw = self.qHeads * self.headDim, self.kvHeads * self.headDim
+        es = qkv.element_size()
+        base = qkv.data_ptr()
+        cos, sin = self.rope
+        self._advance()
+        decode_batched(self.ex, base, out, self.k, self.v, dtype=self.dtype, batch=self.batch,
+                       cacheRows=self.maxPositions, qHeads=self.qHeads, kvHeads=self.kvHeads,
+                       headDim=self.headDim, kvLen=self.maxLen, kvLens=self.lens,
+                       kNew=base + qw * es, vNew=base + (qw + kvw) * es,
+                       windowLeft=self.windowLeft, ropeCos=cos, ropeSin=sin, ropeByPosition=True,
+                       qRowStride=qw + 2 * kvw, kNewRowStride=qw + 2 * kvw,
+                       vNewRowStride=qw + 2 * kvw)
+
+    def _advance(self) -> None:
         if self.maxLen + 1 > self.maxPositions:
             raise ValueError(
                 f"writeRows: rows [{self.maxLen}, {self.maxLen + 1}) exceed dst capacity "
                 f"{self.maxPositions}")
         self.lens.add_(1)
         self.maxLen += 1
+
+    def step(self, q, kNew, vNew, out) -> None:
+        """Appends kNew/vNew at each sequence's end and attends causally."""
+        self._advance()
         decode_batched(self.ex, q, out, self.k, self.v, dtype=self.dtype, batch=self.batch,
                        cacheRows=self.maxPositions, qHeads=self.qHeads, kvHeads=self.kvHeads,
                        headDim=self.headDim, kvLen=self.maxLen, kvLens=self.lens, kNew=kNew,

@@ -12,7 +12,11 @@ buffers that are never pooled or freed here.
 
 One fusion the reference does not have: a decode-step ``attn`` node whose k and
 v are single-row ``writeRows`` appends at the query's position runs as one
-kernel that appends and attends (rt_attn_decode).
+kernel that appends and attends (rt_attn_decode).  When, as in a decoder
+layer's step (packages/runntime/src/zoo/moonshine/decoder.ts:58-76), q and the
+new k row are ``rope`` windows of one fused qkv row over the same tables and
+the new v row is a column ``slice`` (or any other row), those nodes run inside
+the same kernel too: six dispatches become one.
 """
 from __future__ import annotations
 
@@ -161,6 +165,8 @@ class CudaExecutor:
             self._dispatch_write_rows(node, inputs)
         elif op == "rope":
             self._dispatch_rope(node, inputs, out)
+        elif op in ("sliceRows", "sliceCols"):
+            self._dispatch_slice(node, inputs, out)
         else:
             raise RunntimeError("INVALID_ARGUMENT", f"dispatch: no kernel for op '{op}'")
 
@@ -205,9 +211,13 @@ class CudaExecutor:
         fused = (extras or {}).get("fusedAppend")
         if fused is not None:
             d = DecodeArgs()
-            d.q, d.out = q.ptr, out.ptr
+            d.q = fused["q"].ptr + fused["qOffset"] if "q" in fused else q.ptr
+            d.out = out.ptr
             d.kCache, d.vCache = fused["kCache"].ptr, fused["vCache"].ptr
-            d.kNew, d.vNew = fused["kNew"].ptr, fused["vNew"].ptr
+            d.kNew = fused["kNew"].ptr + fused["kNewOffset"]
+            d.vNew = fused["vNew"].ptr + fused["vNewOffset"]
+            if "ropeCos" in fused:
+                d.ropeCos, d.ropeSin = fused["ropeCos"].ptr, fused["ropeSin"].ptr
             d.sinks = sinks.ptr if sinks else None
             d.cacheSeqStride = 0
             d.dtype = DTYPE_CODE[node.shape.dtype]
@@ -215,7 +225,7 @@ class CudaExecutor:
             d.qHeads, d.kvHeads, d.headDim = qHeads, kvHeads, hd
             d.windowLeft, d.splits = wl, 0
             check(self._lib.rt_attn_decode(self.ctx, C.byref(d)), self.ctx)
-            self.dispatches.append("decode+append")
+            self.dispatches.append("decode+rope+append" if "ropeCos" in fused else "decode+append")
             return
         args = AttnArgs()
         args.q, args.k, args.v, args.out = q.ptr, k.ptr, v.ptr, out.ptr
@@ -243,6 +253,15 @@ class CudaExecutor:
                                 C.c_void_p(inputs[2].ptr), C.c_void_p(out.ptr), rows, cols,
                                 headDim, srcStart, width, DTYPE_CODE[xV.shape.dtype]), self.ctx)
         self.dispatches.append("rope")
+
+    def _dispatch_slice(self, node, inputs, out):
+        xV = node.pending.inputs[0]
+        rows, cols = xV.shape.dims
+        start, end = (int(a) for a in node.pending.attrs)
+        box = (start, end, 0, cols) if node.pending.op == "sliceRows" else (0, rows, start, end)
+        check(self._lib.rt_slice(self.ctx, C.c_void_p(inputs[0].ptr), C.c_void_p(out.ptr), rows,
+                                 cols, *box, DTYPE_CODE[xV.shape.dtype]), self.ctx)
+        self.dispatches.append(node.pending.op)
 
     def _dispatch_write_rows(self, node, inputs):
         dstV, srcV = node.pending.inputs
@@ -280,13 +299,20 @@ def _collect_pending(targets: Sequence[Value]) -> List[Value]:
 def _fusable_appends(order: List[Value], targets: Sequence[Value]) -> Dict[int, dict]:
     """attn nodes (by id) that can run as one append+attend kernel: one query
     row at the last position, causal, with k and v being single-row writeRows
-    appends at that position used by nothing else in this evaluation."""
+    appends at that position used by nothing else in this evaluation.  The plan
+    also names the rope / slice nodes feeding q and the new rows that the kernel
+    can absorb ("elided": used once, not targets, rope over the same tables)."""
     uses: Dict[int, int] = {}
     for n in order:
-        for i in set(n.pending.inputs):
+        for i in n.pending.inputs:
             uses[id(i)] = uses.get(id(i), 0) + 1
     target_ids = {id(t) for t in targets}
     pending_ids = {id(n) for n in order}
+
+    def private(v: Value, op: str) -> bool:
+        return (id(v) in pending_ids and v.pending.op == op and uses.get(id(v), 0) == 1
+                and id(v) not in target_ids)
+
     plan: Dict[int, dict] = {}
     for n in order:
         if n.pending.op != "attn":
@@ -295,17 +321,57 @@ def _fusable_appends(order: List[Value], targets: Sequence[Value]) -> Dict[int, 
         ins = n.pending.inputs
         if int(a[9]) or len(ins) < 3 or ins[0].shape.dims[0] != 1 or int(a[4]) != 0:
             continue
-        k, v = ins[1], ins[2]
+        q, k, v = ins[0], ins[1], ins[2]
         ok = True
         for w in (k, v):
-            ok &= (id(w) in pending_ids and w.pending.op == "writeRows"
-                   and uses.get(id(w), 0) == 1 and id(w) not in target_ids
+            ok &= (private(w, "writeRows")
                    and w.pending.inputs[1].shape.dims[0] == 1
                    and int(w.pending.attrs[0]) == int(a[5])
                    and w.shape.dims[0] == int(a[5]) + 1)
-        if ok and k is not v:
-            plan[id(n)] = {"k": k, "v": v}
+        if not ok or k is v:
+            continue
+        entry = {"k": k, "v": v, "elided": []}
+        kNew, vNew = k.pending.inputs[1], v.pending.inputs[1]
+        hd = int(a[2])
+        if (private(q, "rope") and private(kNew, "rope")
+                and q.pending.inputs[1] is kNew.pending.inputs[1]
+                and q.pending.inputs[2] is kNew.pending.inputs[2]
+                and int(q.pending.attrs[0]) == hd and int(kNew.pending.attrs[0]) == hd
+                and q.pending.inputs[0].shape.dims[0] == 1
+                and kNew.pending.inputs[0].shape.dims[0] == 1):
+            entry["rope"] = (q, kNew)
+            entry["elided"] += [q, kNew]
+        if private(vNew, "sliceCols") and vNew.pending.inputs[0].shape.dims[0] == 1:
+            entry["vSlice"] = vNew
+            entry["elided"].append(vNew)
+        plan[id(n)] = entry
     return plan
+
+
+def _window(node: Value, startCol: int):
+    """(buffer, byte offset) of column ``startCol`` of the single row ``node`` reads."""
+    x = node.pending.inputs[0]
+    return x.buffer, startCol * elemBytes(x.shape.dtype)
+
+
+def _fused_extras(f: dict) -> dict:
+    """Buffers (and byte offsets into them) the fused decode step reads."""
+    k, v = f["k"], f["v"]
+    kNew, vNew = k.pending.inputs[1], v.pending.inputs[1]
+    ex = {"kCache": k.pending.inputs[0].buffer, "vCache": v.pending.inputs[0].buffer,
+          "cacheRows": k.pending.inputs[0].shape.dims[0]}
+    if "rope" in f:
+        q = f["rope"][0]
+        ex["q"], ex["qOffset"] = _window(q, int(q.pending.attrs[1]))
+        ex["kNew"], ex["kNewOffset"] = _window(kNew, int(kNew.pending.attrs[1]))
+        ex["ropeCos"], ex["ropeSin"] = q.pending.inputs[1].buffer, q.pending.inputs[2].buffer
+    else:
+        ex["kNew"], ex["kNewOffset"] = kNew.buffer, 0
+    if "vSlice" in f:
+        ex["vNew"], ex["vNewOffset"] = _window(vNew, int(vNew.pending.attrs[0]))
+    else:
+        ex["vNew"], ex["vNewOffset"] = vNew.buffer, 0
+    return ex
 
 
 def evalValues(targets: Sequence[Value], ex: CudaExecutor) -> None:
@@ -316,14 +382,18 @@ def evalValues(targets: Sequence[Value], ex: CudaExecutor) -> None:
     target_ids = {id(t) for t in targets}
     fuse = _fusable_appends(order, targets)
     skipped = {id(w) for f in fuse.values() for w in (f["k"], f["v"])}
+    # Nodes a fused kernel computes on the fly: never dispatched, they stay pending.
+    elided = {id(w) for f in fuse.values() for w in f["elided"]}
     remaining: Dict[int, int] = {}
     for n in order:
         for i in set(n.pending.inputs):
             remaining[id(i)] = remaining.get(id(i), 0) + 1
     aliased = set()
     for node in order:
+        if id(node) in elided:
+            continue
         p = node.pending
-        ins = [i.buffer for i in p.inputs]
+        ins = [None if id(i) in elided else i.buffer for i in p.inputs]
         if p.op in IN_PLACE_OPS:
             out = ins[0]
             aliased.add(id(node))
@@ -333,24 +403,22 @@ def evalValues(targets: Sequence[Value], ex: CudaExecutor) -> None:
             out = ex.acquireOutput(node.shape)
             extras = None
             if id(node) in fuse:
-                k, v = fuse[id(node)]["k"], fuse[id(node)]["v"]
-                extras = {"fusedAppend": {
-                    "kCache": k.pending.inputs[0].buffer, "vCache": v.pending.inputs[0].buffer,
-                    "kNew": k.pending.inputs[1].buffer, "vNew": v.pending.inputs[1].buffer,
-                    "cacheRows": k.pending.inputs[0].shape.dims[0]}}
+                extras = {"fusedAppend": _fused_extras(fuse[id(node)])}
             ex.dispatch(node, ins, out, extras)
         node.setMaterialized(out)
         if id(node) in skipped:
             continue  # its inputs are read by the fused kernel: released after that one
         consumed = [p.inputs]
         if id(node) in fuse:
-            consumed += [fuse[id(node)]["k"].pending.inputs, fuse[id(node)]["v"].pending.inputs]
+            f = fuse[id(node)]
+            consumed += [f["k"].pending.inputs, f["v"].pending.inputs]
+            consumed += [w.pending.inputs for w in f["elided"]]
         for group in consumed:
             for i in set(group):
                 remaining[id(i)] -= 1
                 if (remaining[id(i)] == 0 and id(i) in produced and id(i) not in target_ids):
-                    if id(i) in aliased:
-                        continue  # a view of a caller-owned buffer: stays valid
+                    if id(i) in aliased or id(i) in elided:
+                        continue  # a view of a caller-owned buffer / never materialized
                     ex.releaseOutput(i.buffer, i.shape)
                     i.markReleased()
     ex.submit()

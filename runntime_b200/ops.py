@@ -210,6 +210,51 @@ def rope(x: Value, cos: Value, sin: Value, opts: dict) -> Value:
                    [int(headDim), int(srcStart), int(w)])
 
 
+def _norm_dim(op: str, dim, rank: int) -> int:
+    """packages/runntime/src/core/graph/ops/shared.ts:102-109."""
+    if not _is_int(dim):
+        raise ValueError(f"{op}: dim must be an integer, got {_js(dim)}")
+    d = int(dim) + rank if dim < 0 else int(dim)
+    if d < 0 or d >= rank:
+        raise ValueError(f"{op}: dim {_js(dim)} out of range for a rank-{rank} operand")
+    return d
+
+
+def slice(x: Value, dim, start, end) -> Value:  # noqa: A001 - the reference's name
+    """Narrows a 2-D x to [start, end) along dim, like torch's narrow: how v is
+    cut out of a fused qkv row and k | v out of the fused cross projection
+    (packages/runntime/src/core/graph/ops/shape.ts:69-135)."""
+    dims = x.shape.dims
+    if dims is None or len(dims) != 2:
+        got = "undefined" if dims is None else ",".join(str(d) for d in dims)
+        raise ValueError(f"slice: needs a 2D or 3D operand, got dims {got}")
+    d = _norm_dim("slice", dim, 2)
+    m, n, dtype = want2d("slice", x, FLOAT_DTYPES)
+    size, what = (m, "rows") if d == 0 else (n, "cols")
+    if not _is_int(start) or not _is_int(end) or start < 0 or end > size or start >= end:
+        raise ValueError(f"slice: bad range [{_js(start)}, {_js(end)}) for {size} {what}")
+    start, end = int(start), int(end)
+    if d == 0:
+        return pending(ValueMeta((end - start) * n, dtype, (end - start, n)), "sliceRows", [x],
+                       None, [start, end])
+    return pending(ValueMeta(m * (end - start), dtype, (m, end - start)), "sliceCols", [x], None,
+                   [start, end])
+
+
+def chunk(x: Value, n, dim) -> list:
+    """Splits x into n equal parts along dim, like torch.chunk; exact division only
+    (packages/runntime/src/core/graph/ops/shape.ts:83-96)."""
+    rank = len(x.shape.dims) if x.shape.dims is not None else 0
+    d = _norm_dim("chunk", dim, rank)
+    size = x.shape.dims[d]
+    if not _is_int(n) or n < 1:
+        raise ValueError(f"chunk: n must be a positive integer, got {_js(n)}")
+    if size % n != 0:
+        raise ValueError(f"chunk: dim {_js(dim)} size {size} does not divide into {_js(n)} equal parts")
+    step = size // int(n)
+    return [slice(x, d, i * step, (i + 1) * step) for i in range(int(n))]
+
+
 def writeRows(dst: Value, src: Value, startRow) -> Value:
     """In-place row write: copies src into rows [startRow, startRow + r) of the
     caller-owned buffer behind dst and returns a [startRow + r, cols] view of

@@ -41,11 +41,16 @@ class Recorder:
 
     def dispatch(self, node, inputs, out, extras=None):
         for b in inputs:
+            if b is None:
+                continue  # computed inside the fused kernel
             assert id(b) not in self.released, "reads a released buffer"
         line = f"{self.node_name[id(node)]} -> {self.buf_name[id(out)]}"
         if extras and "fusedAppend" in extras:
             f = extras["fusedAppend"]
             line += f" +append({self.buf_name[id(f['kNew'])]},{self.buf_name[id(f['vNew'])]})"
+            if "ropeCos" in f:
+                line += (f" +rope({self.buf_name[id(f['q'])]}@{f['qOffset']},"
+                         f"k@{f['kNewOffset']},v@{f['vNewOffset']})")
         self.log.append(line)
 
     def submit(self):
@@ -111,3 +116,52 @@ def test_no_fusion_when_the_view_is_also_a_target_or_not_a_single_row():
     assert rec.log[:2] == ["k -> kc", "v -> vc"]
     n = _decode_step(3, wr=INF)  # cross-style window: not the causal decode step
     assert _fusable_appends([n["k"], n["v"], n["y"]], [n["y"]]) == {}
+
+
+def _decoder_layer_step(t, *, share_tables=True, slice_v=True):
+    """q and kNew roped out of one fused qkv row, vNew sliced out of it
+    (packages/runntime/src/zoo/moonshine/decoder.ts:58-76)."""
+    from runntime_b200 import rope, slice as slice_
+    w = 8  # qHeads 2 x headDim 4; kvHeads 2 for this one
+    hd = 4
+    qkv = mat(1, 3 * w, name="qkv")
+    cos, sin, cos2 = mat(1, hd), mat(1, hd), mat(1, hd)
+    kc, vc = mat(16, w), mat(16, w)
+    q = rope(qkv, cos, sin, dict(headDim=hd, srcStart=0, width=w))
+    kNew = rope(qkv, cos if share_tables else cos2, sin, dict(headDim=hd, srcStart=w, width=w))
+    vNew = slice_(qkv, 1, 2 * w, 3 * w) if slice_v else mat(1, w)
+    k, v = writeRows(kc, kNew, t), writeRows(vc, vNew, t)
+    y = sdpa(q, k, v, dict(qHeads=2, kvHeads=2, headDim=hd, windowLeft=INF, windowRight=0,
+                           qPosOffset=t))
+    return dict(qkv=qkv, cos=cos, sin=sin, cos2=cos2, kc=kc, vc=vc, q=q, kNew=kNew, vNew=vNew,
+                k=k, v=v, y=y)
+
+
+def test_decoder_layer_step_is_one_dispatch():
+    n = _decoder_layer_step(5)
+    rec = Recorder(n)
+    evalValues([n["y"]], rec)
+    assert rec.log == ["y -> #0 +append(qkv,qkv) +rope(qkv@0,k@32,v@64)", "submit"]
+    # the absorbed nodes were never dispatched and own no buffer
+    for name in ("q", "kNew", "vNew"):
+        assert n[name].state == "pending"
+    assert n["k"].buffer is n["kc"].buffer
+
+
+def test_rope_is_not_absorbed_over_different_tables_or_when_kept():
+    n = _decoder_layer_step(5, share_tables=False)
+    rec = Recorder(n)
+    evalValues([n["y"]], rec)
+    assert rec.log[:2] == ["q -> #0", "kNew -> #1"]
+    assert rec.log[2] == "y -> #2 +append(#1,qkv)"   # append still fused, v still sliced in place
+    n = _decoder_layer_step(5)
+    rec = Recorder(n)
+    evalValues([n["y"], n["q"]], rec)                # q is wanted by the caller: dispatched
+    assert "q -> #0" in rec.log and not any("+rope" in line for line in rec.log)
+
+
+def test_new_v_row_may_be_a_tensor_of_its_own():
+    n = _decoder_layer_step(5, slice_v=False)
+    rec = Recorder(n)
+    evalValues([n["y"]], rec)
+    assert rec.log == ["y -> #0 +append(qkv,vNew) +rope(qkv@0,k@32,v@0)", "submit"]

@@ -251,3 +251,37 @@ def test_rope_rejects_tables():
         rope(input_([5, 32]), input_([4, HD]), input_([5, HD]), dict(headDim=HD))
     with pytest.raises(ValueError, match=r"cos must be f32"):
         rope(input_([5, 32]), input_([5, HD], "f16"), input_([5, HD]), dict(headDim=HD))
+
+
+# ---- slice / chunk (packages/runntime/src/core/graph/ops/shape.ts:69-135) --------
+
+from runntime_b200 import chunk, slice as slice_  # noqa: E402
+
+
+def test_slice_columns_and_rows():
+    c = slice_(input_([3, 24], "f16"), 1, 16, 24)
+    assert c.shape == meta([3, 8], "f16") and c.pending.op == "sliceCols"
+    assert list(c.pending.attrs) == [16, 24]
+    r = slice_(input_([6, 4]), 0, 2, 5)
+    assert r.shape == meta([3, 4]) and r.pending.op == "sliceRows"
+    assert slice_(input_([6, 4]), -1, 0, 2).pending.op == "sliceCols"
+
+
+def test_slice_rejects_bad_ranges():
+    with pytest.raises(ValueError, match=r"slice: bad range \[4, 4\) for 8 cols"):
+        slice_(input_([2, 8]), 1, 4, 4)
+    with pytest.raises(ValueError, match=r"slice: bad range \[0, 9\) for 8 cols"):
+        slice_(input_([2, 8]), 1, 0, 9)
+    with pytest.raises(ValueError, match=r"slice: bad range \[-1, 1\) for 2 rows"):
+        slice_(input_([2, 8]), 0, -1, 1)
+    with pytest.raises(ValueError, match=r"slice: dim 2 out of range for a rank-2 operand"):
+        slice_(input_([2, 8]), 2, 0, 1)
+
+
+def test_chunk_splits_k_and_v_of_a_fused_projection():
+    k, v = chunk(input_([200, 576], "f16"), 2, 1)
+    assert k.shape == meta([200, 288], "f16") and list(v.pending.attrs) == [288, 576]
+    with pytest.raises(ValueError, match=r"chunk: dim 1 size 576 does not divide into 5 equal parts"):
+        chunk(input_([200, 576]), 5, 1)
+    with pytest.raises(ValueError, match=r"chunk: n must be a positive integer, got 0"):
+        chunk(input_([200, 576]), 0, 1)
