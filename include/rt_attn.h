@@ -254,6 +254,17 @@ RT_API int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* s
                    int64_t rows, int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
                    int32_t dtype);
 
+/* ---- softmax: row-wise over the last dim, optionally masked ---------------------
+ * out [rows, cols] = softmax of each row of x.  With `segments` (f32 [rows, 2],
+ * a [start, end) key range per row) x is square attention scores: row r keeps
+ * keys j with start <= j < end and r - windowLeft <= j <= r + windowRight
+ * (RT_WINDOW_INF = unbounded); the rest come out 0, and a row that keeps nothing
+ * is all 0.  Replaces the 'softmax' op of the matmul-attention path
+ * (packages/runntime/src/core/graph/ops/reduce.ts:12-39; kernel
+ * packages/runntime/src/core/kernels/reduce/softmax.ts:111-186). */
+RT_API int rt_softmax(rt_ctx* ctx, const void* x, void* out, const float* segments, int64_t rows,
+                      int64_t cols, int32_t windowLeft, int32_t windowRight, int32_t dtype);
+
 /* ---- slice: a row or column block of a 2-D tensor as its own tensor ------------
  * out [rowEnd-rowStart, colEnd-colStart] = x[rowStart:rowEnd, colStart:colEnd] of
  * x [rows, cols].  Replaces the 'sliceRows' / 'sliceCols' ops that cut v out of

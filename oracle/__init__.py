@@ -239,6 +239,20 @@ def rope_ref(x, cos, sin, *, headDim, srcStart=0, width=None) -> np.ndarray:
     return out
 
 
+def softmax_ref(x, segs=None, windowLeft=math.inf, windowRight=math.inf) -> np.ndarray:
+    """f64 row softmax of x [rows, cols] (f32 values), masked when ``segs`` is given."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    out = np.empty((rows, cols), dtype=np.float64)
+    sp = None
+    if segs is not None:
+        segs = np.ascontiguousarray(segs, dtype=np.float32)
+        sp = _p(segs)
+    lib().oracle_softmax_f64(_p(x), sp, C.c_int64(rows), C.c_int64(cols),
+                             C.c_int64(_win(windowLeft)), C.c_int64(_win(windowRight)), _p(out))
+    return out
+
+
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
 

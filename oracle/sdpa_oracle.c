@@ -23,6 +23,8 @@
  *     packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422.
  *   - oracle_rope_f64: the rotary embedding that precedes attention in a decoder
  *     layer (packages/runntime/src/core/kernels/attention/rope.ts:36-70).
+ *   - oracle_softmax_f64: the (optionally masked) row softmax of the
+ *     matmul-attention path (packages/runntime/src/core/kernels/reduce/softmax.ts:111-186).
  *   - oracle_random_f32 / oracle_round_f16: the reference tests' input
  *     generator (packages/runntime/test/gpu.ts:114-130).
  *
@@ -214,6 +216,34 @@ void oracle_rope_f64(const float* x, const float* cosT, const float* sinT, int64
       out[t * width + col] = x0 * c - x1 * s;
       out[t * width + col + 1] = x1 * c + x0 * s;
     }
+  }
+}
+
+/* ---- softmax ---------------------------------------------------------------- */
+
+/* Row-wise softmax from the definition, in f64; with segs ([rows, 2] f32) row r
+ * keeps key j when segs[2r] <= j < segs[2r+1] and r - wl <= j <= r + wr, the rest
+ * come out 0 and are left out of the max and the sum.  Semantics:
+ * packages/runntime/test/core/kernels/reduce/softmax.gpu.test.ts:18-37,129-160. */
+void oracle_softmax_f64(const float* x, const float* segs, int64_t rows, int64_t cols, int64_t wl,
+                        int64_t wr, double* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; r++) {
+    int64_t lo = 0, hi = cols;
+    if (segs) {
+      lo = (int64_t)segs[2 * r];
+      hi = (int64_t)segs[2 * r + 1];
+      if (r - wl > lo) lo = r - wl;
+      if (r + wr + 1 < hi) hi = r + wr + 1;
+      if (hi > cols) hi = cols;
+      if (lo < 0) lo = 0;
+    }
+    double mx = -INFINITY, sum = 0.0;
+    for (int64_t j = lo; j < hi; j++)
+      if (x[r * cols + j] > mx) mx = x[r * cols + j];
+    for (int64_t j = lo; j < hi; j++) sum += exp((double)x[r * cols + j] - mx);
+    for (int64_t j = 0; j < cols; j++)
+      out[r * cols + j] = (j >= lo && j < hi) ? exp((double)x[r * cols + j] - mx) / sum : 0.0;
   }
 }
 

@@ -512,6 +512,29 @@ int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, vo
   return RT_OK;
 }
 
+int rt_softmax(rt_ctx* ctx, const void* x, void* out, const float* segments, int64_t rows,
+               int64_t cols, int32_t windowLeft, int32_t windowRight, int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!x || !out) return fail(ctx, RT_INVALID_ARGUMENT, "softmax: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "softmax: bad dtype %d", dtype);
+  if (rows < 1 || cols < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "softmax: empty tensor (%lld x %lld)", (long long)rows,
+                (long long)cols);
+  if (segments && rows != cols)
+    return fail(ctx, RT_INVALID_ARGUMENT, "softmax: a masked softmax needs square scores, got [%lld, %lld]",
+                (long long)rows, (long long)cols);
+  if (segments && (windowLeft < 0 || windowRight < 0))
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "softmax: %s must be a non-negative integer or Infinity, got %d",
+                windowLeft < 0 ? "windowLeft" : "windowRight",
+                windowLeft < 0 ? windowLeft : windowRight);
+  RT_CUDA(ctx, rt::launch_softmax(x, out, segments, rows, cols, windowLeft, windowRight, dtype,
+                                  ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
 int rt_slice(rt_ctx* ctx, const void* x, void* out, int64_t rows, int64_t cols, int64_t rowStart,
              int64_t rowEnd, int64_t colStart, int64_t colEnd, int32_t dtype) {
   RT_ENTER(ctx);

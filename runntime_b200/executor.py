@@ -167,6 +167,8 @@ class CudaExecutor:
             self._dispatch_rope(node, inputs, out)
         elif op in ("sliceRows", "sliceCols"):
             self._dispatch_slice(node, inputs, out)
+        elif op == "softmax":
+            self._dispatch_softmax(node, inputs, out)
         else:
             raise RunntimeError("INVALID_ARGUMENT", f"dispatch: no kernel for op '{op}'")
 
@@ -253,6 +255,18 @@ class CudaExecutor:
                                 C.c_void_p(inputs[2].ptr), C.c_void_p(out.ptr), rows, cols,
                                 headDim, srcStart, width, DTYPE_CODE[xV.shape.dtype]), self.ctx)
         self.dispatches.append("rope")
+
+    def _dispatch_softmax(self, node, inputs, out):
+        a = node.pending.attrs
+        if a is None or len(a) < 3:
+            raise RunntimeError("INVALID_ARGUMENT",
+                                "dispatch: softmax attrs need [masked, windowLeft, windowRight]")
+        rows, cols = node.shape.dims
+        segs = C.c_void_p(inputs[1].ptr) if int(a[0]) else None
+        check(self._lib.rt_softmax(self.ctx, C.c_void_p(inputs[0].ptr), C.c_void_p(out.ptr), segs,
+                                   rows, cols, int(a[1]), int(a[2]), DTYPE_CODE[node.shape.dtype]),
+              self.ctx)
+        self.dispatches.append("softmax")
 
     def _dispatch_slice(self, node, inputs, out):
         xV = node.pending.inputs[0]

@@ -210,6 +210,36 @@ def rope(x: Value, cos: Value, sin: Value, opts: dict) -> Value:
                    [int(headDim), int(srcStart), int(w)])
 
 
+def softmax(x: Value, opts: Optional[dict] = None) -> Value:
+    """Row-wise softmax over the last dim.  With ``segments`` ([M, 2] f32, a
+    [start, end) range per row) x is MxM attention scores: row r keeps the keys in
+    its range and window, r included, and the rest come out 0.  Windows default to
+    Infinity (packages/runntime/src/core/graph/ops/reduce.ts:12-39)."""
+    opts = opts or {}
+    m, n, dtype = want2d("softmax", x, FLOAT_DTYPES)
+    shape = ValueMeta(m * n, dtype, (m, n))
+    segments = opts.get("segments")
+    if segments is None:
+        return pending(shape, "softmax", [x], None, [0, 0, 0])
+    if m != n:
+        raise ValueError(f"softmax: a masked softmax needs square scores, got [{m}, {n}]")
+    if segments.shape.dtype != "f32" or segments.shape.elems != 2 * m:
+        raise ValueError(f"softmax: segments must be f32 [{m}, 2]")
+
+    def lower(name: str, w) -> int:
+        w = math.inf if w is None else w
+        if w == math.inf:
+            return WINDOW_INF
+        if not _is_int(w) or w < 0:
+            raise ValueError(
+                f"softmax: {name} must be a non-negative integer or Infinity, got {_js(w)}")
+        return min(int(w), WINDOW_INF)
+
+    wl = lower("windowLeft", opts.get("windowLeft"))
+    wr = lower("windowRight", opts.get("windowRight"))
+    return pending(shape, "softmax", [x, segments], None, [1, wl, wr])
+
+
 def _norm_dim(op: str, dim, rank: int) -> int:
     """packages/runntime/src/core/graph/ops/shared.ts:102-109."""
     if not _is_int(dim):

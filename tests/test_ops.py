@@ -285,3 +285,38 @@ def test_chunk_splits_k_and_v_of_a_fused_projection():
         chunk(input_([200, 576]), 5, 1)
     with pytest.raises(ValueError, match=r"chunk: n must be a positive integer, got 0"):
         chunk(input_([200, 576]), 0, 1)
+
+
+# ---- softmax (packages/runntime/test/core/graph/ops/reduce.test.ts:17-78) ----------
+
+from runntime_b200 import softmax  # noqa: E402
+
+
+def test_softmax_keeps_the_shape_and_runs_unmasked_without_segments():
+    c = softmax(input_([4, 8], "f16"))
+    assert c.shape == meta([4, 8], "f16") and list(c.pending.attrs) == [0, 0, 0]
+    with pytest.raises(ValueError, match=r"expected a 2D"):
+        softmax(input_([8]))
+
+
+def test_masked_softmax_takes_segments_as_a_second_input():
+    x, segments = input_([5, 5]), input_([5, 2])
+    c = softmax(x, dict(segments=segments, windowLeft=2, windowRight=0))
+    assert c.shape == meta([5, 5]) and list(c.pending.inputs) == [x, segments]
+    assert list(c.pending.attrs) == [1, 2, 0]
+    _, left, right = softmax(x, dict(segments=segments)).pending.attrs
+    assert math.isfinite(left) and left > 1e9 and right == left
+
+
+@pytest.mark.parametrize("x,segments,opts,error", [
+    ([4, 8], ([4, 2], "f32"), {}, r"needs square scores, got \[4, 8\]"),
+    ([5, 5], ([5], "f32"), {}, r"segments must be f32 \[5, 2\]"),
+    ([5, 5], ([5, 2], "f16"), {}, r"segments must be f32"),
+    ([5, 5], ([5, 2], "f32"), dict(windowLeft=-1),
+     r"windowLeft must be a non-negative integer or Infinity, got -1"),
+    ([5, 5], ([5, 2], "f32"), dict(windowRight=0.5),
+     r"windowRight must be a non-negative integer or Infinity, got 0.5"),
+])
+def test_masked_softmax_rejects(x, segments, opts, error):
+    with pytest.raises(ValueError, match=error):
+        softmax(input_(x), dict(segments=input_(*segments), **opts))

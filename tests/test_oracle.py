@@ -187,3 +187,32 @@ def test_rope_against_numpy(rows, cols, hd, start, width):
                      xs[..., 1] * c[..., 0] + xs[..., 0] * s[..., 0]], -1).reshape(rows, w)
     got = oracle.rope_ref(x, cos, sin, headDim=hd, srcStart=start, width=width)
     assert np.allclose(got, want, rtol=1e-14, atol=1e-14)
+
+
+# ---- softmax ----------------------------------------------------------------------
+
+def test_softmax_matches_the_reference_known_answers():
+    # packages/runntime/test/core/kernels/reduce/softmax.gpu.test.ts:100-122:
+    # [1, 2, 3] -> e^[0, 1, 2] / (1 + e + e^2), the same as torch.softmax; 1000 more
+    # only shifts the max.
+    want = [0.09003057, 0.24472847, 0.66524096]
+    got = oracle.softmax_ref(np.array([[1, 2, 3]], np.float32))
+    assert np.allclose(got[0], want, rtol=1e-6, atol=1e-7)
+    got = oracle.softmax_ref(np.array([[1001, 1002, 1003, -1000]], np.float32))
+    assert np.allclose(got[0], want + [0], rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("n,wl,wr", [(12, math.inf, math.inf), (9, math.inf, 0), (136, 2, 1),
+                                     (12, 0, 0)])
+def test_masked_softmax_against_numpy(n, wl, wr):
+    x = (8 * oracle.random_f32(n * n, 2)).reshape(n, n)
+    half = n // 2
+    segs = np.array([[0, half] if r < half else [half, n] for r in range(n)], np.float32)
+    r, j = np.arange(n)[:, None], np.arange(n)[None, :]
+    keep = (j >= segs[:, :1]) & (j < segs[:, 1:]) & (j >= r - wl) & (j <= r + wr)
+    xs = np.where(keep, x.astype(np.float64), -np.inf)
+    e = np.exp(xs - xs.max(axis=1, keepdims=True))
+    want = e / e.sum(axis=1, keepdims=True)
+    got = oracle.softmax_ref(x, segs, wl, wr)
+    assert np.allclose(got, want, rtol=1e-13, atol=1e-15)
+    assert (got[~keep] == 0).all()
