@@ -254,6 +254,19 @@ RT_API int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* s
                    int64_t rows, int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
                    int32_t dtype);
 
+/* ---- localAttention: short causal window with soft-capped, biased scores -------
+ * qkv [rows, 3*heads*headDim] (columns q|k|v); row t of each head sees keys
+ * t-window+1 .. t (window <= 32).  The score of the key j rows back is
+ * softcap * tanh(sum_d (q_d qScale_d) (k_d kScale + rel[j][h*headDim+d]) / softcap);
+ * rel f32 [window, heads*headDim], qScale f32 [headDim]; softmax over the keys,
+ * weighted sum of the values; out [rows, heads*headDim] in `dtype`.  headDim is
+ * a multiple of 4.  Replaces the 'localAttention' op and attnLocal kernel
+ * (packages/runntime/src/core/graph/ops/attention.ts:255-300;
+ * packages/runntime/src/core/kernels/attention/attnLocal.ts:58-123). */
+RT_API int rt_local_attention(rt_ctx* ctx, const void* qkv, const float* rel, const float* qScale,
+                              void* out, int64_t rows, int32_t heads, int32_t headDim,
+                              int32_t window, float kScale, float softcap, int32_t dtype);
+
 /* ---- softmax: row-wise over the last dim, optionally masked ---------------------
  * out [rows, cols] = softmax of each row of x.  With `segments` (f32 [rows, 2],
  * a [start, end) key range per row) x is square attention scores: row r keeps

@@ -239,6 +239,20 @@ def rope_ref(x, cos, sin, *, headDim, srcStart=0, width=None) -> np.ndarray:
     return out
 
 
+def local_attention_ref(qkv, rel, qScale, *, heads, headDim, window, kScale=1.0,
+                        softcap=50.0) -> np.ndarray:
+    """f64 local attention over qkv [rows, 3*heads*headDim] (f32 values)."""
+    qkv = np.ascontiguousarray(qkv, dtype=np.float32)
+    rel = np.ascontiguousarray(rel, dtype=np.float32)
+    qScale = np.ascontiguousarray(qScale, dtype=np.float32)
+    rows = qkv.shape[0]
+    out = np.empty((rows, heads * headDim), dtype=np.float64)
+    lib().oracle_local_attention_f64(_p(qkv), _p(rel), _p(qScale), C.c_int64(rows),
+                                     C.c_int32(heads), C.c_int32(headDim), C.c_int32(window),
+                                     C.c_double(kScale), C.c_double(softcap), _p(out))
+    return out
+
+
 def softmax_ref(x, segs=None, windowLeft=math.inf, windowRight=math.inf) -> np.ndarray:
     """f64 row softmax of x [rows, cols] (f32 values), masked when ``segs`` is given."""
     x = np.ascontiguousarray(x, dtype=np.float32)

@@ -23,6 +23,8 @@
  *     packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422.
  *   - oracle_rope_f64: the rotary embedding that precedes attention in a decoder
  *     layer (packages/runntime/src/core/kernels/attention/rope.ts:36-70).
+ *   - oracle_local_attention_f64: the short-window soft-capped attention of
+ *     packages/runntime/src/core/kernels/attention/attnLocal.ts:58-123.
  *   - oracle_softmax_f64: the (optionally masked) row softmax of the
  *     matmul-attention path (packages/runntime/src/core/kernels/reduce/softmax.ts:111-186).
  *   - oracle_random_f32 / oracle_round_f16: the reference tests' input
@@ -215,6 +217,46 @@ void oracle_rope_f64(const float* x, const float* cosT, const float* sinT, int64
       const double x0 = x[t * cols + srcStart + col], x1 = x[t * cols + srcStart + col + 1];
       out[t * width + col] = x0 * c - x1 * s;
       out[t * width + col + 1] = x1 * c + x0 * s;
+    }
+  }
+}
+
+/* ---- localAttention ---------------------------------------------------------- */
+
+/* Local attention from its definition, in f64: row t of head h scores the key j
+ * rows back as cap * tanh(sum_d q_d qScale_d (k_d kScale + rel[j][d]) / cap) for
+ * j < min(window, t + 1), softmaxes the scores and sums the values.  Semantics:
+ * packages/runntime/test/core/kernels/attention/attnLocal.gpu.test.ts:24-65. */
+void oracle_local_attention_f64(const float* qkv, const float* rel, const float* qScale,
+                                int64_t rows, int32_t heads, int32_t headDim, int32_t window,
+                                double kScale, double softcap, double* out) {
+  const int64_t width = (int64_t)heads * headDim;
+#pragma omp parallel for schedule(static)
+  for (int64_t t = 0; t < rows; t++) {
+    double scores[64];
+    const int n = (int)(window < t + 1 ? window : t + 1);
+    for (int h = 0; h < heads; h++) {
+      const float* q = qkv + t * 3 * width + (int64_t)h * headDim;
+      double mx = -INFINITY;
+      for (int j = 0; j < n; j++) {
+        const float* k = qkv + (t - j) * 3 * width + width + (int64_t)h * headDim;
+        double s = 0.0;
+        for (int i = 0; i < headDim; i++) {
+          const double key = (double)k[i] * kScale + (double)rel[j * width + h * headDim + i];
+          s += (double)q[i] * (double)qScale[i] * key;
+        }
+        scores[j] = softcap * tanh(s / softcap);
+        if (scores[j] > mx) mx = scores[j];
+      }
+      double sum = 0.0;
+      for (int j = 0; j < n; j++) sum += exp(scores[j] - mx);
+      for (int i = 0; i < headDim; i++) {
+        double acc = 0.0;
+        for (int j = 0; j < n; j++)
+          acc += exp(scores[j] - mx) *
+                 (double)qkv[(t - j) * 3 * width + 2 * width + (int64_t)h * headDim + i];
+        out[t * width + (int64_t)h * headDim + i] = acc / sum;
+      }
     }
   }
 }

@@ -69,6 +69,9 @@ SYMBOLS = {
                                          C.c_void_p, C.c_int32]),
     "rt_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                           C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int32]),
+    "rt_local_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float,
+                                     C.c_float, C.c_int32]),
     "rt_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                              C.c_int32, C.c_int32, C.c_int32]),
     "rt_slice": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,

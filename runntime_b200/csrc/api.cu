@@ -6,6 +6,7 @@
 #include <string>
 #include <vector>
 
+#include <cmath>
 #include "common.cuh"
 
 struct rt_ctx {
@@ -508,6 +509,38 @@ int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, vo
                 (long long)width, headDim);
   RT_CUDA(ctx, rt::launch_rope(x, cosT, sinT, out, rows, cols, headDim, srcStart, width, dtype,
                                ctx->stream));
+  ctx->launches++;
+  return RT_OK;
+}
+
+int rt_local_attention(rt_ctx* ctx, const void* qkv, const float* rel, const float* qScale,
+                       void* out, int64_t rows, int32_t heads, int32_t headDim, int32_t window,
+                       float kScale, float softcap, int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!qkv || !rel || !qScale || !out)
+    return fail(ctx, RT_INVALID_ARGUMENT, "localAttention: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "localAttention: bad dtype %d", dtype);
+  if (rows < 1) return fail(ctx, RT_INVALID_ARGUMENT, "localAttention: empty tensor (%lld rows)",
+                            (long long)rows);
+  if (heads < 1 || headDim < 4 || headDim % 4 != 0)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "localAttention: heads %d must be a positive integer and headDim %d a multiple of 4",
+                heads, headDim);
+  if (window < 1 || window > 32)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "localAttention: window %d must be an integer from 1 to 32", window);
+  if (!(softcap > 0.f) || !std::isfinite(kScale))
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "localAttention: softcap must be positive and kScale finite, got %g, %g",
+                (double)softcap, (double)kScale);
+  const uintptr_t word = 4 * (uintptr_t)elem_size(dtype);
+  if (reinterpret_cast<uintptr_t>(qkv) % word || reinterpret_cast<uintptr_t>(out) % word ||
+      reinterpret_cast<uintptr_t>(rel) % 16 || reinterpret_cast<uintptr_t>(qScale) % 16)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "localAttention: tensors must start on a four-element boundary");
+  RT_CUDA(ctx, rt::launch_local_attn(qkv, rel, qScale, out, rows, heads, headDim, window, kScale,
+                                     softcap, dtype, ctx->stream));
   ctx->launches++;
   return RT_OK;
 }

@@ -162,6 +162,9 @@ cudaError_t launch_merge_partials(const float* partials, int parts, int64_t unit
 cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
                         int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
                         int dtype, cudaStream_t s);
+cudaError_t launch_local_attn(const void* qkv, const float* rel, const float* qScale, void* out,
+                              int64_t rows, int heads, int hd, int window, float kScale,
+                              float softcap, int dtype, cudaStream_t s);
 cudaError_t launch_softmax(const void* x, void* out, const float* segs, int64_t rows, int64_t cols,
                            int64_t wl, int64_t wr, int dtype, cudaStream_t s);
 cudaError_t launch_slice(const void* x, void* out, int64_t rows, int64_t srcColBytes,

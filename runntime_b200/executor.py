@@ -169,6 +169,14 @@ class CudaExecutor:
             self._dispatch_slice(node, inputs, out)
         elif op == "softmax":
             self._dispatch_softmax(node, inputs, out)
+        elif op == "localAttention":
+            heads, hd, window, kScale, softcap = node.pending.attrs
+            check(self._lib.rt_local_attention(
+                self.ctx, C.c_void_p(inputs[0].ptr), C.c_void_p(inputs[1].ptr),
+                C.c_void_p(inputs[2].ptr), C.c_void_p(out.ptr), node.shape.dims[0], int(heads),
+                int(hd), int(window), float(kScale), float(softcap),
+                DTYPE_CODE[node.shape.dtype]), self.ctx)
+            self.dispatches.append("localAttention")
         else:
             raise RunntimeError("INVALID_ARGUMENT", f"dispatch: no kernel for op '{op}'")
 

@@ -210,6 +210,42 @@ def rope(x: Value, cos: Value, sin: Value, opts: dict) -> Value:
                    [int(headDim), int(srcStart), int(w)])
 
 
+ATTN_LOCAL_MAX_WINDOW = 32  # most keys a query of localAttention sees
+
+
+def localAttention(qkv: Value, rel: Value, qScale: Value, opts: dict) -> Value:
+    """Local attention over a fused qkv slab [T, 3*heads*headDim]: row t sees keys
+    t - window + 1 .. t.  The score of the key j rows back is
+    cap * tanh((q * qScale) . (k * kScale + rel[j]) / cap), with rel
+    [window, heads*headDim] one f32 bias row per distance and qScale [headDim]
+    f32 per column of q.  Returns [T, heads*headDim]
+    (packages/runntime/src/core/graph/ops/attention.ts:255-300)."""
+    heads, headDim, window = opts["heads"], opts["headDim"], opts["window"]
+    kScale, softcap = opts["kScale"], opts["softcap"]
+    t, w, dtype = want2d("localAttention", qkv, FLOAT_DTYPES)
+    if not _is_int(heads) or heads < 1 or not _is_int(headDim) or headDim % 4 != 0:
+        raise ValueError(f"localAttention: heads {_js(heads)} must be a positive integer and "
+                         f"headDim {_js(headDim)} a multiple of 4")
+    heads, headDim = int(heads), int(headDim)
+    width = heads * headDim
+    if w != 3 * width:
+        raise ValueError(
+            f"localAttention: qkv must have 3·heads·headDim = {3 * width} cols, got {w}")
+    if not _is_int(window) or window < 1 or window > ATTN_LOCAL_MAX_WINDOW:
+        raise ValueError(f"localAttention: window {_js(window)} must be an integer from 1 to "
+                         f"{ATTN_LOCAL_MAX_WINDOW}")
+    window = int(window)
+    if rel.shape.dtype != "f32" or rel.shape.elems != window * width:
+        raise ValueError(f"localAttention: rel must be f32 [{window}, {width}]")
+    if qScale.shape.dtype != "f32" or qScale.shape.elems != headDim:
+        raise ValueError(f"localAttention: qScale must be f32 [{headDim}]")
+    if not (softcap > 0) or not math.isfinite(kScale):
+        raise ValueError("localAttention: softcap must be positive and kScale finite, got "
+                         f"{_js(softcap)}, {_js(kScale)}")
+    return pending(ValueMeta(t * width, dtype, (t, width)), "localAttention", [qkv, rel, qScale],
+                   None, [heads, headDim, window, kScale, softcap])
+
+
 def softmax(x: Value, opts: Optional[dict] = None) -> Value:
     """Row-wise softmax over the last dim.  With ``segments`` ([M, 2] f32, a
     [start, end) range per row) x is MxM attention scores: row r keeps the keys in

@@ -117,3 +117,32 @@ def test_n_of_1_inputs_at_long_sequence_keep_the_tolerance(ex):
     want = oracle.sdpa_ref(q, k, v, qHeads=1, kvHeads=1, headDim=hd, windowRight=0,
                            qPosOffset=T - 256)
     assert np.abs(out.reshape(want.shape) - want).max() <= 2e-3
+
+
+@pytest.mark.parametrize("hd,heads,kvHeads,wl,wr,packed", [
+    (256, 3, 1, 512, 512, False),    # EmbeddingGemma sliding layer
+    (256, 3, 1, INF, INF, False),    # EmbeddingGemma global layer
+    (64, 4, 4, INF, INF, True),      # a packed bidirectional encoder batch
+    (128, 8, 8, INF, 0, True),
+])
+def test_greedy_packed_batch_of_ragged_sequences(ex, hd, heads, kvHeads, wl, wr, packed):
+    """Sequences of unequal length packed back to back, a [start, end) range per
+    row, T rounded up with rows that keep nothing — the batch the embedders build
+    (packages/runntime/src/zoo/embeddinggemma2/embedCore.ts:43-73,131-134) — on
+    the tensor-core kernel: row tiles straddle several sequences."""
+    lens = [37, 300, 5, 130, 1, 263, 128, 129]
+    T = (sum(lens) + 3) // 4 * 4 + 4          # padded rows at the end
+    c = _c(qLen=T, kvLen=T, qHeads=heads, kvHeads=kvHeads, headDim=hd, windowLeft=wl,
+           windowRight=wr, segments=True, packed=packed, maxSegment=max(lens))
+    x = make_inputs(c, "f16")
+    segs = np.zeros((T, 2), np.float32)
+    at = 0
+    for n in lens:
+        segs[at:at + n] = (at, at + n)
+        at += n
+    x.segs = segs
+    got = run_sdpa(ex, x)
+    assert ex.dispatches[-1] == "prefill_tc"
+    want = oracle.sdpa_ref_inputs(x)
+    oracle.assert_close(got, want, "f16")
+    assert (got.reshape(T, -1)[at:] == 0).all()

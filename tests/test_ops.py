@@ -320,3 +320,33 @@ def test_masked_softmax_takes_segments_as_a_second_input():
 def test_masked_softmax_rejects(x, segments, opts, error):
     with pytest.raises(ValueError, match=error):
         softmax(input_(x), dict(segments=input_(*segments), **opts))
+
+
+# ---- localAttention (packages/runntime/test/core/graph/ops/attention.test.ts:291-332) ----
+
+from runntime_b200 import localAttention  # noqa: E402
+
+LOCAL = dict(heads=2, headDim=HD, window=3, kScale=1, softcap=50)
+
+
+def test_local_attention_gives_one_row_of_heads_times_head_dim():
+    c = localAttention(input_([5, 48]), input_([3, 16]), input_([HD]), LOCAL)
+    assert c.shape == meta([5, 16]) and c.pending.op == "localAttention"
+    assert list(c.pending.attrs) == [2, HD, 3, 1, 50]
+
+
+@pytest.mark.parametrize("over,error", [
+    (dict(qkv=([5, 40],)), r"48 cols, got 40"),
+    (dict(rel=([4, 16],)), r"rel must be f32 \[3, 16\]"),
+    (dict(rel=([3, 16], "f16")), r"rel must be f32"),
+    (dict(qScale=([4],)), r"qScale must be f32 \[8\]"),
+    (dict(opts=dict(window=33)), r"window 33 must be an integer from 1 to 32"),
+    (dict(opts=dict(headDim=6)), r"headDim 6 a multiple of 4"),
+    (dict(opts=dict(softcap=0)), r"softcap must be positive"),
+])
+def test_local_attention_rejects(over, error):
+    qkv = input_(*over.get("qkv", ([5, 48],)))
+    rel = input_(*over.get("rel", ([3, 16],)))
+    qScale = input_(*over.get("qScale", ([HD],)))
+    with pytest.raises(ValueError, match=error):
+        localAttention(qkv, rel, qScale, dict(LOCAL, **over.get("opts", {})))

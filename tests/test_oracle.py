@@ -216,3 +216,51 @@ def test_masked_softmax_against_numpy(n, wl, wr):
     got = oracle.softmax_ref(x, segs, wl, wr)
     assert np.allclose(got, want, rtol=1e-13, atol=1e-15)
     assert (got[~keep] == 0).all()
+
+
+# ---- localAttention -----------------------------------------------------------------
+
+def _local_numpy(qkv, rel, qScale, heads, hd, window, kScale, softcap):
+    """Independent numpy restatement: banded scores from full matrices."""
+    rows, width = qkv.shape[0], heads * hd
+    x = qkv.astype(np.float64)
+    out = np.zeros((rows, width))
+    for h in range(heads):
+        q = x[:, h * hd:(h + 1) * hd] * qScale.astype(np.float64)
+        k = x[:, width + h * hd:width + (h + 1) * hd] * kScale
+        v = x[:, 2 * width + h * hd:2 * width + (h + 1) * hd]
+        s = np.full((rows, rows), -np.inf)
+        for j in range(window):
+            r = rel[j, h * hd:(h + 1) * hd].astype(np.float64)
+            t = np.arange(j, rows)
+            s[t, t - j] = np.einsum("td,td->t", q[t], k[t - j] + r)
+        s = softcap * np.tanh(s / softcap)
+        s[np.isnan(s)] = -np.inf
+        band = np.tril(np.ones((rows, rows), bool)) & ~np.tril(np.ones((rows, rows), bool), -window)
+        s = np.where(band, s, -np.inf)
+        e = np.exp(s - s.max(axis=1, keepdims=True))
+        out[:, h * hd:(h + 1) * hd] = (e / e.sum(axis=1, keepdims=True)) @ v
+    return out
+
+
+@pytest.mark.parametrize("rows,heads,hd,window,kScale,softcap", [
+    (50, 8, 128, 12, math.log1p(math.e) / math.log(2), 50), (6, 2, 8, 1, 1, 50),
+    (40, 2, 16, 32, 1, 50), (3, 2, 8, 12, 1, 50), (16, 2, 32, 6, 4, 0.5), (10, 2, 8, 3, -1.5, 50)])
+def test_local_attention_against_numpy(rows, heads, hd, window, kScale, softcap):
+    width = heads * hd
+    qkv = oracle.random_f32(rows * 3 * width, 1).reshape(rows, 3 * width)
+    rel = oracle.random_f32(window * width, 2).reshape(window, width)
+    qScale = oracle.random_f32(hd, 3)
+    got = oracle.local_attention_ref(qkv, rel, qScale, heads=heads, headDim=hd, window=window,
+                                     kScale=kScale, softcap=softcap)
+    want = _local_numpy(qkv, rel, qScale, heads, hd, window, kScale, softcap)
+    assert np.allclose(got, want, rtol=1e-11, atol=1e-13)
+
+
+def test_local_attention_window_one_returns_v():
+    rows, heads, hd = 6, 2, 8
+    width = heads * hd
+    qkv = oracle.random_f32(rows * 3 * width, 1).reshape(rows, 3 * width)
+    got = oracle.local_attention_ref(qkv, np.zeros((1, width), np.float32),
+                                     np.ones(hd, np.float32), heads=heads, headDim=hd, window=1)
+    assert np.array_equal(got, qkv[:, 2 * width:].astype(np.float64))
