@@ -66,8 +66,10 @@ RT_API int rt_ctx_destroy(rt_ctx* ctx);
  * restores the context's stream. */
 RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
 /* Context options.  RT_OPT_PREFILL_TC (default 1): route eligible f16 prefill
- * shapes to the tensor-core kernel; 0 sends every prefill to the FP32-pipe
- * kernel (both compute the same op; the switch exists for testing). */
+ * shapes to a tensor-core kernel, the library choosing between its two (one or
+ * two 128-row query tiles per thread block); 0 sends every prefill to the
+ * FP32-pipe kernel, 2 forces one tile, 3 forces two tiles where that kernel
+ * applies (all compute the same op; the switch exists for testing). */
 #define RT_OPT_PREFILL_TC 1
 RT_API int rt_ctx_set_option(rt_ctx* ctx, int option, int value);
 /* Message of the last failure on this context (or, with ctx == NULL, of the

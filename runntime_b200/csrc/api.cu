@@ -28,6 +28,9 @@ struct rt_ctx {
 namespace {
 
 constexpr uint32_t kLive = 0x52544358u;  // 'RTCX'
+// Whether the default routing (RT_OPT_PREFILL_TC = 1) takes the two-tile kernel
+// where it applies.
+constexpr bool kPreferTwoTiles = true;
 constexpr uint32_t kDead = 0x44454144u;  // 'DEAD'
 
 thread_local std::string tlsError;
@@ -304,7 +307,10 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
 int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
   RT_ENTER(ctx);
   if (option == RT_OPT_PREFILL_TC) {
-    ctx->useTc = value != 0;
+    if (value < 0 || value > 3)
+      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..3, got %d",
+                  value);
+    ctx->useTc = value;
     return RT_OK;
   }
   return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: unknown option %d", option);
@@ -367,10 +373,19 @@ int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* ho
   return rt_sync(ctx);
 }
 
+// 0 = FP32-pipe kernel, 1 = tensor cores, one query tile per CTA, 2 = two tiles per CTA.
+static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dtype) {
+  if (!ctx->useTc || !rt::prefill_tc_supported(p, dtype)) return 0;
+  if (ctx->useTc != 2 && rt::prefill_tc2_supported(p, dtype) &&
+      (ctx->useTc == 3 || kPreferTwoTiles))
+    return 2;
+  return 1;
+}
+
 static const char* route_of(const rt_ctx* ctx, const rt_attn_args* a) {
   if (a->qLen == 1) return "decode";
-  return (ctx->useTc && rt::prefill_tc_supported(to_params(a), a->dtype)) ? "prefill_tc"
-                                                                          : "prefill_simt";
+  const int k = prefill_kernel_of(ctx, to_params(a), a->dtype);
+  return k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
 }
 
 int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
@@ -408,9 +423,12 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
     return run_decode(ctx, p, a->dtype);
   }
   const rt::AttnParams p = to_params(a);
-  if (ctx->useTc && rt::prefill_tc_supported(p, a->dtype)) {
+  const int kernel = prefill_kernel_of(ctx, p, a->dtype);
+  if (kernel != 0) {
     std::string err;
-    cudaError_t e = rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
+    cudaError_t e = kernel == 2
+                        ? rt::launch_prefill_tc2(p, ctx->statusDev, ctx->stream, &err)
+                        : rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
     if (e != cudaSuccess)
       return fail(ctx, RT_EXECUTION_FAILED, "prefill_tc launch: %s %s", cudaGetErrorString(e),
                   err.c_str());

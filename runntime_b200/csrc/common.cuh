@@ -154,6 +154,9 @@ cudaError_t launch_prefill_simt(const AttnParams& p, int dtype, cudaStream_t s);
 bool prefill_tc_supported(const AttnParams& p, int dtype);
 cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaStream_t s,
                               std::string* err);
+// Two query tiles per CTA (head sizes 64 and 128, more than 128 query rows).
+bool prefill_tc2_supported(const AttnParams& p, int dtype);
+cudaError_t launch_prefill_tc2(const AttnParams& p, int* status, cudaStream_t s, std::string* err);
 // Fills kvPerCta/keySlots/stages/splits; returns false with a message when the shape cannot run.
 bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);

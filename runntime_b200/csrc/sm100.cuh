@@ -62,6 +62,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// The same wait for warps that are not on the critical path: sleeps between polls,
+// so that many waiting warps do not crowd the instruction issue and the barrier
+// unit of a sub-partition that also holds the thread issuing the tensor-core work.
+template <int SLEEP_NS>
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  volatile int* abortFlag) {
+  for (uint32_t i = 0; i < kWaitLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(SLEEP_NS);
+    if ((i & 31u) == 31u && *abortFlag) return false;
+  }
+  *abortFlag = 1;
+  return false;
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
@@ -131,6 +146,20 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    bar)
                : "memory");
+}
+// True in exactly one lane of a converged warp.  Unlike a test of the lane index
+// it leaves the surrounding code warp-uniform for the compiler, so operands of
+// the tensor-core instructions issued under it (descriptors, TMEM addresses) stay
+// in uniform registers instead of being moved there one by one in a divergent
+// branch — which costs the issuing thread more time than the MMA takes to run.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+      "elect.sync rx|px, 0xffffffff;\n\t"
+      "@px mov.s32 %0, 1;\n\t}"
+      : "+r"(pred));
+  return pred != 0;
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc], f16 inputs, f32 accumulate.
 __device__ __forceinline__ void mma_f16_ss(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc,

@@ -54,17 +54,34 @@ TC_CASES = [
 ]
 
 
+@pytest.fixture
+def one_tile(ex):
+    """The kernel with one 128-row query tile per thread block, for every shape."""
+    from runntime_b200._lib import OPT_PREFILL_TC
+    ex.setOption(OPT_PREFILL_TC, 2)
+    yield ex
+    ex.setOption(OPT_PREFILL_TC, 1)
+
+
 @pytest.mark.parametrize("name,c", TC_CASES, ids=[n for n, _ in TC_CASES])
-def test_tensor_core_prefill_against_oracle(ex, name, c):
-    check_sdpa(ex, c, "f16", route="prefill_tc")
+def test_tensor_core_prefill_against_oracle(one_tile, name, c):
+    check_sdpa(one_tile, c, "f16", route="prefill_tc")
+
+
+def test_default_routing_between_the_two_tensor_core_kernels(ex):
+    big = _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=1, headDim=128, windowRight=0)
+    check_sdpa(ex, big, "f16", route="prefill_tc2")
+    check_sdpa(ex, big.with_(headDim=64), "f16", route="prefill_tc2")
+    check_sdpa(ex, big.with_(headDim=256), "f16", route="prefill_tc")       # needs all of TMEM for one tile
+    check_sdpa(ex, big.with_(qLen=128, windowRight=INF), "f16", route="prefill_tc")  # a single tile of rows
 
 
 @pytest.mark.parametrize("hd", [64, 128, 256])
-def test_every_option_takes_the_tensor_core_route(ex, hd):
+def test_every_option_takes_the_tensor_core_route(one_tile, hd):
     for name, c in cases.option_cases(300, hd):
         if c.packed and hd > 128:
             continue
-        check_sdpa(ex, c, "f16", route="prefill_tc")
+        check_sdpa(one_tile, c, "f16", route="prefill_tc")
 
 
 def test_matches_the_fp32_pipe_kernel(ex):
@@ -73,7 +90,14 @@ def test_matches_the_fp32_pipe_kernel(ex):
            sinks=True)
     x = make_inputs(c, "f16")
     tc = run_sdpa(ex, x)
-    assert ex.dispatches[-1] == "prefill_tc"
+    assert ex.dispatches[-1] == "prefill_tc2"
+    ex.setOption(OPT_PREFILL_TC, 2)
+    try:
+        one = run_sdpa(ex, x)
+        assert ex.dispatches[-1] == "prefill_tc"
+    finally:
+        ex.setOption(OPT_PREFILL_TC, 1)
+    assert np.abs(tc - one).max() < 1e-3
     ex.setOption(OPT_PREFILL_TC, 0)
     try:
         simt = run_sdpa(ex, x)
@@ -95,7 +119,7 @@ def test_large_scores_need_the_rescale_path(ex):
     opts = dict(qHeads=1, kvHeads=1, headDim=hd, windowLeft=INF, windowRight=INF)
     out = rt.toArray(rt.sdpa(ex.upload(q, [T, hd], "f16"), ex.upload(k, [T, hd], "f16"),
                              ex.upload(v, [T, hd], "f16"), opts), ex)
-    assert ex.dispatches[-1] == "prefill_tc"
+    assert ex.dispatches[-1] == "prefill_tc2"
     want = oracle.sdpa_ref(q, k, v, qHeads=1, kvHeads=1, headDim=hd)
     oracle.assert_close(out, want, "f16")
 
@@ -142,7 +166,46 @@ def test_greedy_packed_batch_of_ragged_sequences(ex, hd, heads, kvHeads, wl, wr,
         at += n
     x.segs = segs
     got = run_sdpa(ex, x)
-    assert ex.dispatches[-1] == "prefill_tc"
+    assert ex.dispatches[-1] == ("prefill_tc" if hd == 256 else "prefill_tc2")
     want = oracle.sdpa_ref_inputs(x)
     oracle.assert_close(got, want, "f16")
     assert (got.reshape(T, -1)[at:] == 0).all()
+
+
+# ---- two query tiles per thread block (head sizes 64 and 128) ----------------------
+
+@pytest.fixture
+def two_tiles(ex):
+    from runntime_b200._lib import OPT_PREFILL_TC
+    ex.setOption(OPT_PREFILL_TC, 3)
+    yield ex
+    ex.setOption(OPT_PREFILL_TC, 1)
+
+
+def _two_tile_ok(c):
+    return c.headDim in (64, 128) and c.qLen > 128
+
+
+TWO_TILE_CASES = [(n, c) for n, c in TC_CASES if _two_tile_ok(c)] + [
+    ("causal_odd_rows", _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=1, headDim=128, windowRight=0)),
+    ("second_tile_partly_past_the_end", _c(qLen=300, kvLen=300, qHeads=1, kvHeads=1, headDim=64,
+                                           windowRight=0)),
+    ("second_tile_empty_band", _c(qLen=256, kvLen=100, qHeads=1, kvHeads=1, headDim=64,
+                                  windowLeft=0, windowRight=INF, qPosOffset=0)),
+    ("cross_long_keys", _c(qLen=257, kvLen=3000, qHeads=4, kvHeads=2, headDim=128)),
+    ("sliding_window_gqa_sinks", _c(qLen=1500, kvLen=1500, qHeads=6, kvHeads=2, headDim=64,
+                                    windowLeft=200, windowRight=0, sinks=True)),
+    ("decode_chunk_offset", _c(qLen=384, kvLen=2048, qHeads=2, kvHeads=2, headDim=128,
+                               windowRight=0, qPosOffset=1664)),
+]
+
+
+@pytest.mark.parametrize("name,c", TWO_TILE_CASES, ids=[n for n, _ in TWO_TILE_CASES])
+def test_two_tile_kernel_against_oracle(two_tiles, name, c):
+    check_sdpa(two_tiles, c, "f16", route="prefill_tc2")
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_every_option_on_the_two_tile_kernel(two_tiles, hd):
+    for name, c in cases.option_cases(300, hd):
+        check_sdpa(two_tiles, c, "f16", route="prefill_tc2")
