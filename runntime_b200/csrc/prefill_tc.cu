@@ -317,14 +317,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
         TC_TRACE(2, j);
         const bool fullTile = lo <= key0 && end >= key0 + CW - 1;
-        if (!fullTile || p.hasKeyBias) {
+        if (p.hasKeyBias) {
+          // columns [b0, b1) of this tile get the bias (select, no branch per element)
+          const int b0 = p.biasStart - key0, b1 = p.biasEnd - key0;
 #pragma unroll
           for (int c = 0; c < CW; c++) {
-            const int jj = key0 + c;
-            float s = __uint_as_float(sv[c]);
-            if (p.hasKeyBias && jj >= p.biasStart && jj < p.biasEnd) s += p.biasValue;
-            sv[c] = __float_as_uint((jj >= lo && jj <= end) ? s : -INFINITY);
+            const float s = __uint_as_float(sv[c]);
+            sv[c] = __float_as_uint((c >= b0 && c < b1) ? s + p.biasValue : s);
           }
+        }
+        if (!fullTile) {
+          // visible columns of this row are the interval [c0, c0 + span]; one unsigned
+          // compare and one select per score
+          const int c0 = lo <= end ? lo - key0 : (1 << 30);  // a row that sees nothing: no column passes
+          const unsigned span = lo <= end ? (unsigned)(end - lo) : 0u;
+#pragma unroll
+          for (int c = 0; c < CW; c++)
+            sv[c] = ((unsigned)(c - c0) <= span) ? sv[c] : 0xff800000u;  // -inf
         }
         // Row max with four independent chains of 3-input max.
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};

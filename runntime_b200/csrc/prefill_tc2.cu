@@ -31,9 +31,6 @@ using namespace tc;
 #ifndef RT_TC2_STAGGER_NS
 #define RT_TC2_STAGGER_NS 1000
 #endif
-#ifndef RT_TC2_SLEEP
-#define RT_TC2_SLEEP 40
-#endif
 constexpr int kThreads2 = 384;
 #ifndef RT_TC2_REGS_SOFTMAX
 #define RT_TC2_REGS_SOFTMAX 216
@@ -321,33 +318,46 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       tmem_wait_ld();
       TC_TRACE(2, i);
       const bool fullTile = lo <= key0 && end >= key0 + BK - 1;
-      if (!fullTile || p.hasKeyBias) {
+      if (p.hasKeyBias) {
+        // columns [b0, b1) of this tile get the bias (select, no branch per element)
+        const int b0 = p.biasStart - key0, b1 = p.biasEnd - key0;
 #pragma unroll
         for (int c = 0; c < BK; c++) {
-          const int jj = key0 + c;
-          float s = __uint_as_float(sv[c]);
-          if (p.hasKeyBias && jj >= p.biasStart && jj < p.biasEnd) s += p.biasValue;
-          sv[c] = __float_as_uint((jj >= lo && jj <= end) ? s : -INFINITY);
+          const float s = __uint_as_float(sv[c]);
+          sv[c] = __float_as_uint((c >= b0 && c < b1) ? s + p.biasValue : s);
         }
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (!fullTile) {
+        // visible columns of this row are the interval [c0, c0 + span]; one unsigned
+        // compare and one select per score
+        const int c0 = lo <= end ? lo - key0 : (1 << 30);  // a row that sees nothing: no column passes
+        const unsigned span = lo <= end ? (unsigned)(end - lo) : 0u;
 #pragma unroll
-      for (int c = 0; c < BK; c += 8) {
+        for (int c = 0; c < BK; c++)
+          sv[c] = ((unsigned)(c - c0) <= span) ? sv[c] : 0xff800000u;  // -inf
+      }
+      TC_TRACE(6, i);
+      // Row maximum (four independent chains of 3-input max), folded into whichever
+      // loop runs first.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      auto foldMax = [&](int c) {  // columns c .. c+7
 #pragma unroll
         for (int u = 0; u < 4; u++)
           mx4[u] = max3(mx4[u], __uint_as_float(sv[c + 2 * u]), __uint_as_float(sv[c + 2 * u + 1]));
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
-      const bool grow = mx > mref + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, grow)) {
+      };
+      // Lazy rescale: the reference point mref moves only when some row's maximum
+      // grew by more than 2^8 (whole warp together, because TMEM loads and stores are
+      // warp-collective).  O holds the tiles up to i-1; their P V products were issued,
+      // by the same thread, before S(i), whose completion this warp has already seen:
+      // they are done, and the accumulator can be scaled in place.
+      auto rescale = [&]() {
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
+        if (!__any_sync(0xffffffffu, mx > mref + kRescaleThreshold)) return false;
         const float mnew = fmaxf(mref, mx);
         const float f = fast_exp2(mref - mnew);
         mref = mnew;
         l *= f;
         if (i > 0) {
-          // O holds the tiles up to i-1.  Their P V products were issued, by the same
-          // thread, before S(i), whose completion this warp has already seen: they are
-          // done, and the accumulator can be scaled in place.
 #pragma unroll
           for (int c = 0; c < HD; c += 32) {
             uint32_t o[32];
@@ -358,37 +368,62 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             tmem_st32(oCol + c, o);
           }
         }
-      }
-      TC_TRACE(3, i);
-      const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mref, -mref);
-      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
-                        make_float2(0.f, 0.f)};
-      // Two halves of 64 scores: the packed P of a half goes to TMEM before the
-      // next half is computed, which keeps the live registers under the budget.
-#pragma unroll
-      for (int half = 0; half < 2; half++) {
-        uint32_t pk[32];
+        return true;
+      };
+      float2 sum2[4];
+      uint32_t pk[32];
+      // p = 2^(s*log2e - mref) for 64 scores: one packed FFMA per two scores, MUFU,
+      // four independent packed sums, packed to f16 pairs.  With `withMax` the row
+      // maximum over all 128 scores is gathered in the same loop, where its
+      // instructions hide under the special-function unit's.
+      auto expHalf = [&](int half, bool withMax) {
+        const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mref, -mref);
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
           const int cc = half * 64 + c;
           const float2 t = fma2(make_float2(__uint_as_float(sv[cc]), __uint_as_float(sv[cc + 1])),
                                 scale2, shift2);
-#ifdef RT_TC2_STUB_EXP
-          const float2 pe = t;
-#else
           const float2 pe = exp2_pair(t, c >> 1);
-#endif
           sum2[(c >> 1) & 3] = add2(sum2[(c >> 1) & 3], pe);
           const __half2 hp = __floats2half2_rn(pe.x, pe.y);
           pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          if (withMax && (c & 3) == 0) foldMax(2 * c);  // 16 steps x 8 columns = all 128
         }
+      };
+      auto publish = [&](int half) {
         tmem_st32(sCol + half * 32, pk);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars.pReady[q][half]));
         TC_TRACE(4 + half, i);
+      };
+      auto clearSums = [&]() {
+#pragma unroll
+        for (int u = 0; u < 4; u++) sum2[u] = make_float2(0.f, 0.f);
+      };
+      clearSums();
+      if (i == 0) {
+        // First tile: there is no reference point yet, the maximum comes first.
+#pragma unroll
+        for (int c = 0; c < BK; c += 8) foldMax(c);
+        rescale();
+        TC_TRACE(3, i);
+        expHalf(0, false);
+      } else {
+        // Later tiles: start the exponentials against the current reference point
+        // at once; the maximum is rarely 2^8 above it, and when it is the half is
+        // simply computed again.
+        TC_TRACE(3, i);
+        expHalf(0, true);
+        if (rescale()) {
+          clearSums();
+          expHalf(0, false);
+        }
       }
+      publish(0);
+      expHalf(1, false);
+      publish(1);
       const float2 s01 = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
       l += s01.x + s01.y;
     }

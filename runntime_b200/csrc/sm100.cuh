@@ -62,21 +62,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
-// The same wait for warps that are not on the critical path: sleeps between polls,
-// so that many waiting warps do not crowd the instruction issue and the barrier
-// unit of a sub-partition that also holds the thread issuing the tensor-core work.
-template <int SLEEP_NS>
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
-                                                  volatile int* abortFlag) {
-  for (uint32_t i = 0; i < kWaitLimit; i++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(SLEEP_NS);
-    if ((i & 31u) == 31u && *abortFlag) return false;
-  }
-  *abortFlag = 1;
-  return false;
-}
-
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
