@@ -28,9 +28,11 @@ struct rt_ctx {
 namespace {
 
 constexpr uint32_t kLive = 0x52544358u;  // 'RTCX'
-// Whether the default routing (RT_OPT_PREFILL_TC = 1) takes the two-tile kernel
-// where it applies.
-constexpr bool kPreferTwoTiles = true;
+// The default routing (RT_OPT_PREFILL_TC = 1) takes the two-tile kernel once the
+// grid has this many thread blocks per SM: it runs half as many, twice as long
+// blocks, so on a small grid the last, partly filled wave costs more than the
+// faster steady state gains (measured: 512 blocks on 148 SMs lose, 16384 win).
+constexpr int64_t kTwoTileBlocksPerSm = 6;
 constexpr uint32_t kDead = 0x44454144u;  // 'DEAD'
 
 thread_local std::string tlsError;
@@ -376,9 +378,10 @@ int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* ho
 // 0 = FP32-pipe kernel, 1 = tensor cores, one query tile per CTA, 2 = two tiles per CTA.
 static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dtype) {
   if (!ctx->useTc || !rt::prefill_tc_supported(p, dtype)) return 0;
-  if (ctx->useTc != 2 && rt::prefill_tc2_supported(p, dtype) &&
-      (ctx->useTc == 3 || kPreferTwoTiles))
-    return 2;
+  if (ctx->useTc != 2 && rt::prefill_tc2_supported(p, dtype)) {
+    const int64_t blocks = (p.qLen + 255) / 256 * p.qHeads;
+    if (ctx->useTc == 3 || blocks >= kTwoTileBlocksPerSm * ctx->smCount) return 2;
+  }
   return 1;
 }
 

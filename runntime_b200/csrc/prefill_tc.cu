@@ -32,9 +32,12 @@
 // memory for an SS-form P V (the stores and the proxy fence cost more than the
 // faster MMA gains); two threads per row (the special-function unit, 16 ex2 per
 // clock per SM, is the shared limit and the per-tile exchange of row maxima keeps
-// both halves' ex2 phases in lockstep); two query tiles per CTA; evaluating part
-// of the exponentials by polynomial on the FMA pipe (more issue slots than the
-// MUFU cycles it frees; RT_POLY_NUM in tc_common.cuh, default 0).
+// both halves' ex2 phases in lockstep); evaluating part of the exponentials by
+// polynomial on the FMA pipe (more issue slots than the MUFU cycles it frees;
+// RT_POLY_NUM in tc_common.cuh, default 0).  Two query tiles per CTA is faster on
+// large grids at head sizes 64 and 128 and lives in prefill_tc2.cu; this kernel
+// keeps head size 256 (its accumulator leaves no tensor memory for a second tile)
+// and small grids.
 //
 // Every wait is bounded (sm100.cuh); a wait that runs out sets the status word
 // and the CTA winds down through the common exit that frees its tensor memory.

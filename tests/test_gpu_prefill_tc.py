@@ -69,11 +69,14 @@ def test_tensor_core_prefill_against_oracle(one_tile, name, c):
 
 
 def test_default_routing_between_the_two_tensor_core_kernels(ex):
-    big = _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=1, headDim=128, windowRight=0)
+    """Two query tiles per block only on grids of several waves (6 blocks per SM)."""
+    small = _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=1, headDim=128, windowRight=0)
+    check_sdpa(ex, small, "f16", route="prefill_tc")
+    # 9 row pairs x 128 heads = 1152 blocks >= 6 x 148
+    big = _c(qLen=2304, kvLen=2304, qHeads=128, kvHeads=8, headDim=64, windowLeft=64, windowRight=0)
     check_sdpa(ex, big, "f16", route="prefill_tc2")
-    check_sdpa(ex, big.with_(headDim=64), "f16", route="prefill_tc2")
-    check_sdpa(ex, big.with_(headDim=256), "f16", route="prefill_tc")       # needs all of TMEM for one tile
-    check_sdpa(ex, big.with_(qLen=128, windowRight=INF), "f16", route="prefill_tc")  # a single tile of rows
+    check_sdpa(ex, big.with_(headDim=256, qHeads=32, kvHeads=8, qLen=512, kvLen=512), "f16",
+               route="prefill_tc")       # head size 256 needs all of TMEM for one tile
 
 
 @pytest.mark.parametrize("hd", [64, 128, 256])
@@ -90,14 +93,14 @@ def test_matches_the_fp32_pipe_kernel(ex):
            sinks=True)
     x = make_inputs(c, "f16")
     tc = run_sdpa(ex, x)
-    assert ex.dispatches[-1] == "prefill_tc2"
-    ex.setOption(OPT_PREFILL_TC, 2)
+    assert ex.dispatches[-1] == "prefill_tc"
+    ex.setOption(OPT_PREFILL_TC, 3)
     try:
-        one = run_sdpa(ex, x)
-        assert ex.dispatches[-1] == "prefill_tc"
+        two = run_sdpa(ex, x)
+        assert ex.dispatches[-1] == "prefill_tc2"
     finally:
         ex.setOption(OPT_PREFILL_TC, 1)
-    assert np.abs(tc - one).max() < 1e-3
+    assert np.abs(tc - two).max() < 1e-3
     ex.setOption(OPT_PREFILL_TC, 0)
     try:
         simt = run_sdpa(ex, x)
@@ -107,9 +110,12 @@ def test_matches_the_fp32_pipe_kernel(ex):
     assert np.abs(tc - simt).max() < 2e-3
 
 
-def test_large_scores_need_the_rescale_path(ex):
-    """Scores that keep growing along the keys force repeated accumulator rescales."""
+@pytest.mark.parametrize("mode,route", [(2, "prefill_tc"), (3, "prefill_tc2")])
+def test_large_scores_need_the_rescale_path(ex, mode, route):
+    """Scores that keep growing along the keys force repeated accumulator rescales
+    (in the two-tile kernel: every tile's first half is computed twice)."""
     import runntime_b200 as rt
+    from runntime_b200._lib import OPT_PREFILL_TC
     T, hd = 640, 64
     rng = np.random.default_rng(1)
     q = np.ones((T, hd), np.float32) * 0.25
@@ -117,9 +123,13 @@ def test_large_scores_need_the_rescale_path(ex):
     k = oracle.round_f16(k.astype(np.float32))
     v = oracle.round_f16(rng.standard_normal((T, hd)).astype(np.float32))
     opts = dict(qHeads=1, kvHeads=1, headDim=hd, windowLeft=INF, windowRight=INF)
-    out = rt.toArray(rt.sdpa(ex.upload(q, [T, hd], "f16"), ex.upload(k, [T, hd], "f16"),
-                             ex.upload(v, [T, hd], "f16"), opts), ex)
-    assert ex.dispatches[-1] == "prefill_tc2"
+    ex.setOption(OPT_PREFILL_TC, mode)
+    try:
+        out = rt.toArray(rt.sdpa(ex.upload(q, [T, hd], "f16"), ex.upload(k, [T, hd], "f16"),
+                                 ex.upload(v, [T, hd], "f16"), opts), ex)
+    finally:
+        ex.setOption(OPT_PREFILL_TC, 1)
+    assert ex.dispatches[-1] == route
     want = oracle.sdpa_ref(q, k, v, qHeads=1, kvHeads=1, headDim=hd)
     oracle.assert_close(out, want, "f16")
 
@@ -166,7 +176,7 @@ def test_greedy_packed_batch_of_ragged_sequences(ex, hd, heads, kvHeads, wl, wr,
         at += n
     x.segs = segs
     got = run_sdpa(ex, x)
-    assert ex.dispatches[-1] == ("prefill_tc" if hd == 256 else "prefill_tc2")
+    assert ex.dispatches[-1] == "prefill_tc"
     want = oracle.sdpa_ref_inputs(x)
     oracle.assert_close(got, want, "f16")
     assert (got.reshape(T, -1)[at:] == 0).all()
