@@ -2,6 +2,7 @@
 """Benchmark of the attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c4|c3|c2|c1]
+    python bench.py --workload rope|softmax|local|step   # the operators beside attention
     python bench.py --impl reference ...        # the CPU restatement, host cores
 
 One JSON line on stdout (rank 0).  The default workload is the large causal
@@ -613,12 +614,170 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------
+# the operators either side of attention: rope, masked softmax, localAttention and the
+# fused decoder-layer step (HBM- or latency-bound; one GPU, replicas if more)
+# ----------------------------------------------------------------------------
+
+AUX = {
+    "rope": dict(name="rope_f16_65536x4096_hd128", rows=65536, cols=4096, hd=128),
+    "softmax": dict(name="masked_softmax_f16_16384x16384_causal_2_segments", n=16384),
+    "local": dict(name="local_attention_f16_T262144_8x128_window12", rows=262144, heads=8, hd=128,
+                  window=12),
+    "step": dict(name="moonshine_tiny_decoder_layer_step_f16_batch64_rope_append_attend",
+                 batch=64, heads=8, hd=36, maxPos=448),
+}
+
+
+def run_aux(args):
+    import ctypes as C
+    import numpy as np
+    import torch
+    import oracle
+    import runntime_b200 as rt
+    from runntime_b200._lib import DTYPE_CODE, check
+    if int(os.environ.get("RANK", "0")) != 0:
+        return  # these operators do not shard: other ranks would only be replicas
+    key, cfg = args.workload, AUX[args.workload]
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ex = rt.CudaExecutor(0)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    lib, peaks = ex._lib, load_peaks()
+    g = torch.Generator(device=dev).manual_seed(11)
+    f16 = DTYPE_CODE["f16"]
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    cores = oracle.num_threads()
+    unit = "GB/s"
+    if key == "rope":
+        R, W, hd = cfg["rows"], cfg["cols"], cfg["hd"]
+        x = torch.randn(R, W, generator=g, device=dev, dtype=torch.float16)
+        ang = torch.rand(R, hd // 2, generator=g, device=dev) * 6.28
+        cos, sin = (t.repeat_interleave(2, dim=1).contiguous() for t in (ang.cos(), ang.sin()))
+        out = torch.empty_like(x)
+        step = lambda i: check(lib.rt_rope(ex.ctx, ptr(x), ptr(cos), ptr(sin), ptr(out), R, W, hd,
+                                           0, W, f16), ex.ctx)
+        work = 2 * x.numel() * 2 + 2 * cos.numel() * 4
+        host_in, host_out = [x], out
+        n = 2048  # CPU sample rows
+        xs = np.random.default_rng(1).standard_normal((n, W)).astype(np.float32)
+        cs = np.ones((n, hd), np.float32)
+        cpu = lambda: oracle.rope_ref(xs, cs, cs, headDim=hd)
+        cpu_work, sample = 2 * n * W * 2 + 2 * n * hd * 4, f"{n} of {R} rows (f64 restatement)"
+    elif key == "softmax":
+        n = cfg["n"]
+        x = (torch.randn(n, n, generator=g, device=dev) * 3).to(torch.float16)
+        segs = torch.empty(n, 2, device=dev)
+        segs[: n // 2] = torch.tensor([0.0, n // 2], device=dev)
+        segs[n // 2:] = torch.tensor([n // 2, float(n)], device=dev)
+        out = torch.empty_like(x)
+        step = lambda i: check(lib.rt_softmax(ex.ctx, ptr(x), ptr(out), ptr(segs), n, n,
+                                              rt._lib.WINDOW_INF, 0, f16), ex.ctx)
+        # a causal row r of segment [s, e) reads r - s + 1 scores; every row writes n
+        half = n // 2
+        kept = 2 * (half * (half + 1) // 2)
+        work = kept * 2 + n * n * 2
+        host_in, host_out = [x], out
+        m = 2048
+        xs = np.random.default_rng(1).standard_normal((m, m)).astype(np.float32)
+        sg = np.array([[0, m]] * m, np.float32)
+        cpu = lambda: oracle.softmax_ref(xs, sg, math.inf, 0)
+        cpu_work, sample = (m * (m + 1) // 2) * 2 + m * m * 2, f"{m} x {m} causal (f64 restatement)"
+    elif key == "local":
+        R, H, hd, wn = cfg["rows"], cfg["heads"], cfg["hd"], cfg["window"]
+        w = H * hd
+        qkv = torch.randn(R, 3 * w, generator=g, device=dev, dtype=torch.float16)
+        rel = torch.randn(wn, w, generator=g, device=dev)
+        qs = torch.rand(hd, generator=g, device=dev)
+        out = torch.empty(R, w, device=dev, dtype=torch.float16)
+        step = lambda i: check(lib.rt_local_attention(ex.ctx, ptr(qkv), ptr(rel), ptr(qs), ptr(out),
+                                                      R, H, hd, wn, 1.0, 50.0, f16), ex.ctx)
+        work = qkv.numel() * 2 + out.numel() * 2
+        host_in, host_out = [qkv], out
+        m = 1024
+        xs = np.random.default_rng(1).standard_normal((m, 3 * w)).astype(np.float32)
+        rl, q1 = rel.cpu().numpy(), qs.cpu().numpy()
+        cpu = lambda: oracle.local_attention_ref(xs, rl, q1, heads=H, headDim=hd, window=wn)
+        cpu_work, sample = m * 4 * w * 2, f"{m} of {R} rows (f64 restatement)"
+    else:  # step: rope x2 + slice + writeRows x2 + attention of one decoder layer, batch of sequences
+        from runntime_b200.engine import decode_batched
+        B, H, hd, P = cfg["batch"], cfg["heads"], cfg["hd"], cfg["maxPos"]
+        w = H * hd
+        kc = torch.randn(B, P, w, generator=g, device=dev, dtype=torch.float16)
+        vc = torch.randn(B, P, w, generator=g, device=dev, dtype=torch.float16)
+        lens = torch.randint(1, P - 8, (B,), generator=torch.Generator().manual_seed(3))
+        kvLens = (lens + 1).to(torch.int32).to(dev)   # visible rows including the appended one
+        tab = torch.rand(P, hd // 2, generator=g, device=dev) * 6.28
+        cos = (tab.cos().repeat_interleave(2, 1) * hd ** -0.25).contiguous()
+        sin = (tab.sin().repeat_interleave(2, 1) * hd ** -0.25).contiguous()
+        qkv = torch.randn(B, 3 * w, generator=g, device=dev, dtype=torch.float16)
+        out = torch.empty(B, w, device=dev, dtype=torch.float16)
+        base, maxLen = qkv.data_ptr(), int(lens.max()) + 1
+
+        def step(i):  # the same positions every step: the append rewrites the same rows
+            decode_batched(ex, base, out, kc, vc, dtype="f16", batch=B, cacheRows=P, qHeads=H,
+                           kvHeads=H, headDim=hd, kvLen=maxLen, kvLens=kvLens, kNew=base + w * 2,
+                           vNew=base + 2 * w * 2, ropeCos=cos, ropeSin=sin, ropeByPosition=True,
+                           qRowStride=3 * w, kNewRowStride=3 * w, vNewRowStride=3 * w)
+        work = sum(2 * (int(L) + 1) * w * 2 for L in lens) + B * (3 * w + w + 2 * w) * 2
+        host_in, host_out = [qkv], out
+        cpu, cpu_work, sample = None, 0, ""
+    flushbuf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    small = key == "step"
+    n0 = ex.launchCount()
+    sampler = ClockSampler(0) if not args.no_clocks else None
+    if sampler:
+        sampler.start()
+    ms = timed(torch, None, 1, step, args.steps, args.warmup, (lambda: flushbuf.fill_(1)) if small else None)
+    clocks = sampler.stop() if sampler else None
+    launches = (ex.launchCount() - n0) * args.steps // (args.steps + args.warmup)
+    value = work * args.steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": f"{key}_hbm_gbs", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": cfg["name"],
+                   "l2": "256 MB flush between timed steps" if small else "inputs larger than L2",
+                   "parallelism": "replicas only"},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"]},
+        "clocks": clocks, "gpu_launches": launches,
+    }
+    if not args.no_e2e:
+        hin = [t.cpu().pin_memory() for t in host_in]
+        hout = torch.empty(host_out.shape, dtype=host_out.dtype).pin_memory()
+
+        def e2e(i):
+            for d, h in zip(host_in, hin):
+                d.copy_(h, non_blocking=True)
+            step(i)
+            hout.copy_(host_out, non_blocking=True)
+        ems = timed(torch, None, 1, e2e, max(2, min(args.steps, 3)), 1)
+        esteps = max(2, min(args.steps, 3))
+        line["e2e"] = {"value": work * esteps / (ems * 1e-3) / 1e9, "unit": unit,
+                       "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
+                       "d2h_bytes_per_step": host_out.numel() * host_out.element_size(),
+                       "ms_per_step": ems / esteps}
+    if cpu is not None and not args.no_cpu:
+        cpu()
+        n, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < 5.0 and n < 50:
+            cpu()
+            n += 1
+        dt = (time.perf_counter() - t0) / n
+        line["cpu_baseline"] = {"value": cpu_work / dt / 1e9, "unit": unit, "cores": cores,
+                                "kind": "port", "sample": f"{sample}; {n} passes of {dt * 1e3:.1f} ms"}
+    print(json.dumps(line), flush=True)
+    ex.dispose()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c5", choices=sorted(CONFIGS))
+    ap.add_argument("--workload", default="c5", choices=sorted(CONFIGS) + sorted(AUX))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode rider of c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
@@ -633,7 +792,13 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="override the workload's batch (small cases for profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload in AUX:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the reference arm covers the attention workloads c1..c5 only"}))
+        else:
+            run_aux(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
