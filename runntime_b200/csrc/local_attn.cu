@@ -6,13 +6,20 @@
 // (packages/runntime/src/core/kernels/attention/attnLocal.ts:58-123; op
 // packages/runntime/src/core/graph/ops/attention.ts:255-300).
 //
-// One warp per (row, head), eight per CTA.  Each lane owns four-element words of
-// the head: it keeps its share of q * qScale in registers (heads up to 512 wide,
-// re-read beyond), adds its share of every distance's dot product, and the
-// `window` partial sums are then reduced across the warp together.  K, V and the
-// bias rows are read with 8- or 16-byte accesses; every K/V row is re-read by the
-// `window` queries that see it, which L1/L2 absorb (the window's rows are
-// adjacent), so HBM sees the slab once and the output once.
+// Tiled kernel (heads up to 512 wide): a CTA takes a run of consecutive rows of
+// one head and stages their K and V rows, the window-1 rows before them and the
+// head's bias rows in shared memory once, so every K/V row leaves L2 once per
+// CTA instead of once per query that sees it (window times).  One warp per row
+// inside the tile: each lane owns four-element words of the head, keeps its
+// share of q * qScale in registers, adds its share of every distance's dot
+// product from shared memory, and the partial sums are reduced across the warp.
+// HBM-bound: the slab is read once (plus (window-1)/tileRows of K and V again at
+// tile seams) and the output written once.
+//
+// Row kernel (any head width): one warp per (row, head), operands straight from
+// global memory; every K/V row is re-read by the `window` queries that see it,
+// which L1/L2 absorb.  Used when a tile would not fit shared memory.
+#include <type_traits>
 #include "common.cuh"
 
 namespace rt {
@@ -148,11 +155,168 @@ local_attn_kernel(const T* __restrict__ qkv, const float* __restrict__ rel,
   }
 }
 
+// ---- tiled kernel ------------------------------------------------------------------
+constexpr int kTileThreads = 256;
+
+template <typename T, int WMAX>
+__global__ void __launch_bounds__(kTileThreads)
+local_attn_tiled_kernel(const T* __restrict__ qkv, const float* __restrict__ rel,
+                        const float* __restrict__ qScale, T* __restrict__ out, int64_t rows,
+                        int heads, int hd, int window, int tileRows, float kScale, float softcap) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = blockIdx.y;
+  const int64_t t0 = (int64_t)blockIdx.x * tileRows;            // first query row of the tile
+  const int64_t first = t0 - (window - 1) > 0 ? t0 - (window - 1) : 0;  // first staged key row
+  const int nq = (int)min((int64_t)tileRows, rows - t0);
+  const int staged = (int)(t0 + nq - first);
+  const int words = hd >> 2;
+  const int64_t width = (int64_t)heads * hd, rowElems = 3 * width;
+  const int maxStaged = tileRows + window - 1;
+  T* sK = reinterpret_cast<T*>(smem);
+  T* sV = sK + (size_t)maxStaged * hd;
+  float* sRel = reinterpret_cast<float*>(sV + (size_t)maxStaged * hd);
+
+  // Stage K and V rows [first, first + staged) of this head and the head's bias rows.
+  for (int i = threadIdx.x; i < staged * words; i += kTileThreads) {
+    const int r = i / words, w = i - r * words;
+    const T* src = qkv + (first + r) * rowElems + width + (int64_t)h * hd + 4 * w;
+    using Word = typename std::conditional<sizeof(T) == 2, uint2, uint4>::type;
+    *reinterpret_cast<Word*>(sK + (size_t)r * hd + 4 * w) = *reinterpret_cast<const Word*>(src);
+    *reinterpret_cast<Word*>(sV + (size_t)r * hd + 4 * w) = *reinterpret_cast<const Word*>(src + width);
+  }
+  for (int i = threadIdx.x; i < window * words; i += kTileThreads) {
+    const int j = i / words, w = i - j * words;
+    *reinterpret_cast<float4*>(sRel + (size_t)j * hd + 4 * w) =
+        *reinterpret_cast<const float4*>(rel + (int64_t)j * width + (int64_t)h * hd + 4 * w);
+  }
+  __syncthreads();
+
+  for (int r = warp; r < nq; r += kTileThreads / 32) {
+    const int64_t t = t0 + r;
+    const int n = (int)min((int64_t)window, t + 1);
+    const int kr = (int)(t - first);  // staged index of key t
+    const T* qp = qkv + t * rowElems + (int64_t)h * hd;
+    float4 qreg[kRegWords];
+#pragma unroll
+    for (int i = 0; i < kRegWords; i++) {
+      const int w = lane + 32 * i;
+      qreg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (w < words) {
+        const float4 q = load4<T>(qp + 4 * w), sc = load4<float>(qScale + 4 * w);
+        qreg[i] = make_float4(q.x * sc.x, q.y * sc.y, q.z * sc.z, q.w * sc.w);
+      }
+    }
+    // Lane j ends up with the score of distance j: every lane adds its share of each
+    // dot product, the shares are summed across the warp, and lane j keeps sum j.
+    float mine = 0.f;
+#pragma unroll
+    for (int j = 0; j < WMAX; j++) {
+      if (j < n) {
+        const T* kp = sK + (size_t)(kr - j) * hd;
+        const float* rp = sRel + (size_t)j * hd;
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kRegWords; i++) {
+          const int w = lane + 32 * i;
+          if (w < words) {
+            const float4 k = load4<T>(kp + 4 * w), rl = load4<float>(rp + 4 * w);
+            const float4 q = qreg[i];
+            s = fmaf(q.x, fmaf(k.x, kScale, rl.x), s);
+            s = fmaf(q.y, fmaf(k.y, kScale, rl.y), s);
+            s = fmaf(q.z, fmaf(k.z, kScale, rl.z), s);
+            s = fmaf(q.w, fmaf(k.w, kScale, rl.w), s);
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == j) mine = s;
+      }
+    }
+    // Softcap, softmax: one tanh and one exp per lane instead of `window` of each.
+    const float sc = lane < n ? softcap * tanhf(mine / softcap) : -3.402823466e38f;
+    float m = sc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float pr = lane < n ? expf(sc - m) : 0.f;
+    float sum = pr;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float pn = pr / sum;  // distance 0 always exists, so sum >= 1
+    T* op = out + t * width + (int64_t)h * hd;
+    float4 acc[kRegWords];
+#pragma unroll
+    for (int i = 0; i < kRegWords; i++) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < WMAX; j++) {
+      if (j < n) {
+        const float pj = __shfl_sync(0xffffffffu, pn, j);
+        const T* vp = sV + (size_t)(kr - j) * hd;
+#pragma unroll
+        for (int i = 0; i < kRegWords; i++) {
+          const int w = lane + 32 * i;
+          if (w < words) {
+            const float4 v = load4<T>(vp + 4 * w);
+            acc[i].x = fmaf(pj, v.x, acc[i].x);
+            acc[i].y = fmaf(pj, v.y, acc[i].y);
+            acc[i].z = fmaf(pj, v.z, acc[i].z);
+            acc[i].w = fmaf(pj, v.w, acc[i].w);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kRegWords; i++) {
+      const int w = lane + 32 * i;
+      if (w < words) store4<T>(op + 4 * w, acc[i]);
+    }
+  }
+}
+
+// Rows per tile so that K, V and the bias rows fit `budget` bytes; 0 if not even 8 fit.
+int tile_rows_for(int hd, int window, int esize, size_t budget) {
+  const size_t relBytes = (size_t)window * hd * 4;
+  for (int tr : {128, 64, 32, 16, 8}) {
+    const size_t need = 2 * (size_t)(tr + window - 1) * hd * esize + relBytes;
+    if (need <= budget) return tr;
+  }
+  return 0;
+}
+
+template <typename T>
+cudaError_t launch_tiled(const void* qkv, const float* rel, const float* qScale, void* out,
+                         int64_t rows, int heads, int hd, int window, int tileRows, float kScale,
+                         float softcap, cudaStream_t s) {
+  const size_t smemBytes = 2 * (size_t)(tileRows + window - 1) * hd * sizeof(T) +
+                           (size_t)window * hd * 4;
+  auto kern = window <= 16 ? local_attn_tiled_kernel<T, 16> : local_attn_tiled_kernel<T, 32>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smemBytes);
+  if (e != cudaSuccess) return e;
+  const dim3 grid((unsigned)((rows + tileRows - 1) / tileRows), (unsigned)heads);
+  kern<<<grid, kTileThreads, smemBytes, s>>>(static_cast<const T*>(qkv), rel, qScale,
+                                             static_cast<T*>(out), rows, heads, hd, window,
+                                             tileRows, kScale, softcap);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_local_attn(const void* qkv, const float* rel, const float* qScale, void* out,
                               int64_t rows, int heads, int hd, int window, float kScale,
                               float softcap, int dtype, cudaStream_t s) {
+  // The tiled kernel wants the head in registers (<= 512 wide), a grid within the
+  // y limit and a tile that fits shared memory beside a second resident CTA.
+  const int esize = dtype == RT_F16 ? 2 : 4;
+  const int tileRows = (hd <= 128 * kRegWords && heads <= 65535)
+                           ? tile_rows_for(hd, window, esize, 100 * 1024) : 0;
+  if (tileRows > 0 && (rows + tileRows - 1) / tileRows <= 0x7fffffffll) {
+    return dtype == RT_F16
+               ? launch_tiled<__half>(qkv, rel, qScale, out, rows, heads, hd, window, tileRows,
+                                      kScale, softcap, s)
+               : launch_tiled<float>(qkv, rel, qScale, out, rows, heads, hd, window, tileRows,
+                                     kScale, softcap, s);
+  }
   const int64_t blocks = (rows * heads + kWarps - 1) / kWarps;
   if (blocks > 0x7fffffffll) return cudaErrorInvalidValue;
   if (dtype == RT_F16)

@@ -1,6 +1,7 @@
 // Small kernels beside attention: the standalone KV-cache append (writeRows),
 // the rotary embedding that precedes it, and the cross-device merge of
 // (m, l, acc) partials.
+#include <type_traits>
 #include "common.cuh"
 
 namespace rt {
@@ -101,6 +102,46 @@ __global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ c
   }
 }
 
+// Vector path: a thread takes one 16-byte (or, for heads like 36 and 52 halves wide,
+// 8-byte) group of columns of a head for one row, loads the row's cos/sin for those columns once and
+// walks over the heads of the window, so the tables cost one read per row and column
+// group instead of one per element.  Needs headDim, srcStart, the row strides and the
+// base addresses on boundaries of the group size.
+template <typename T, int V>   // V elements (V*sizeof(T) = 16 or 8 bytes) per thread and access
+__global__ void rope_vec_kernel(const T* __restrict__ x, const float* __restrict__ cosT,
+                                const float* __restrict__ sinT, T* __restrict__ out, int64_t rows,
+                                int64_t srcCols, int hd, int64_t srcStart, int64_t width) {
+  using Word = typename std::conditional<V * sizeof(T) == 16, uint4, uint2>::type;
+  const int groups = hd / V;
+  const int nHeads = (int)(width / hd);
+  const int64_t total = rows * groups;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t row = i / groups;
+    const int c0 = (int)(i - row * groups) * V;
+    float c[V / 2], sn[V / 2];
+#pragma unroll
+    for (int e = 0; e < V / 2; e += 2) {  // tables are pair-duplicated: entries 0, 2 of a float4
+      const float4 cv = *reinterpret_cast<const float4*>(cosT + row * hd + c0 + 2 * e);
+      const float4 sv = *reinterpret_cast<const float4*>(sinT + row * hd + c0 + 2 * e);
+      c[e] = cv.x, c[e + 1] = cv.z, sn[e] = sv.x, sn[e + 1] = sv.z;
+    }
+    const T* src = x + row * srcCols + srcStart + c0;
+    T* dst = out + row * width + c0;
+    for (int h = 0; h < nHeads; h++) {
+      Word raw = *reinterpret_cast<const Word*>(src + (int64_t)h * hd);
+      T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int e = 0; e < V / 2; e++) {
+        float r0, r1;
+        rope_pair(to_f32<T>(v[2 * e]), to_f32<T>(v[2 * e + 1]), c[e], sn[e], r0, r1);
+        v[2 * e] = from_f32<T>(r0), v[2 * e + 1] = from_f32<T>(r1);
+      }
+      *reinterpret_cast<Word*>(dst + (int64_t)h * hd) = raw;
+    }
+  }
+}
+
 template <typename T>
 void rope_launch(const void* x, const float* cosT, const float* sinT, void* out, int64_t rows,
                  int64_t srcCols, int hd, int64_t srcStart, int64_t width, unsigned blocks,
@@ -110,6 +151,27 @@ void rope_launch(const void* x, const float* cosT, const float* sinT, void* out,
                       (reinterpret_cast<uintptr_t>(out) % pairBytes == 0);
   auto* xi = static_cast<const T*>(x);
   auto* oi = static_cast<T*>(out);
+  const auto aligned = [&](int v) {
+    const uintptr_t bytes = v * sizeof(T);
+    return hd % v == 0 && hd % 4 == 0 && srcStart % v == 0 && srcCols % v == 0 && width % v == 0 &&
+           reinterpret_cast<uintptr_t>(x) % bytes == 0 && reinterpret_cast<uintptr_t>(out) % bytes == 0 &&
+           reinterpret_cast<uintptr_t>(cosT) % 16 == 0 && reinterpret_cast<uintptr_t>(sinT) % 16 == 0;
+  };
+  const auto vblocks = [&](int v) {
+    const int64_t vb = (rows * (hd / v) + 255) / 256;
+    return (unsigned)(vb > 148 * 32 ? 148 * 32 : vb);
+  };
+  constexpr int V16 = 16 / sizeof(T);
+  if (aligned(V16)) {
+    rope_vec_kernel<T, V16><<<vblocks(V16), 256, 0, s>>>(xi, cosT, sinT, oi, rows, srcCols, hd,
+                                                         srcStart, width);
+    return;
+  }
+  if (sizeof(T) == 2 && aligned(4)) {
+    rope_vec_kernel<T, 4><<<vblocks(4), 256, 0, s>>>(xi, cosT, sinT, oi, rows, srcCols, hd,
+                                                     srcStart, width);
+    return;
+  }
   if (paired)
     rope_kernel<T, true><<<blocks, 256, 0, s>>>(xi, cosT, sinT, oi, rows, srcCols, hd, srcStart, width);
   else
