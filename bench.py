@@ -196,7 +196,22 @@ class Decode:
             self.ck = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
             self.cv = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
             self.out2 = torch.empty_like(self.q)
-        self.sharded = ShardedDecode() if (self.shard_kv and world > 1) else None
+        # KV rows split over ranks: the partials are traded through peer memory by the decode
+        # kernel itself (--exchange peer, the default) or by one NCCL all-gather (--exchange nccl,
+        # also the fallback when symmetric memory cannot be set up).
+        self.sharded = self.peer = None
+        self.exchange = "none"
+        if self.shard_kv and world > 1:
+            if cfg.get("exchange", "peer") == "peer":
+                try:
+                    from runntime_b200.engine import PeerExchangeDecode
+                    self.peer = PeerExchangeDecode(units=nb * cfg["qHeads"], headDim=hd, device=dev)
+                    self.exchange = "peer memory, in the decode kernel"
+                except Exception as e:  # noqa: BLE001 - any set-up failure means: use NCCL
+                    sys.stderr.write(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL\n")
+            if self.peer is None:
+                self.sharded = ShardedDecode()
+                self.exchange = "one NCCL all-gather"
         self.partials = (torch.empty(nb * cfg["qHeads"], 2 + hd, dtype=torch.float32, device=dev)
                          if self.sharded else None)
 
@@ -219,7 +234,7 @@ class Decode:
 
     def launches_per_step(self):
         n = 1 + (1 if self.cfg["cross"] else 0)
-        return n + (1 if self.sharded else 0)
+        return n + (1 if (self.sharded or self.peer) else 0)
 
     def step(self, layer=0):
         from runntime_b200.engine import decode_batched
@@ -228,6 +243,9 @@ class Decode:
             return
         common = dict(dtype="f16", batch=self.b, qHeads=c["qHeads"], kvHeads=c["kvHeads"],
                       headDim=c["hd"])
+        if self.peer:
+            self.peer.step(self.ex, self.q, self.k, self.v, self.out, shardRows=self.rows, **common)
+            return
         if self.sharded:
             self.sharded.step(self.ex, self.q, self.k, self.v, self.out, shardRows=self.rows,
                               partials=self.partials, **common)
@@ -482,6 +500,7 @@ def run_gpu(args):
 
     def measure(key, steps, warmup, with_e2e):
         cfg = dict(CONFIGS[key])
+        cfg["exchange"] = args.exchange
         if args.batch and key == args.workload:
             cfg["batch"] = args.batch
             cfg["name"] += f"_batch{args.batch}"
@@ -548,6 +567,7 @@ def run_gpu(args):
         # roofline of the dominant kernel on this rank: its algorithmic work / its launch time
         achieved = per_launch_local / (ms / steps * 1e-3) / (1e12 if bound == "tensor" else 1e9)
         res = {
+            "exchange": getattr(wl, "exchange", None),
             "metric": metric_name(cfg), "value": value, "unit": unit, "ms_per_step": ms / steps,
             "dtype": cfg["dtype"], "workload": cfg["name"],
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak,
@@ -591,7 +611,8 @@ def run_gpu(args):
             "config": {"workload": cfg["name"], "l2": main["l2"], "launch": main["launch"],
                        "parallelism": ("sequences sharded over ranks, no collective"
                                        if cfg["kind"] == "prefill" else
-                                       "KV rows sharded over ranks, one all-gather of partials"
+                                       "KV rows sharded over ranks, partials exchanged by "
+                                       + str(main.get("exchange"))
                                        if cfg.get("lens") is None else "sequences sharded over ranks")},
             "roofline": main["roofline"], "clocks": main["clocks"],
             "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
@@ -603,7 +624,8 @@ def run_gpu(args):
         if extra:
             line["decode"] = {k: extra.get(k) for k in ("metric", "value", "unit", "ms_per_step",
                                                         "workload", "roofline", "e2e",
-                                                        "gpu_launches", "clocks", "launch")}
+                                                        "gpu_launches", "clocks", "launch",
+                                                        "exchange")}
             if world == 1 and not args.no_cpu:
                 v, cores, desc, _ = cpu_sample("c4", budget_s=6.0)
                 line["decode"]["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores,
@@ -787,6 +809,8 @@ def main():
                     help="launch decode steps directly instead of replaying a CUDA graph")
     ap.add_argument("--tc-mode", type=int, default=None,
                     help="RT_OPT_PREFILL_TC value (0: FP32-pipe kernel, 1: tensor-core kernel)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="how KV-sharded decode trades partials between ranks")
     ap.add_argument("--rows", type=int, default=0,
                     help="override the workload's sequence / cache length (small cases)")
     ap.add_argument("--batch", type=int, default=0,

@@ -182,6 +182,30 @@ RT_API int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** rou
  * f32 [batch, qHeads, 2+headDim] = (m, l, acc) per head for a later
  * rt_attn_merge_partials (KV-sequence sharding across GPUs); keyOffset is
  * not needed because the softmax algebra is position-free. */
+/* Exchange of the partials between the GPUs that hold the KV rows of the same
+ * sequences (one process per GPU; every pointer below is an address in THIS
+ * process: a peer's buffer mapped here, for example through CUDA IPC or
+ * torch's symmetric memory).  With it rt_attn_decode writes this rank's
+ * (m, l, acc) rows straight into every peer's buffer from the decode kernel,
+ * signals them, and runs a merge kernel that waits (bounded, about a second)
+ * for all peers' rows of the same step before it merges: the decode step, the
+ * all-gather and the merge of packages/runntime/src/core/kernels/attention/
+ * attnDecode.ts:388-424 lifted across devices, without a library collective.
+ * Every rank must make the same sequence of calls.  Buffers alternate between
+ * two halves by step parity, so a rank one step ahead never overwrites rows a
+ * slower peer is still merging.  All words start at zero. */
+#define RT_MAX_PEERS 8
+typedef struct {
+  int32_t world;                   /* ranks sharing the sequences, 1..RT_MAX_PEERS */
+  int32_t rank;                    /* this rank */
+  float* partials[RT_MAX_PEERS];   /* rank r's buffer: f32 [2][world][batch*qHeads][2+headDim] */
+  uint32_t* flags[RT_MAX_PEERS];   /* rank r's arrival words: [world] */
+  uint32_t* step;                  /* this rank's step counter (one word) */
+  uint32_t* done;                  /* this rank's finished-block counter (one word) */
+  int32_t phases;                  /* 0 or 3: the whole step; 1: attend and send only; 2: wait and
+                                      merge only (for callers that put other work in between) */
+} rt_exchange;
+
 typedef struct {
   const void* q;          /* device [batch, qHeads*headDim] */
   void* out;              /* device [batch, qHeads*headDim] (unused with partialsOut) */
@@ -208,6 +232,7 @@ typedef struct {
   int64_t qRowStride;     /* elements between q rows; 0 = qHeads*headDim (dense) */
   int64_t kNewRowStride;  /* elements between kNew rows; 0 = kvHeads*headDim */
   int64_t vNewRowStride;  /* elements between vNew rows; 0 = kvHeads*headDim */
+  const rt_exchange* exchange; /* host pointer or NULL: merge with the other ranks' rows into out */
 } rt_decode_args;
 
 RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);

@@ -34,6 +34,18 @@ class AttnArgs(C.Structure):
     ]
 
 
+MAX_PEERS = 8
+
+
+class Exchange(C.Structure):
+    """rt_exchange: where the ranks sharing a set of sequences trade partials."""
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32),
+        ("partials", C.c_void_p * MAX_PEERS), ("flags", C.c_void_p * MAX_PEERS),
+        ("step", C.c_void_p), ("done", C.c_void_p), ("phases", C.c_int32),
+    ]
+
+
 class DecodeArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("out", C.c_void_p), ("kCache", C.c_void_p), ("vCache", C.c_void_p),
@@ -45,6 +57,7 @@ class DecodeArgs(C.Structure):
         ("headDim", C.c_int32), ("windowLeft", C.c_int32), ("splits", C.c_int32),
         ("ropeByPosition", C.c_int32), ("ropeCos", C.c_void_p), ("ropeSin", C.c_void_p),
         ("qRowStride", C.c_int64), ("kNewRowStride", C.c_int64), ("vNewRowStride", C.c_int64),
+        ("exchange", C.POINTER(Exchange)),
     ]
 
 

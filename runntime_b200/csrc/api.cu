@@ -487,7 +487,18 @@ int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
     return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: %s", why);
   rt::DecodeParams p{};
   rt::decode_params_from_args(*a, p);
-  return run_decode(ctx, p, a->dtype);
+  const int phases = a->exchange && a->exchange->phases ? a->exchange->phases : 3;
+  if (phases & 1) {
+    const int s = run_decode(ctx, p, a->dtype);
+    if (s != RT_OK) return s;
+  }
+  if (!a->exchange || !(phases & 2)) return RT_OK;
+  const rt_exchange& x = *a->exchange;
+  RT_CUDA(ctx, rt::launch_merge_exchanged(x.partials[x.rank], x.flags[x.rank], x.step, x.world,
+                                          (int64_t)a->batch * a->qHeads, a->headDim, a->out,
+                                          a->dtype, ctx->statusDev, ctx->stream));
+  ctx->launches++;
+  return RT_OK;
 }
 
 int rt_attn_merge_partials(rt_ctx* ctx, const float* partials, int32_t parts, int64_t units,

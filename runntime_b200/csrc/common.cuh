@@ -95,6 +95,12 @@ struct DecodeParams {
   const float* ropeSin;
   int32_t ropeByPos;
   int64_t qRowStride, kNewRowStride, vNewRowStride;
+  // cross-GPU exchange of the final partials (xWorld = 0: off); see rt_exchange
+  float* xPartials[RT_MAX_PEERS];
+  uint32_t* xFlags[RT_MAX_PEERS];
+  uint32_t* xStep;
+  uint32_t* xDone;
+  int32_t xWorld, xRank;
 };
 
 // Copies the caller's decode arguments (already validated) into kernel parameters.
@@ -122,6 +128,18 @@ inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
   p.qRowStride = a.qRowStride ? a.qRowStride : (int64_t)a.qHeads * a.headDim;
   p.kNewRowStride = a.kNewRowStride ? a.kNewRowStride : (int64_t)a.kvHeads * a.headDim;
   p.vNewRowStride = a.vNewRowStride ? a.vNewRowStride : (int64_t)a.kvHeads * a.headDim;
+  p.xWorld = 0;
+  if (a.exchange) {
+    p.xWorld = a.exchange->world;
+    p.xRank = a.exchange->rank;
+    for (int r = 0; r < RT_MAX_PEERS; r++) {
+      p.xPartials[r] = r < a.exchange->world ? a.exchange->partials[r] : nullptr;
+      p.xFlags[r] = r < a.exchange->world ? a.exchange->flags[r] : nullptr;
+    }
+    p.xStep = a.exchange->step;
+    p.xDone = a.exchange->done;
+    p.partialsOut = nullptr;
+  }
 }
 
 // What is wrong with the rope / stride fields of decode arguments, or NULL.
@@ -134,6 +152,15 @@ inline const char* decode_rope_args_error(const rt_decode_args& a) {
   if (a.kNewRowStride < 0 || (a.kNewRowStride && a.kNewRowStride < kvw) ||
       a.vNewRowStride < 0 || (a.vNewRowStride && a.vNewRowStride < kvw))
     return "kNewRowStride / vNewRowStride is smaller than one kv row";
+  if (a.exchange) {
+    const rt_exchange& x = *a.exchange;
+    if (x.world < 1 || x.world > RT_MAX_PEERS || x.rank < 0 || x.rank >= x.world)
+      return "exchange: world must be 1..8 and rank inside it";
+    if (!x.step || !x.done || !a.out) return "exchange: step, done and out must be given";
+    if (x.phases < 0 || x.phases > 3) return "exchange: phases must be 0..3";
+    for (int r = 0; r < x.world; r++)
+      if (!x.partials[r] || !x.flags[r]) return "exchange: a peer buffer is NULL";
+  }
   return nullptr;
 }
 
@@ -162,6 +189,10 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_merge_partials(const float* partials, int parts, int64_t units, int hd,
                                   void* out, int dtype, cudaStream_t s);
+// Merge of the exchanged partials: waits for every rank's arrival word to reach *step.
+cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, const uint32_t* step,
+                                   int world, int64_t units, int hd, void* out, int dtype,
+                                   int* status, cudaStream_t s);
 cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
                         int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
                         int dtype, cudaStream_t s);

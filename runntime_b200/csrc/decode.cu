@@ -118,6 +118,40 @@ __device__ __forceinline__ void process_key(const T* kp, const T* vp, const floa
   }
 }
 
+// Cross-GPU hand-over, called by the consumer threads of the block that wrote the final
+// rows of (sequence b, head block zb) into this rank's slot: copies those rows into the
+// same slot of every peer's buffer (plain stores to peer memory), and the last block of
+// the launch to finish advances this rank's step counter and publishes it in every
+// rank's arrival word for this rank.
+__device__ __forceinline__ void exchange_rows(const DecodeParams& p, float* mySlot,
+                                              int64_t slotFloats, int b, int zb, int hq, int h0,
+                                              int tid) {
+  const int stride = 2 + p.hd;
+  const int64_t first = ((int64_t)b * p.qHeads + h0) * stride;  // this block's rows: contiguous
+  const int n = hq * stride;
+  __threadfence();                       // the rows written by this block's threads ...
+  named_barrier_sync(1, kConsumers);     // ... are visible to all of them
+  const int64_t slotOffset = mySlot - p.xPartials[p.xRank];
+  for (int r = 0; r < p.xWorld; r++) {
+    if (r == p.xRank) continue;
+    float* dst = p.xPartials[r] + slotOffset + first;
+    for (int i = tid; i < n; i += kConsumers) dst[i] = __ldcg(mySlot + first + i);
+  }
+  __threadfence_system();                // peer stores ordered before the signal below
+  named_barrier_sync(1, kConsumers);
+  if (tid == 0) {
+    const unsigned total = gridDim.y * gridDim.z;  // one finishing block per (sequence, head block)
+    if (atomicAdd(p.xDone, 1u) == total - 1) {
+      *p.xDone = 0;
+      __threadfence_system();
+      const uint32_t epoch = atomicAdd(p.xStep, 1u) + 1u;
+      for (int r = 0; r < p.xWorld; r++)
+        *reinterpret_cast<volatile uint32_t*>(p.xFlags[r] + p.xRank) = epoch;
+      __threadfence_system();
+    }
+  }
+}
+
 template <typename T, int HDP, bool EXACT, int VEC, bool BULK>
 __global__ void __launch_bounds__(BULK ? kConsumers + 32 : kConsumers, HDP <= 64 ? 2 : 1)
 decode_kernel(const DecodeParams p) {
@@ -140,6 +174,17 @@ decode_kernel(const DecodeParams p) {
   const int sliceElems = nkv * hd;
   const int rowElems = p.kvHeads * hd;
   const bool hasNew = p.kNew != nullptr;
+  // Where the final (m, l, acc) rows go, if not into `out`: the caller's buffer, or —
+  // with the cross-GPU exchange — this rank's slot of its own exchange buffer, in the
+  // half that belongs to the step now starting (the step counter moves only after
+  // every block of this launch has finished, so all blocks read the same value).
+  float* partialsOut = p.partialsOut;
+  int64_t xSlotFloats = 0;
+  if (p.xWorld > 0) {
+    const uint32_t parity = (*reinterpret_cast<volatile uint32_t*>(p.xStep) + 1u) & 1u;
+    xSlotFloats = (int64_t)p.batch * p.qHeads * (2 + p.hd);
+    partialsOut = p.xPartials[p.xRank] + ((int64_t)parity * p.xWorld + p.xRank) * xSlotFloats;
+  }
 
   // Key range of this sequence that lives in the cache.
   int64_t lo, end, L = 0;
@@ -359,10 +404,10 @@ decode_kernel(const DecodeParams p) {
       L = fmaf(r[1], w, L);
       for (int c = 0, x = slot; x < hd; x += KS, c++) o[c] = fmaf(r[2 + x], w, o[c]);
     }
-    const bool toPartials = p.partialsOut != nullptr;
+    const bool toPartials = partialsOut != nullptr;
     if (p.splits == 1) {
       if (toPartials) {
-        float* dst = p.partialsOut + ((int64_t)b * p.qHeads + h) * stride;
+        float* dst = partialsOut + ((int64_t)b * p.qHeads + h) * stride;
         if (slot == 0) {
           dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
           dst[1] = L;
@@ -385,7 +430,10 @@ decode_kernel(const DecodeParams p) {
       for (int x = slot; x < hd; x += KS) dst[2 + x] = o[c++];
     }
   }
-  if (p.splits == 1) return;
+  if (p.splits == 1) {
+    if (p.xWorld > 0) exchange_rows(p, partialsOut, xSlotFloats, b, zb, hq, kvh0 * group, tid);
+    return;
+  }
 
   // ---- last CTA of the sequence merges the splits ----
   __threadfence();
@@ -405,24 +453,25 @@ decode_kernel(const DecodeParams p) {
     float L = 0.f;
     for (int s = 0; s < p.splits; s++)
       L = fmaf(__ldcg(base + s * ss + 1), fast_exp2(__ldcg(base + s * ss) - M), L);
-    const bool toPartials = p.partialsOut != nullptr;
+    const bool toPartials = partialsOut != nullptr;
     const float invL = L > 0.f ? 1.f / L : 0.f;
     for (int x = slot; x < hd; x += KS) {
       float o = 0.f;
       for (int s = 0; s < p.splits; s++)
         o = fmaf(__ldcg(base + s * ss + 2 + x), fast_exp2(__ldcg(base + s * ss) - M), o);
       if (toPartials)
-        p.partialsOut[((int64_t)b * p.qHeads + h) * stride + 2 + x] = o;
+        partialsOut[((int64_t)b * p.qHeads + h) * stride + 2 + x] = o;
       else
         static_cast<T*>(p.out)[((int64_t)b * p.qHeads + h) * hd + x] = from_f32<T>(o * invL);
     }
     if (toPartials && slot == 0) {
-      float* dst = p.partialsOut + ((int64_t)b * p.qHeads + h) * stride;
+      float* dst = partialsOut + ((int64_t)b * p.qHeads + h) * stride;
       dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
       dst[1] = L;
     }
   }
   if (tid == 0) p.counters[b * gridDim.z + zb] = 0;  // ready for the next launch
+  if (p.xWorld > 0) exchange_rows(p, partialsOut, xSlotFloats, b, zb, hq, kvh0 * group, tid);
 }
 
 size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
@@ -611,6 +660,9 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
                        "device pointers");
   if (a->dtype != RT_F32 && a->dtype != RT_F16)
     return static_fail(RT_INVALID_ARGUMENT, "rt_attn_decode_noalloc: dtype is neither f32 nor f16");
+  if (a->exchange)
+    return static_fail(RT_INVALID_ARGUMENT,
+                       "rt_attn_decode_noalloc: the cross-GPU exchange needs rt_attn_decode");
   if (a->batch < 1 || a->batch > 65535 || a->cacheRows < 1 || a->qHeads < 1 || a->headDim < 1 ||
       a->headDim > 128 || a->kvHeads < 1 || a->qHeads % a->kvHeads != 0 || a->kvLen < 0 ||
       a->kvLen > a->cacheRows || (!a->kvLens && a->kvLen < 1) || a->windowLeft < 0 ||

@@ -59,6 +59,63 @@ __global__ void merge_partials_kernel(const float* __restrict__ partials, int pa
   }
 }
 
+// The same merge over the rows the ranks exchanged: buffer holds two halves of
+// [world][units][2+hd]; the half of the step just computed is *step & 1.  Each block
+// first waits until every rank's arrival word has reached *step (the decode kernels of
+// the peers publish it after their rows have landed here).  The wait is bounded: about
+// a second, then the block records the failure in *status and writes zeros.
+template <typename T>
+__global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
+                                       const uint32_t* __restrict__ flags,
+                                       const uint32_t* __restrict__ step, int world,
+                                       int64_t units, int hd, T* __restrict__ out, int* status) {
+  __shared__ int sOk;
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(step);
+  if (threadIdx.x == 0) sOk = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const volatile uint32_t* f = flags + threadIdx.x;
+    bool arrived = false;
+    for (int i = 0; i < (1 << 20); i++) {   // about a second with the sleeps below
+      // signed distance: a peer may already be a step ahead
+      if ((int32_t)(*f - epoch) >= 0) { arrived = true; break; }
+      __nanosleep(i < 64 ? 100 : 1000);
+    }
+    if (!arrived) sOk = 0;
+  }
+  __syncthreads();
+  __threadfence_system();  // the peers' rows, stored before their signal, are read below
+  const int lane = threadIdx.x & 31;
+  const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (!sOk) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
+    if (u < units)
+      for (int x = lane; x < hd; x += 32) out[u * hd + x] = from_f32<T>(0.f);
+    return;
+  }
+  if (u >= units) return;
+  const int64_t stride = 2 + hd;
+  const float* partials = buffer + (int64_t)(epoch & 1u) * world * units * stride;
+  float M = kNegSeed;
+  for (int p = lane; p < world; p += 32) M = fmaxf(M, __ldcg(partials + ((int64_t)p * units + u) * stride));
+  M = warp_max(M);
+  float L = 0.f;
+  for (int p = lane; p < world; p += 32) {
+    const float* r = partials + ((int64_t)p * units + u) * stride;
+    L += __ldcg(r + 1) * __expf(__ldcg(r) - M);
+  }
+  L = warp_sum(L);
+  const float invL = L > 0.f ? 1.f / L : 0.f;
+  for (int x = lane; x < hd; x += 32) {
+    float o = 0.f;
+    for (int p = 0; p < world; p++) {
+      const float* r = partials + ((int64_t)p * units + u) * stride;
+      o = fmaf(__ldcg(r + 2 + x), __expf(__ldcg(r) - M), o);
+    }
+    out[u * hd + x] = from_f32<T>(o * invL);
+  }
+}
+
 // Rotary embedding, one thread per interleaved pair of a column window of x:
 // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) with pair-duplicated f32 tables
 // [rows, headDim]; packages/runntime/src/core/kernels/attention/rope.ts:36-70.
@@ -236,6 +293,20 @@ cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes
     write_rows_kernel<uint16_t><<<blocks(n), threads, 0, s>>>(
         reinterpret_cast<uint16_t*>(d), static_cast<const uint16_t*>(src), n);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, const uint32_t* step,
+                                   int world, int64_t units, int hd, void* out, int dtype,
+                                   int* status, cudaStream_t s) {
+  const int warps = 8;
+  const unsigned grid = (unsigned)((units + warps - 1) / warps);
+  if (dtype == RT_F16)
+    merge_exchanged_kernel<__half><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, units, hd,
+                                                                static_cast<__half*>(out), status);
+  else
+    merge_exchanged_kernel<float><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, units, hd,
+                                                               static_cast<float*>(out), status);
   return cudaGetLastError();
 }
 

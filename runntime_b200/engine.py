@@ -21,7 +21,7 @@ from __future__ import annotations
 import ctypes as C
 from typing import Optional, Tuple
 
-from ._lib import AttnArgs, DecodeArgs, DTYPE_CODE, WINDOW_INF, check
+from ._lib import AttnArgs, DecodeArgs, DTYPE_CODE, Exchange, WINDOW_INF, check
 from .executor import CudaExecutor
 
 
@@ -62,7 +62,7 @@ def decode_batched(ex: CudaExecutor, q, out, kCache, vCache, *, dtype: str, batc
                    kvLens=None, kNew=None, vNew=None, cacheSeqStride: Optional[int] = None,
                    windowLeft=None, sinks=None, partialsOut=None, splits: int = 0,
                    ropeCos=None, ropeSin=None, ropeByPosition: bool = False, qRowStride: int = 0,
-                   kNewRowStride: int = 0, vNewRowStride: int = 0) -> None:
+                   kNewRowStride: int = 0, vNewRowStride: int = 0, exchange=None) -> None:
     """One decode step for ``batch`` sequences; see rt_attn_decode in
     include/rt_attn.h.  ``kvLen`` is the (maximum) visible length including the
     appended row; ``kvLens`` gives it per sequence.  With ``ropeCos``/``ropeSin``
@@ -80,6 +80,8 @@ def decode_batched(ex: CudaExecutor, q, out, kCache, vCache, *, dtype: str, batc
     d.windowLeft, d.splits = _win(windowLeft), splits
     d.ropeCos, d.ropeSin, d.ropeByPosition = _ptr(ropeCos), _ptr(ropeSin), int(ropeByPosition)
     d.qRowStride, d.kNewRowStride, d.vNewRowStride = qRowStride, kNewRowStride, vNewRowStride
+    if exchange is not None:
+        d.exchange = C.pointer(exchange)
     check(ex._lib.rt_attn_decode(ex.ctx, C.byref(d)), ex.ctx)
 
 
@@ -166,6 +168,66 @@ def shard_rows(total: int, world: int, rank: int) -> Tuple[int, int]:
     base, extra = divmod(total, world)
     start = rank * base + min(rank, extra)
     return start, start + base + (1 if rank < extra else 0)
+
+
+def exchange_words(world: int, units: int, headDim: int) -> Tuple[int, int]:
+    """(floats of one rank's partials buffer, 32-bit words of its control block)
+    for the cross-GPU exchange: two halves of [world, units, 2+headDim] partials;
+    [world] arrival words + step counter + finished-block counter."""
+    return 2 * world * units * (2 + headDim), world + 2
+
+
+def make_exchange(world: int, rank: int, partialPtrs, controlPtrs) -> Exchange:
+    """rt_exchange over every rank's partials buffer and control block as mapped in
+    this process (``controlPtrs[r]``: rank r's [world] arrival words, then its step
+    counter, then its finished-block counter, all zero at the start)."""
+    x = Exchange()
+    x.world, x.rank = world, rank
+    for r in range(world):
+        x.partials[r] = _ptr(partialPtrs[r])
+        x.flags[r] = _ptr(controlPtrs[r])
+    x.step = _ptr(controlPtrs[rank]) + 4 * world
+    x.done = _ptr(controlPtrs[rank]) + 4 * (world + 1)
+    return x
+
+
+class PeerExchangeDecode:
+    """KV-sequence-sharded decode whose ranks trade partials through peer memory:
+    the decode kernel stores this rank's (m, l, acc) rows into every peer's buffer
+    and signals them, a merge kernel waits for all ranks' rows of the step and
+    merges — no library collective on the step.  The buffers come from torch's
+    symmetric memory (one process per GPU, NVLink peers)."""
+
+    def __init__(self, *, units: int, headDim: int, device, group=None):
+        import os
+        import torch
+        import torch.distributed as dist
+        # plain peer mappings only: no NVLink multicast object is bound to these buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        nfloat, nword = exchange_words(self.world, units, headDim)
+        group_name = (group or dist.group.WORLD).group_name
+        self.partials = symm.empty(nfloat, dtype=torch.float32, device=device)
+        self.control = symm.empty(nword, dtype=torch.int32, device=device)
+        self.partials.zero_()
+        self.control.zero_()
+        hp = symm.rendezvous(self.partials, group_name)
+        hc = symm.rendezvous(self.control, group_name)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)           # everybody's words are zero before anybody signals
+        self.exchange = make_exchange(self.world, self.rank, [int(p) for p in hp.buffer_ptrs],
+                                      [int(p) for p in hc.buffer_ptrs])
+        self._handles = (hp, hc)
+
+    def step(self, ex: CudaExecutor, q, kShard, vShard, out, *, dtype: str, batch: int,
+             shardRows: int, qHeads: int, kvHeads: int, headDim: int, kvLens=None,
+             splits: int = 0):
+        decode_batched(ex, q, out, kShard, vShard, dtype=dtype, batch=batch, cacheRows=shardRows,
+                       qHeads=qHeads, kvHeads=kvHeads, headDim=headDim, kvLen=shardRows,
+                       kvLens=kvLens, splits=splits, exchange=self.exchange)
+        return out
 
 
 class ShardedDecode:

@@ -161,3 +161,67 @@ def test_no_buffer_leak_across_evals(ex):
     assert ex.liveBuffers() == base + 1
     ex.destroy(x)
     assert ex.liveBuffers() == base
+
+
+@pytest.mark.parametrize("world,splits,dtype", [(1, 0, "f16"), (2, 0, "f16"), (4, 3, "f16"),
+                                                (8, 0, "f16"), (3, 2, "f32")])
+def test_peer_exchange_of_partials_emulated_on_one_gpu(ex, world, splits, dtype):
+    """The cross-GPU exchange with every "rank" on this GPU: the ranks' decode
+    launches run one after the other (each writes its rows into all the buffers and
+    signals), then each rank's merge finds all arrival words already set.  Three
+    steps, so that both halves of the buffers and the step counters are exercised."""
+    import torch
+    from runntime_b200.engine import decode_batched, exchange_words, make_exchange, shard_rows
+    batch, heads, kvHeads, hd, rows = 5, 8, 4, 64, 700
+    dev = torch.device("cuda", 0)
+    tdt = torch.float16 if dtype == "f16" else torch.float32
+    g = torch.Generator().manual_seed(9)
+    units = batch * heads
+    nfloat, nword = exchange_words(world, units, hd)
+    partials = [torch.zeros(nfloat, dtype=torch.float32, device=dev) for _ in range(world)]
+    control = [torch.zeros(nword, dtype=torch.int32, device=dev) for _ in range(world)]
+    xs = [make_exchange(world, r, partials, control) for r in range(world)]
+    outs = [torch.empty(batch, heads * hd, dtype=tdt, device=dev) for _ in range(world)]
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        for step in range(3):
+            k = torch.randn(batch, rows, kvHeads * hd, generator=g).to(tdt)
+            v = torch.randn(batch, rows, kvHeads * hd, generator=g).to(tdt)
+            q = (torch.randn(batch, heads * hd, generator=g) / 8).to(tdt)
+            qd = q.to(dev)
+            shards = []
+            for r in range(world):
+                s, e = shard_rows(rows, world, r)
+                shards.append((k[:, s:e].contiguous().to(dev), v[:, s:e].contiguous().to(dev), e - s))
+            # decode kernels of all ranks first, their merges after: nothing waits on a later launch
+            from runntime_b200._lib import DecodeArgs, DTYPE_CODE, check
+            import ctypes as C
+            for r in range(world):
+                ks, vs, n = shards[r]
+                d = DecodeArgs()
+                d.q, d.out = qd.data_ptr(), outs[r].data_ptr()
+                d.kCache, d.vCache = ks.data_ptr(), vs.data_ptr()
+                d.cacheSeqStride = n * kvHeads * hd
+                d.dtype = DTYPE_CODE[dtype]
+                d.batch, d.cacheRows, d.kvLen = batch, n, n
+                d.qHeads, d.kvHeads, d.headDim = heads, kvHeads, hd
+                d.windowLeft, d.splits = 0x3fffffff, splits
+                d.exchange = C.pointer(xs[r])
+                shards[r] = shards[r] + (d,)
+            for phase in (1, 2):   # 1: attend and send, 2: wait and merge
+                for r in range(world):
+                    xs[r].phases = phase
+                    check(ex._lib.rt_attn_decode(ex.ctx, C.byref(shards[r][3])), ex.ctx)
+            ex.sync()
+            for b in range(batch):
+                ref = oracle.sdpa_ref(q[b:b + 1].float().numpy(), k[b].float().numpy(),
+                                      v[b].float().numpy(), qHeads=heads, kvHeads=kvHeads,
+                                      headDim=hd)
+                for r in range(world):
+                    oracle.assert_close(outs[r][b].float().cpu().numpy(), ref.reshape(-1), dtype,
+                                        f"step {step} rank {r} seq {b}")
+            assert all(int(c[world].item()) == step + 1 for c in control)      # step counters
+            assert all((c[:world] == step + 1).all().item() for c in control)  # arrival words
+            assert all(int(c[world + 1].item()) == 0 for c in control)         # block counters reset
+    finally:
+        ex.setStream(None)
