@@ -187,8 +187,8 @@ RT_API int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** rou
  * process: a peer's buffer mapped here, for example through CUDA IPC or
  * torch's symmetric memory).  With it rt_attn_decode writes this rank's
  * (m, l, acc) rows straight into every peer's buffer from the decode kernel,
- * signals them, and runs a merge kernel that waits (bounded, about a second)
- * for all peers' rows of the same step before it merges: the decode step, the
+ * signals them (a one-thread kernel), and runs a merge kernel that waits
+ * (bounded, about a second) for all peers' rows of the same step before it merges: the decode step, the
  * all-gather and the merge of packages/runntime/src/core/kernels/attention/
  * attnDecode.ts:388-424 lifted across devices, without a library collective.
  * Every rank must make the same sequence of calls.  Buffers alternate between
@@ -201,7 +201,6 @@ typedef struct {
   float* partials[RT_MAX_PEERS];   /* rank r's buffer: f32 [2][world][batch*qHeads][2+headDim] */
   uint32_t* flags[RT_MAX_PEERS];   /* rank r's arrival words: [world] */
   uint32_t* step;                  /* this rank's step counter (one word) */
-  uint32_t* done;                  /* this rank's finished-block counter (one word) */
   int32_t phases;                  /* 0 or 3: the whole step; 1: attend and send only; 2: wait and
                                       merge only (for callers that put other work in between) */
 } rt_exchange;

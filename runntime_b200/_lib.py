@@ -42,7 +42,7 @@ class Exchange(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32),
         ("partials", C.c_void_p * MAX_PEERS), ("flags", C.c_void_p * MAX_PEERS),
-        ("step", C.c_void_p), ("done", C.c_void_p), ("phases", C.c_int32),
+        ("step", C.c_void_p), ("phases", C.c_int32),
     ]
 
 

@@ -491,6 +491,11 @@ int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
   if (phases & 1) {
     const int s = run_decode(ctx, p, a->dtype);
     if (s != RT_OK) return s;
+    if (a->exchange) {
+      RT_CUDA(ctx, rt::launch_exchange_signal(a->exchange->step, a->exchange->flags,
+                                              a->exchange->world, a->exchange->rank, ctx->stream));
+      ctx->launches++;
+    }
   }
   if (!a->exchange || !(phases & 2)) return RT_OK;
   const rt_exchange& x = *a->exchange;

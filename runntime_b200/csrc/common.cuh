@@ -99,7 +99,6 @@ struct DecodeParams {
   float* xPartials[RT_MAX_PEERS];
   uint32_t* xFlags[RT_MAX_PEERS];
   uint32_t* xStep;
-  uint32_t* xDone;
   int32_t xWorld, xRank;
 };
 
@@ -137,7 +136,6 @@ inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
       p.xFlags[r] = r < a.exchange->world ? a.exchange->flags[r] : nullptr;
     }
     p.xStep = a.exchange->step;
-    p.xDone = a.exchange->done;
     p.partialsOut = nullptr;
   }
 }
@@ -156,7 +154,7 @@ inline const char* decode_rope_args_error(const rt_decode_args& a) {
     const rt_exchange& x = *a.exchange;
     if (x.world < 1 || x.world > RT_MAX_PEERS || x.rank < 0 || x.rank >= x.world)
       return "exchange: world must be 1..8 and rank inside it";
-    if (!x.step || !x.done || !a.out) return "exchange: step, done and out must be given";
+    if (!x.step || !a.out) return "exchange: step and out must be given";
     if (x.phases < 0 || x.phases > 3) return "exchange: phases must be 0..3";
     for (int r = 0; r < x.world; r++)
       if (!x.partials[r] || !x.flags[r]) return "exchange: a peer buffer is NULL";
@@ -189,6 +187,10 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_merge_partials(const float* partials, int parts, int64_t units, int hd,
                                   void* out, int dtype, cudaStream_t s);
+// After a decode launch with the exchange: advances *step and publishes it in every rank's
+// arrival word for this rank.
+cudaError_t launch_exchange_signal(uint32_t* step, uint32_t* const* flags, int world, int rank,
+                                   cudaStream_t s);
 // Merge of the exchanged partials: waits for every rank's arrival word to reach *step.
 cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, const uint32_t* step,
                                    int world, int64_t units, int hd, void* out, int dtype,

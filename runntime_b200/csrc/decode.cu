@@ -120,35 +120,23 @@ __device__ __forceinline__ void process_key(const T* kp, const T* vp, const floa
 
 // Cross-GPU hand-over, called by the consumer threads of the block that wrote the final
 // rows of (sequence b, head block zb) into this rank's slot: copies those rows into the
-// same slot of every peer's buffer (plain stores to peer memory), and the last block of
-// the launch to finish advances this rank's step counter and publishes it in every
-// rank's arrival word for this rank.
-__device__ __forceinline__ void exchange_rows(const DecodeParams& p, float* mySlot,
-                                              int64_t slotFloats, int b, int zb, int hq, int h0,
-                                              int tid) {
+// same slot of every peer's buffer (plain stores to peer memory).  The ranks are told by
+// the small kernel that follows this one in the stream: a kernel's stores, peer stores
+// included, are complete when it ends, so that kernel only has to publish the step —
+// fencing at system scope in every block here costs microseconds per wave of blocks.
+__device__ __forceinline__ void exchange_rows(const DecodeParams& p, float* mySlot, int b, int hq,
+                                              int h0, int tid) {
+  if (p.xWorld <= 1) return;
   const int stride = 2 + p.hd;
   const int64_t first = ((int64_t)b * p.qHeads + h0) * stride;  // this block's rows: contiguous
   const int n = hq * stride;
-  __threadfence();                       // the rows written by this block's threads ...
-  named_barrier_sync(1, kConsumers);     // ... are visible to all of them
+  __threadfence();                     // the rows written by this block's threads ...
+  named_barrier_sync(1, kConsumers);   // ... are visible to all of them
   const int64_t slotOffset = mySlot - p.xPartials[p.xRank];
   for (int r = 0; r < p.xWorld; r++) {
     if (r == p.xRank) continue;
     float* dst = p.xPartials[r] + slotOffset + first;
     for (int i = tid; i < n; i += kConsumers) dst[i] = __ldcg(mySlot + first + i);
-  }
-  __threadfence_system();                // peer stores ordered before the signal below
-  named_barrier_sync(1, kConsumers);
-  if (tid == 0) {
-    const unsigned total = gridDim.y * gridDim.z;  // one finishing block per (sequence, head block)
-    if (atomicAdd(p.xDone, 1u) == total - 1) {
-      *p.xDone = 0;
-      __threadfence_system();
-      const uint32_t epoch = atomicAdd(p.xStep, 1u) + 1u;
-      for (int r = 0; r < p.xWorld; r++)
-        *reinterpret_cast<volatile uint32_t*>(p.xFlags[r] + p.xRank) = epoch;
-      __threadfence_system();
-    }
   }
 }
 
@@ -176,14 +164,13 @@ decode_kernel(const DecodeParams p) {
   const bool hasNew = p.kNew != nullptr;
   // Where the final (m, l, acc) rows go, if not into `out`: the caller's buffer, or —
   // with the cross-GPU exchange — this rank's slot of its own exchange buffer, in the
-  // half that belongs to the step now starting (the step counter moves only after
-  // every block of this launch has finished, so all blocks read the same value).
+  // half that belongs to the step now starting (the step counter is moved by the kernel
+  // that follows this one, so all blocks read the same value).
   float* partialsOut = p.partialsOut;
-  int64_t xSlotFloats = 0;
   if (p.xWorld > 0) {
     const uint32_t parity = (*reinterpret_cast<volatile uint32_t*>(p.xStep) + 1u) & 1u;
-    xSlotFloats = (int64_t)p.batch * p.qHeads * (2 + p.hd);
-    partialsOut = p.xPartials[p.xRank] + ((int64_t)parity * p.xWorld + p.xRank) * xSlotFloats;
+    const int64_t slotFloats = (int64_t)p.batch * p.qHeads * (2 + p.hd);
+    partialsOut = p.xPartials[p.xRank] + ((int64_t)parity * p.xWorld + p.xRank) * slotFloats;
   }
 
   // Key range of this sequence that lives in the cache.
@@ -431,7 +418,7 @@ decode_kernel(const DecodeParams p) {
     }
   }
   if (p.splits == 1) {
-    if (p.xWorld > 0) exchange_rows(p, partialsOut, xSlotFloats, b, zb, hq, kvh0 * group, tid);
+    if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hq, kvh0 * group, tid);
     return;
   }
 
@@ -471,7 +458,7 @@ decode_kernel(const DecodeParams p) {
     }
   }
   if (tid == 0) p.counters[b * gridDim.z + zb] = 0;  // ready for the next launch
-  if (p.xWorld > 0) exchange_rows(p, partialsOut, xSlotFloats, b, zb, hq, kvh0 * group, tid);
+  if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hq, kvh0 * group, tid);
 }
 
 size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {

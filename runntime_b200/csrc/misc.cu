@@ -59,6 +59,23 @@ __global__ void merge_partials_kernel(const float* __restrict__ partials, int pa
   }
 }
 
+// Runs after a decode launch that stored this rank's rows into the peers' buffers.  That
+// kernel has ended, so its stores are complete; one thread fences at system scope,
+// advances this rank's step counter and stores the new value into every rank's arrival
+// word for this rank.
+struct FlagPointers {
+  uint32_t* rank[RT_MAX_PEERS];
+};
+__global__ void exchange_signal_kernel(uint32_t* step, FlagPointers flags, int world, int rank) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  __threadfence_system();
+  const uint32_t epoch = *step + 1u;
+  *step = epoch;
+  for (int r = 0; r < world; r++)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.rank[r] + rank), "r"(epoch)
+                 : "memory");
+}
+
 // The same merge over the rows the ranks exchanged: buffer holds two halves of
 // [world][units][2+hd]; the half of the step just computed is *step & 1.  Each block
 // first waits until every rank's arrival word has reached *step (the decode kernels of
@@ -74,17 +91,21 @@ __global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
   if (threadIdx.x == 0) sOk = 1;
   __syncthreads();
   if ((int)threadIdx.x < world) {
-    const volatile uint32_t* f = flags + threadIdx.x;
+    // An acquire load at system scope pairs with the peer's fence + store: once the
+    // word is seen, the rows stored before it are visible too (no full fence needed,
+    // which costs microseconds in every block).
+    const uint32_t* f = flags + threadIdx.x;
     bool arrived = false;
     for (int i = 0; i < (1 << 20); i++) {   // about a second with the sleeps below
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
       // signed distance: a peer may already be a step ahead
-      if ((int32_t)(*f - epoch) >= 0) { arrived = true; break; }
+      if ((int32_t)(seen - epoch) >= 0) { arrived = true; break; }
       __nanosleep(i < 64 ? 100 : 1000);
     }
     if (!arrived) sOk = 0;
   }
   __syncthreads();
-  __threadfence_system();  // the peers' rows, stored before their signal, are read below
   const int lane = threadIdx.x & 31;
   const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (!sOk) {
@@ -293,6 +314,14 @@ cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes
     write_rows_kernel<uint16_t><<<blocks(n), threads, 0, s>>>(
         reinterpret_cast<uint16_t*>(d), static_cast<const uint16_t*>(src), n);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_exchange_signal(uint32_t* step, uint32_t* const* flags, int world, int rank,
+                                   cudaStream_t s) {
+  FlagPointers f{};
+  for (int r = 0; r < world && r < RT_MAX_PEERS; r++) f.rank[r] = flags[r];
+  exchange_signal_kernel<<<1, 32, 0, s>>>(step, f, world, rank);
   return cudaGetLastError();
 }
 

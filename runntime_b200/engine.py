@@ -173,21 +173,20 @@ def shard_rows(total: int, world: int, rank: int) -> Tuple[int, int]:
 def exchange_words(world: int, units: int, headDim: int) -> Tuple[int, int]:
     """(floats of one rank's partials buffer, 32-bit words of its control block)
     for the cross-GPU exchange: two halves of [world, units, 2+headDim] partials;
-    [world] arrival words + step counter + finished-block counter."""
-    return 2 * world * units * (2 + headDim), world + 2
+    [world] arrival words + step counter."""
+    return 2 * world * units * (2 + headDim), world + 1
 
 
 def make_exchange(world: int, rank: int, partialPtrs, controlPtrs) -> Exchange:
     """rt_exchange over every rank's partials buffer and control block as mapped in
     this process (``controlPtrs[r]``: rank r's [world] arrival words, then its step
-    counter, then its finished-block counter, all zero at the start)."""
+    counter, all zero at the start)."""
     x = Exchange()
     x.world, x.rank = world, rank
     for r in range(world):
         x.partials[r] = _ptr(partialPtrs[r])
         x.flags[r] = _ptr(controlPtrs[r])
     x.step = _ptr(controlPtrs[rank]) + 4 * world
-    x.done = _ptr(controlPtrs[rank]) + 4 * (world + 1)
     return x
 
 

@@ -222,6 +222,5 @@ def test_peer_exchange_of_partials_emulated_on_one_gpu(ex, world, splits, dtype)
                                         f"step {step} rank {r} seq {b}")
             assert all(int(c[world].item()) == step + 1 for c in control)      # step counters
             assert all((c[:world] == step + 1).all().item() for c in control)  # arrival words
-            assert all(int(c[world + 1].item()) == 0 for c in control)         # block counters reset
     finally:
         ex.setStream(None)

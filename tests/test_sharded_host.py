@@ -94,11 +94,11 @@ def test_exchange_layout_of_buffers_and_control_words():
     from runntime_b200.engine import exchange_words, make_exchange
     world, units, hd = 4, 512 * 8, 52
     nfloat, nword = exchange_words(world, units, hd)
-    assert nfloat == 2 * world * units * 54 and nword == world + 2
+    assert nfloat == 2 * world * units * 54 and nword == world + 1
     bufs = [0x10000000 + r * 0x1000000 for r in range(world)]
     ctl = [0x90000000 + r * 0x100 for r in range(world)]
     x = make_exchange(world, 2, bufs, ctl)
     assert (x.world, x.rank) == (4, 2)
     assert [x.partials[r] for r in range(world)] == bufs and x.partials[4] is None
     assert [x.flags[r] for r in range(world)] == ctl
-    assert x.step == ctl[2] + 4 * world and x.done == ctl[2] + 4 * (world + 1)
+    assert x.step == ctl[2] + 4 * world
