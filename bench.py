@@ -148,11 +148,42 @@ class Prefill:
         self.hout = t.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
 
     def e2e_step(self, layer=0):
-        self.q.copy_(self.hq, non_blocking=True)
-        self.k.copy_(self.hk, non_blocking=True)
-        self.v.copy_(self.hv, non_blocking=True)
-        self.step(layer)
-        self.hout.copy_(self.out, non_blocking=True)
+        """Host buffers in, host buffer out, pipelined over groups of sequences: the
+        upload of group g+1, the attention of group g and the download of group g-1 run
+        on three streams (the two PCIe directions and the SMs work at the same time)."""
+        from runntime_b200.engine import prefill_batched
+        t, c = self.torch, self.cfg
+        if self.nb == 0:
+            return
+        per = 8 if self.nb >= 16 else self.nb        # sequences per group
+        if not hasattr(self, "_streams"):
+            self._streams = (t.cuda.Stream(), t.cuda.Stream(), t.cuda.Stream())
+        up, run, down = self._streams
+        main = t.cuda.current_stream()
+        for st in self._streams:
+            st.wait_stream(main)
+        wl, wr = self.windows(layer)
+        S = c["seq"]
+        for b0 in range(0, self.nb, per):
+            b1 = min(b0 + per, self.nb)
+            r0, r1 = b0 * S, b1 * S
+            with t.cuda.stream(up):
+                self.q[r0:r1].copy_(self.hq[r0:r1], non_blocking=True)
+                self.k[r0:r1].copy_(self.hk[r0:r1], non_blocking=True)
+                self.v[r0:r1].copy_(self.hv[r0:r1], non_blocking=True)
+            run.wait_stream(up)
+            with t.cuda.stream(run):
+                self.ex.setStream(run.cuda_stream)
+                prefill_batched(self.ex, self.q[r0:r1], self.k[r0:r1], self.v[r0:r1], self.out[r0:r1],
+                                dtype=c["dtype"], batch=b1 - b0, seqStride=S,
+                                seqLens=self.lens[b0:b1], qHeads=c["qHeads"],
+                                kvHeads=c["kvHeads"], headDim=c["hd"], windowLeft=wl,
+                                windowRight=wr)
+            down.wait_stream(run)
+            with t.cuda.stream(down):
+                self.hout[r0:r1].copy_(self.out[r0:r1], non_blocking=True)
+        self.ex.setStream(main.cuda_stream)
+        main.wait_stream(down)
 
 
 class Decode:
