@@ -280,6 +280,28 @@ RT_API int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* s
                    int64_t rows, int64_t cols, int32_t headDim, int64_t srcStart, int64_t width,
                    int32_t dtype);
 
+/* ---- matmul: the projections either side of attention ---------------------------
+ * out [m, n] = act(a [m, k] * B + bias [n]) + addend [m, n], B = rows
+ * [baseRow, baseRow+k) of b [bRows, n] (a view into a taller fused weight; baseRow 0
+ * and bRows = k for a plain weight).  bias and addend may be NULL.  activation:
+ * 0 none, 1 tanh, 2 gelu, 3 silu, 4 relu, 5 geluTanh, 6 elu
+ * (packages/runntime/src/core/kernels/activations.ts:6-14), applied before the
+ * addend.  All tensors in `dtype`, f32 accumulation.  Replaces the 'matmul' op for
+ * plain f32/f16 weights: the fused qkv / q / kv projections and o_proj with its
+ * residual addend (packages/runntime/src/core/graph/ops/matmul.ts:28-99;
+ * packages/runntime/src/core/nn/layers.ts:252-263).  Quantized weights are not
+ * covered. */
+RT_API int rt_matmul(rt_ctx* ctx, const void* a, const void* b, const void* bias,
+                     const void* addend, void* out, int64_t m, int64_t k, int64_t n, int64_t bRows,
+                     int64_t baseRow, int32_t activation, int32_t dtype);
+
+/* ---- argmaxDot: fused gemv + argmax, the greedy decoding head ---------------------
+ * out[0] (f32) = the row index v of w [rows, cols] with the largest w[v] . x
+ * (x one row of `cols`), the lowest index on ties; the logits are never written
+ * (packages/runntime/src/core/graph/ops/matmul.ts:316-333). */
+RT_API int rt_argmax_dot(rt_ctx* ctx, const void* w, const void* x, float* out, int64_t rows,
+                         int64_t cols, int32_t dtype);
+
 /* ---- localAttention: short causal window with soft-capped, biased scores -------
  * qkv [rows, 3*heads*headDim] (columns q|k|v); row t of each head sees keys
  * t-window+1 .. t (window <= 32).  The score of the key j rows back is

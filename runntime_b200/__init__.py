@@ -11,12 +11,13 @@ there is no CPU path.
 from .errors import RUNNTIME_ERROR_CODES, RunntimeError
 from .executor import CudaExecutor, evalValues, gpuExecutor, toArray
 from .nn import MultiHeadAttention, Parameter
-from .ops import chunk, localAttention, rope, sdpa, sdpaPacked, slice, softmax, writeRows
+from .ops import (ACT_CODE, argmaxDot, chunk, localAttention, matmul, rope, sdpa, sdpaPacked,
+                  slice, softmax, writeRows)
 from .value import DeviceBuffer, Value, ValueMeta, materialized, matrix, pending
 
 __all__ = [
     "RUNNTIME_ERROR_CODES", "RunntimeError", "CudaExecutor", "gpuExecutor", "evalValues",
     "toArray", "MultiHeadAttention", "Parameter", "rope", "sdpa", "sdpaPacked", "writeRows",
-    "slice", "chunk", "softmax", "localAttention",
+    "slice", "chunk", "softmax", "localAttention", "matmul", "argmaxDot", "ACT_CODE",
     "DeviceBuffer", "Value", "ValueMeta", "materialized", "matrix", "pending",
 ]

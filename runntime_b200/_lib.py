@@ -82,6 +82,11 @@ SYMBOLS = {
                                          C.c_void_p, C.c_int32]),
     "rt_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                           C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int32]),
+    "rt_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                            C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
+                            C.c_int32]),
+    "rt_argmax_dot": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                C.c_int64, C.c_int32]),
     "rt_local_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                      C.c_float, C.c_int32]),

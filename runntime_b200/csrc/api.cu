@@ -550,6 +550,46 @@ int rt_rope(rt_ctx* ctx, const void* x, const float* cosT, const float* sinT, vo
   return RT_OK;
 }
 
+int rt_matmul(rt_ctx* ctx, const void* a, const void* b, const void* bias, const void* addend,
+              void* out, int64_t m, int64_t k, int64_t n, int64_t bRows, int64_t baseRow,
+              int32_t activation, int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!a || !b || !out) return fail(ctx, RT_INVALID_ARGUMENT, "matmul: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "matmul: both inputs must be f32 or both f16");
+  if (m < 1 || k < 1 || n < 1)
+    return fail(ctx, RT_INVALID_ARGUMENT, "matmul: empty tensor (a=[%lld,%lld] b=[%lld,%lld])",
+                (long long)m, (long long)k, (long long)bRows, (long long)n);
+  if (baseRow < 0 || baseRow + k > bRows)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "matmul: bad baseRow %lld — need integer >= 0 with baseRow+K (%lld) <= rows (%lld)",
+                (long long)baseRow, (long long)k, (long long)bRows);
+  if (activation < 0 || activation > 6)
+    return fail(ctx, RT_INVALID_ARGUMENT,
+                "unknown activation code %d — valid codes are 0..6", activation);
+  const char* bp = static_cast<const char*>(b) + baseRow * n * elem_size(dtype);
+  RT_CUDA(ctx, rt::launch_matmul(a, bp, bias, addend, out, m, k, n, activation, dtype, ctx->stream));
+  ctx->launches += (m > 8 && m <= 16) ? 2 : 1;
+  return RT_OK;
+}
+
+int rt_argmax_dot(rt_ctx* ctx, const void* w, const void* x, float* out, int64_t rows, int64_t cols,
+                  int32_t dtype) {
+  RT_ENTER(ctx);
+  if (!w || !x || !out) return fail(ctx, RT_INVALID_ARGUMENT, "argmaxDot: NULL pointer");
+  if (dtype != RT_F32 && dtype != RT_F16)
+    return fail(ctx, RT_INVALID_ARGUMENT, "argmaxDot: bad dtype %d", dtype);
+  if (rows < 1 || cols < 1 || rows > 0xffffffffll)
+    return fail(ctx, RT_INVALID_ARGUMENT, "argmaxDot: empty or oversized tensor (%lld x %lld)",
+                (long long)rows, (long long)cols);
+  int s = ensure_scratch(ctx, 64, 1);
+  if (s != RT_OK) return s;
+  RT_CUDA(ctx, rt::launch_argmax_dot(w, x, out, rows, cols, dtype,
+                                     reinterpret_cast<unsigned long long*>(ctx->scratch), ctx->stream));
+  ctx->launches += 2;
+  return RT_OK;
+}
+
 int rt_local_attention(rt_ctx* ctx, const void* qkv, const float* rel, const float* qScale,
                        void* out, int64_t rows, int32_t heads, int32_t headDim, int32_t window,
                        float kScale, float softcap, int32_t dtype) {

@@ -169,6 +169,29 @@ class CudaExecutor:
             self._dispatch_slice(node, inputs, out)
         elif op == "softmax":
             self._dispatch_softmax(node, inputs, out)
+        elif op == "matmul":
+            hasBias, hasAddend, act, baseRow, _ = (int(v) for v in node.pending.attrs)
+            ins = node.pending.inputs
+            m, k = ins[0].shape.dims
+            bRows, n = ins[1].shape.dims
+            nxt = 2
+            bias = addend = None
+            if hasBias:
+                bias = C.c_void_p(inputs[nxt].ptr)
+                nxt += 1
+            if hasAddend:
+                addend = C.c_void_p(inputs[nxt].ptr)
+            check(self._lib.rt_matmul(self.ctx, C.c_void_p(inputs[0].ptr), C.c_void_p(inputs[1].ptr),
+                                      bias, addend, C.c_void_p(out.ptr), m, k, n, bRows, baseRow,
+                                      act, DTYPE_CODE[node.shape.dtype]), self.ctx)
+            self.dispatches.append("matmul")
+        elif op == "argmaxDot":
+            wV = node.pending.inputs[0]
+            rows, cols = wV.shape.dims
+            check(self._lib.rt_argmax_dot(self.ctx, C.c_void_p(inputs[0].ptr),
+                                          C.c_void_p(inputs[1].ptr), C.c_void_p(out.ptr), rows,
+                                          cols, DTYPE_CODE[wV.shape.dtype]), self.ctx)
+            self.dispatches.append("argmaxDot")
         elif op == "localAttention":
             heads, hd, window, kScale, softcap = node.pending.attrs
             check(self._lib.rt_local_attention(

@@ -210,6 +210,64 @@ def rope(x: Value, cos: Value, sin: Value, opts: dict) -> Value:
                    [int(headDim), int(srcStart), int(w)])
 
 
+ACT_CODE = {"none": 0, "tanh": 1, "gelu": 2, "silu": 3, "relu": 4, "geluTanh": 5, "elu": 6}
+
+
+def matmul(a: Value, b: Value, opts: Optional[dict] = None) -> Value:
+    """2D matrix multiply, a [M,K] x b [K,N] to [M,N], with the fused bias,
+    activation and addend epilogue: act(a·b + bias) + addend.  ``baseRow`` views K
+    rows of a taller fused b.  Plain f32/f16 weights only (quantized weights are
+    not built).  packages/runntime/src/core/graph/ops/matmul.ts:28-99."""
+    opts = opts or {}
+    if any(opts.get(k) for k in ("scales", "bits", "groupSize")) or b.shape.dtype == "quantW":
+        raise ValueError("matmul: quantW weights are not supported by this build")
+    ad, bd = a.shape.dims, b.shape.dims
+    if ad is None or len(ad) != 2 or bd is None or len(bd) != 2:
+        raise ValueError("matmul: both inputs must be 2D matrices (use matrix())")
+    if a.shape.dtype != b.shape.dtype or a.shape.dtype not in FLOAT_DTYPES:
+        raise ValueError("matmul: both inputs must be f32 or both f16, got "
+                         f"{a.shape.dtype} and {b.shape.dtype}")
+    dtype = a.shape.dtype
+    m, k = ad
+    rows, n = bd
+    baseRow = opts.get("baseRow")
+    base = 0 if baseRow is None else baseRow
+    if not _is_int(base) or base < 0 or base + k > rows:
+        raise ValueError(f"matmul: bad baseRow {_js(base)} — need integer >= 0 with baseRow+K "
+                         f"({k}) <= rows ({rows})")
+    if baseRow is None and k != rows:
+        raise ValueError(f"matmul: inner dims disagree — a=[{m},{k}] b=[{rows},{n}]")
+    bias, addend = opts.get("bias"), opts.get("addend")
+    if bias is not None and (bias.shape.dtype != dtype or bias.shape.elems != n):
+        raise ValueError(f"matmul: bias must be {dtype} [N] = {n} elems, got "
+                         f"({bias.shape.elems},{bias.shape.dtype})")
+    if addend is not None and (addend.shape.dtype != dtype or addend.shape.elems != m * n):
+        raise ValueError(f"matmul: addend must be {dtype} [M,N] = {m * n} elems, got "
+                         f"({addend.shape.elems},{addend.shape.dtype})")
+    act = opts.get("activation")
+    if act is not None and act not in ACT_CODE:
+        raise ValueError(f"matmul: unknown activation {act}")
+    inputs = [a, b] + ([bias] if bias is not None else []) + ([addend] if addend is not None else [])
+    return pending(ValueMeta(m * n, dtype, (m, n)), "matmul", inputs, None,
+                   [1 if bias is not None else 0, 1 if addend is not None else 0,
+                    ACT_CODE[act] if act else 0, int(base), 0 if baseRow is None else 1])
+
+
+def argmaxDot(w: Value, x: Value) -> Value:
+    """Fused gemv and argmax for greedy decoding: w [V,N] · x [1,N] to the argmax
+    row index, lowest on ties; always f32
+    (packages/runntime/src/core/graph/ops/matmul.ts:316-333)."""
+    _, n, wDtype = want2d("argmaxDot.w", w, FLOAT_DTYPES)
+    xr, xn, xDtype = want2d("argmaxDot.x", x, FLOAT_DTYPES)
+    if xr != 1:
+        raise ValueError(f"argmaxDot: x must be a single row, got {xr}")
+    if xn != n:
+        raise ValueError(f"argmaxDot: x cols {xn} != w cols {n}")
+    if wDtype != xDtype:
+        raise ValueError(f"argmaxDot: w dtype {wDtype} must match x's {xDtype}")
+    return pending(ValueMeta(1, "f32", (1, 1)), "argmaxDot", [w, x])
+
+
 ATTN_LOCAL_MAX_WINDOW = 32  # most keys a query of localAttention sees
 
 

@@ -350,3 +350,49 @@ def test_local_attention_rejects(over, error):
     qScale = input_(*over.get("qScale", ([HD],)))
     with pytest.raises(ValueError, match=error):
         localAttention(qkv, rel, qScale, dict(LOCAL, **over.get("opts", {})))
+
+
+# ---- matmul / argmaxDot (packages/runntime/test/core/graph/ops/matmul.test.ts) -------
+
+from runntime_b200 import ACT_CODE, argmaxDot, matmul  # noqa: E402
+
+
+@pytest.mark.parametrize("a,b,out", [([2, 3], [3, 5], [2, 5]), ([1, 288], [288, 864], [1, 864]),
+                                     ([4, 3], [3, 1], [4, 1]), ([1, 1], [1, 1], [1, 1])])
+def test_matmul_shapes(a, b, out):
+    c = matmul(input_(a), input_(b))
+    assert c.shape == meta(out) and c.pending.op == "matmul"
+    assert matmul(input_([2, 3], "f16"), input_([3, 5], "f16")).shape == meta([2, 5], "f16")
+
+
+def test_matmul_epilogue_inputs_and_attrs():
+    a, b, bias, addend = input_([2, 3]), input_([3, 5]), input_([5]), input_([2, 5])
+    c = matmul(a, b, dict(bias=bias, addend=addend, activation="gelu"))
+    assert list(c.pending.inputs) == [a, b, bias, addend]
+    assert list(c.pending.attrs) == [1, 1, ACT_CODE["gelu"], 0, 0]   # hasBias, hasAddend, act, baseRow, hasBaseRow
+    assert list(matmul(a, b, dict(activation="geluTanh")).pending.attrs) == [0, 0, 5, 0, 0]
+    assert list(matmul(a, input_([9, 5]), dict(baseRow=6)).pending.attrs) == [0, 0, 0, 6, 1]
+
+
+@pytest.mark.parametrize("a,b,opts,error", [
+    ([2, 3], ([4, 5],), {}, r"inner dims disagree — a=\[2,3\] b=\[4,5\]"),
+    ([6], ([6, 2],), {}, r"must be 2D"),
+    ([2, 3], ([3, 5], "f16"), {}, r"must be f32 or both f16, got f32 and f16"),
+    ([2, 3], ([3, 5],), dict(bias=([3],)), r"bias must be f32 \[N\] = 5 elems"),
+    ([2, 3], ([3, 5],), dict(bias=([5], "f16")), r"bias must be f32"),
+    ([2, 3], ([3, 5],), dict(addend=([5],)), r"addend must be f32 \[M,N\] = 10 elems"),
+    ([2, 3], ([9, 5],), dict(baseRow=7), r"bad baseRow 7"),
+])
+def test_matmul_rejects(a, b, opts, error):
+    o = {k: (input_(*v) if isinstance(v, tuple) else v) for k, v in opts.items()}
+    with pytest.raises(ValueError, match=error):
+        matmul(input_(a), input_(*b), o)
+
+
+def test_argmax_dot_gives_one_f32_index():
+    assert argmaxDot(input_([50000, 16], "f16"), input_([1, 16], "f16")).shape == meta([1, 1])
+    for x, error in ((input_([2, 16]), r"must be a single row, got 2"),
+                     (input_([1, 8]), r"x cols 8 != w cols 16"),
+                     (input_([1, 16], "f16"), r"must match x's f16")):
+        with pytest.raises(ValueError, match=error):
+            argmaxDot(input_([100, 16]), x)
