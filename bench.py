@@ -2,7 +2,7 @@
 """Benchmark of the attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c4|c3|c2|c1]
-    python bench.py --workload rope|softmax|local|step   # the operators beside attention
+    python bench.py --workload rope|softmax|local|step|gemv|argmax   # the operators beside attention
     python bench.py --impl reference ...        # the CPU restatement, host cores
 
 One JSON line on stdout (rank 0).  The default workload is the large causal
@@ -677,6 +677,8 @@ AUX = {
     "softmax": dict(name="masked_softmax_f16_16384x16384_causal_2_segments", n=16384),
     "local": dict(name="local_attention_f16_T262144_8x128_window12", rows=262144, heads=8, hd=128,
                   window=12),
+    "gemv": dict(name="decode_projection_f16_m8_k4096_n12288_bias_addend", m=8, k=4096, n=12288),
+    "argmax": dict(name="greedy_head_argmaxdot_f16_v262144_n2048", rows=262144, cols=2048),
     "step": dict(name="moonshine_tiny_decoder_layer_step_f16_batch64_rope_append_attend",
                  batch=64, heads=8, hd=36, maxPos=448),
 }
@@ -752,6 +754,35 @@ def run_aux(args):
         rl, q1 = rel.cpu().numpy(), qs.cpu().numpy()
         cpu = lambda: oracle.local_attention_ref(xs, rl, q1, heads=H, headDim=hd, window=wn)
         cpu_work, sample = m * 4 * w * 2, f"{m} of {R} rows (f64 restatement)"
+    elif key == "gemv":
+        M, K, N = cfg["m"], cfg["k"], cfg["n"]
+        a = torch.randn(M, K, generator=g, device=dev, dtype=torch.float16)
+        b = (torch.randn(K, N, generator=g, device=dev) / 64).to(torch.float16)
+        bias = torch.randn(N, generator=g, device=dev, dtype=torch.float16)
+        add = torch.randn(M, N, generator=g, device=dev, dtype=torch.float16)
+        out = torch.empty(M, N, device=dev, dtype=torch.float16)
+        step = lambda i: check(lib.rt_matmul(ex.ctx, ptr(a), ptr(b), ptr(bias), ptr(add), ptr(out),
+                                             M, K, N, K, 0, 0, f16), ex.ctx)
+        work = (K * N + M * K + N + 2 * M * N) * 2     # the weight, read once, dominates
+        host_in, host_out = [a], out
+        kk, nn = 1024, 3072
+        a1 = np.random.default_rng(1).standard_normal((M, kk)).astype(np.float32)
+        b1 = np.random.default_rng(2).standard_normal((kk, nn)).astype(np.float32)
+        cpu = lambda: a1 @ b1
+        cpu_work, sample = (kk * nn + M * kk + M * nn) * 2, f"[{M},{kk}] x [{kk},{nn}] numpy f32 (BLAS)"
+    elif key == "argmax":
+        R, W = cfg["rows"], cfg["cols"]
+        w = torch.randn(R, W, generator=g, device=dev, dtype=torch.float16)
+        x = torch.randn(1, W, generator=g, device=dev, dtype=torch.float16)
+        out = torch.empty(1, device=dev, dtype=torch.float32)
+        step = lambda i: check(lib.rt_argmax_dot(ex.ctx, ptr(w), ptr(x), ptr(out), R, W, f16), ex.ctx)
+        work = (R * W + W) * 2 + 4
+        host_in, host_out = [x], out
+        r1 = 16384
+        w1 = np.random.default_rng(1).standard_normal((r1, W)).astype(np.float32)
+        x1 = np.random.default_rng(2).standard_normal(W).astype(np.float32)
+        cpu = lambda: int(np.argmax(w1 @ x1))
+        cpu_work, sample = r1 * W * 2, f"{r1} of {R} rows, numpy f32 gemv + argmax"
     else:  # step: rope x2 + slice + writeRows x2 + attention of one decoder layer, batch of sequences
         from runntime_b200.engine import decode_batched
         B, H, hd, P = cfg["batch"], cfg["heads"], cfg["hd"], cfg["maxPos"]

@@ -568,8 +568,14 @@ int rt_matmul(rt_ctx* ctx, const void* a, const void* b, const void* bias, const
     return fail(ctx, RT_INVALID_ARGUMENT,
                 "unknown activation code %d — valid codes are 0..6", activation);
   const char* bp = static_cast<const char*>(b) + baseRow * n * elem_size(dtype);
-  RT_CUDA(ctx, rt::launch_matmul(a, bp, bias, addend, out, m, k, n, activation, dtype, ctx->stream));
-  ctx->launches += (m > 8 && m <= 16) ? 2 : 1;
+  const size_t need = rt::matmul_scratch_need(m, k, n, dtype);
+  if (need) {
+    const int s = ensure_scratch(ctx, need, 1);
+    if (s != RT_OK) return s;
+  }
+  RT_CUDA(ctx, rt::launch_matmul(a, bp, bias, addend, out, m, k, n, activation, dtype,
+                                 need ? ctx->scratch : nullptr, ctx->stream));
+  ctx->launches += ((m > 8 && m <= 16) ? 2 : 1) + (need ? 1 : 0);
   return RT_OK;
 }
 

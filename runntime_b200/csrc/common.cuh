@@ -198,9 +198,11 @@ cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, c
 cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
                         int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
                         int dtype, cudaStream_t s);
+// Scratch (f32 partial sums of the K slices) a matmul of this shape wants; 0 = none.
+size_t matmul_scratch_need(int64_t M, int64_t K, int64_t N, int dtype);
 cudaError_t launch_matmul(const void* a, const void* b, const void* bias, const void* addend,
                           void* out, int64_t M, int64_t K, int64_t N, int act, int dtype,
-                          cudaStream_t s);
+                          float* scratch, cudaStream_t s);
 cudaError_t launch_argmax_dot(const void* w, const void* x, float* out, int64_t V, int64_t N,
                               int dtype, unsigned long long* scratch, cudaStream_t s);
 cudaError_t launch_local_attn(const void* qkv, const float* rel, const float* qScale, void* out,

@@ -8,11 +8,12 @@
 // Two kernels, both on the FP32 pipes with f32 accumulation:
 //  - skinny (M <= 16, the decode step): weight-bandwidth bound.  A block owns a strip of
 //    32 sixteen-byte column groups; its eight warps split K, every warp streaming whole
-//    512-byte row pieces of b with 16-byte loads while the few rows of a come from L1;
+//    row pieces of b (8 or 16 bytes per lane) while the few rows of a come from L1;
 //    the warps' sums meet in shared memory.  b is read once (twice for M > 8).
 //  - tiled (any M): 64 x 64 output tile per block, 16-deep K steps through shared memory,
 //    4 x 4 outputs per thread.  This is the general fallback, not a tensor-core GEMM.
 #include <cfloat>
+#include <type_traits>
 #include "common.cuh"
 
 namespace rt {
@@ -60,58 +61,113 @@ __device__ __forceinline__ void load_vec<__half>(const __half* p, float (&f)[8])
   }
 }
 
-// ---- skinny: M <= MR rows per pass, N a multiple of the vector width -----------------
+// ---- skinny: M <= 8 rows per pass, N a multiple of the vector width ----------------------
+// A block owns a strip of 256 sixteen-byte column groups (4 KB of every row of b,
+// contiguous in memory: narrow strips waste most of each DRAM page) and a slice of K.
+// Every thread keeps its own 8 x V accumulators, takes eight rows of b per step (eight
+// 16-byte loads in flight, kept packed until used) and reads a from shared memory, where
+// the block's rows of a for its K slice are staged as f32 once.  With one slice the
+// epilogue is applied here; with more, the sums are added into `partial` [M][N] f32
+// (zeroed before the launch) and matmul_skinny_finish_kernel applies the epilogue.
 constexpr int kSkinnyThreads = 256;
 constexpr int kSkinnyRows = 8;
+constexpr int kSkinnyU = 8;
 
 template <typename T>
-__global__ void __launch_bounds__(kSkinnyThreads)
+__global__ void __launch_bounds__(kSkinnyThreads, 2)
 matmul_skinny_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ bias,
-                     const T* __restrict__ addend, T* __restrict__ out, int m0, int M, int64_t K,
-                     int64_t N, int act) {
-  constexpr int V = 16 / sizeof(T);
-  __shared__ float sAcc[kSkinnyRows][32 * V];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t col = ((int64_t)blockIdx.x * 32 + lane) * V;
+                     const T* __restrict__ addend, T* __restrict__ out, float* __restrict__ partial,
+                     int m0, int M, int64_t K, int64_t N, int kPerSlice, int act) {
+  constexpr int V = 16 / sizeof(T), U = kSkinnyU;
+  extern __shared__ __align__(16) float sA[];          // [kSkinnyRows][kPad]
+  const int64_t col = ((int64_t)blockIdx.x * kSkinnyThreads + threadIdx.x) * V;
   const int rows = min(kSkinnyRows, M - m0);
-  for (int i = threadIdx.x; i < kSkinnyRows * 32 * V; i += kSkinnyThreads)
-    (&sAcc[0][0])[i] = 0.f;
+  const int64_t kBegin = (int64_t)blockIdx.y * kPerSlice;
+  const int kLen = (int)min((int64_t)kPerSlice, K - kBegin);
+  const int kPad = (kPerSlice + U - 1) / U * U;
+  for (int i = threadIdx.x; i < kSkinnyRows * kPad; i += kSkinnyThreads) {
+    const int r = i / kPad, kk = i - r * kPad;
+    sA[i] = (r < rows && kk < kLen) ? to_f32<T>(a[(int64_t)(m0 + r) * K + kBegin + kk]) : 0.f;
+  }
   __syncthreads();
+  const bool inRange = col < N;
   float acc[kSkinnyRows][V];
 #pragma unroll
   for (int r = 0; r < kSkinnyRows; r++)
 #pragma unroll
     for (int v = 0; v < V; v++) acc[r][v] = 0.f;
-  if (col < N) {
-    const T* ap = a + (int64_t)m0 * K;
-    for (int64_t k = warp; k < K; k += kSkinnyThreads / 32) {
-      float bv[V];
-      load_vec<T>(b + k * N + col, bv);
+  const T* bp = b + kBegin * N + col;
+  for (int k0 = 0; inRange && k0 < kLen; k0 += U) {
+    uint4 raw[U];
 #pragma unroll
-      for (int r = 0; r < kSkinnyRows; r++) {
-        if (r < rows) {
-          const float av = to_f32<T>(ap[(int64_t)r * K + k]);  // same address across the warp
-#pragma unroll
-          for (int v = 0; v < V; v++) acc[r][v] = fmaf(av, bv[v], acc[r][v]);
-        }
-      }
+    for (int u = 0; u < U; u++) {
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (k0 + u < kLen) raw[u] = *reinterpret_cast<const uint4*>(bp + (int64_t)(k0 + u) * N);
     }
 #pragma unroll
-    for (int r = 0; r < kSkinnyRows; r++)
-      if (r < rows)
+    for (int u4 = 0; u4 < U; u4 += 4) {
+      float bv[4][V];
 #pragma unroll
-        for (int v = 0; v < V; v++) atomicAdd(&sAcc[r][lane * V + v], acc[r][v]);
+      for (int u = 0; u < 4; u++) load_vec<T>(reinterpret_cast<const T*>(&raw[u4 + u]), bv[u]);
+#pragma unroll
+      for (int r = 0; r < kSkinnyRows; r++) {
+        // four consecutive k of row r in one broadcast load; rows past M hold zeros
+        const float4 av = *reinterpret_cast<const float4*>(&sA[r * kPad + k0 + u4]);
+        const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+          for (int v = 0; v < V; v++) acc[r][v] = fmaf(a4[u], bv[u][v], acc[r][v]);
+      }
+    }
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < rows * 32 * V; i += kSkinnyThreads) {
-    const int r = i / (32 * V), c = i - r * (32 * V);
-    const int64_t n = (int64_t)blockIdx.x * 32 * V + c;
-    if (n >= N) continue;
-    float y = sAcc[r][c];
-    if (bias) y += to_f32<T>(bias[n]);
+  if (partial) {
+    // Row by row through shared memory, so that the adds into the f32 accumulator are
+    // coalesced (a lane per consecutive column) instead of eight columns per lane.
+    __syncthreads();                         // everybody is done reading sA
+    float* sRow = sA;                        // kSkinnyThreads * V floats fit: see the launcher
+#pragma unroll
+    for (int r = 0; r < kSkinnyRows; r++) {
+      if (r >= rows) break;
+#pragma unroll
+      for (int v = 0; v < V; v++) sRow[threadIdx.x * V + v] = acc[r][v];
+      __syncthreads();
+      const int64_t n0 = (int64_t)blockIdx.x * kSkinnyThreads * V;
+      for (int c = threadIdx.x; c < kSkinnyThreads * V; c += kSkinnyThreads)
+        if (n0 + c < N) atomicAdd(&partial[(int64_t)(m0 + r) * N + n0 + c], sRow[c]);
+      __syncthreads();
+    }
+    return;
+  }
+  if (!inRange) return;
+#pragma unroll
+  for (int r = 0; r < kSkinnyRows; r++) {
+    if (r >= rows) continue;
+#pragma unroll
+    for (int v = 0; v < V; v++) {
+      const int64_t n = col + v;
+      float y = acc[r][v];
+      if (bias) y += to_f32<T>(bias[n]);
+      y = apply_act(y, act);
+      if (addend) y += to_f32<T>(addend[(int64_t)(m0 + r) * N + n]);
+      out[(int64_t)(m0 + r) * N + n] = from_f32<T>(y);
+    }
+  }
+}
+
+template <typename T>
+__global__ void matmul_skinny_finish_kernel(const float* __restrict__ partial,
+                                            const T* __restrict__ bias,
+                                            const T* __restrict__ addend, T* __restrict__ out,
+                                            int64_t M, int64_t N, int act) {
+  const int64_t total = M * N;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    float y = partial[i];
+    if (bias) y += to_f32<T>(bias[i % N]);
     y = apply_act(y, act);
-    if (addend) y += to_f32<T>(addend[(int64_t)(m0 + r) * N + n]);
-    out[(int64_t)(m0 + r) * N + n] = from_f32<T>(y);
+    if (addend) y += to_f32<T>(addend[i]);
+    out[i] = from_f32<T>(y);
   }
 }
 
@@ -183,14 +239,25 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t idx) 
 template <typename T>
 __global__ void __launch_bounds__(256)
 argmax_dot_kernel(const T* __restrict__ w, const T* __restrict__ x, int64_t V, int64_t N,
-                  unsigned long long* best) {
+                  unsigned long long* best, bool vec) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   unsigned long long mine = 0ull;
   for (int64_t v = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); v < V; v += warps) {
     const T* row = w + v * N;
     float s = 0.f;
-    for (int64_t n = lane; n < N; n += 32) s = fmaf(to_f32<T>(row[n]), to_f32<T>(x[n]), s);
+    if (vec) {
+      constexpr int VV = 16 / sizeof(T);
+      for (int64_t n = (int64_t)lane * VV; n < N; n += 32 * VV) {
+        float wv[VV], xv[VV];
+        load_vec<T>(row + n, wv);
+        load_vec<T>(x + n, xv);
+#pragma unroll
+        for (int e = 0; e < VV; e++) s = fmaf(wv[e], xv[e], s);
+      }
+    } else {
+      for (int64_t n = lane; n < N; n += 32) s = fmaf(to_f32<T>(row[n]), to_f32<T>(x[n]), s);
+    }
     s = warp_sum(s);
     const unsigned long long key = argmax_key(s, (uint32_t)v);
     if (key > mine) mine = key;
@@ -202,42 +269,76 @@ __global__ void argmax_finish_kernel(const unsigned long long* best, float* out)
   out[0] = (float)(0xffffffffu - (uint32_t)(*best & 0xffffffffull));
 }
 
-}  // namespace
 
-cudaError_t launch_matmul(const void* a, const void* b, const void* bias, const void* addend,
-                          void* out, int64_t M, int64_t K, int64_t N, int act, int dtype,
-                          cudaStream_t s) {
-  const int esize = dtype == RT_F16 ? 2 : 4;
-  const int V = 16 / esize;
-  const bool vecOk = N % V == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0;
-  if (M <= 2 * kSkinnyRows && vecOk) {
-    const unsigned grid = (unsigned)((N + 32 * V - 1) / (32 * V));
-    for (int m0 = 0; m0 < M; m0 += kSkinnyRows) {
-      if (dtype == RT_F16)
-        matmul_skinny_kernel<__half><<<grid, kSkinnyThreads, 0, s>>>(
-            static_cast<const __half*>(a), static_cast<const __half*>(b),
-            static_cast<const __half*>(bias), static_cast<const __half*>(addend),
-            static_cast<__half*>(out), m0, (int)M, K, N, act);
-      else
-        matmul_skinny_kernel<float><<<grid, kSkinnyThreads, 0, s>>>(
-            static_cast<const float*>(a), static_cast<const float*>(b),
-            static_cast<const float*>(bias), static_cast<const float*>(addend),
-            static_cast<float*>(out), m0, (int)M, K, N, act);
+// K slices for the skinny kernel: enough blocks for two per SM, at least 32 rows
+// each, and few enough rows that the slice of a fits shared memory.
+int skinny_slices(int64_t K, int64_t strips) {
+  int64_t want = (2 * 148 + strips - 1) / strips;
+  const int64_t maxByRows = K / 32 > 0 ? K / 32 : 1;
+  if (want > maxByRows) want = maxByRows;
+  const int64_t minBySmem = (K + 1023) / 1024;
+  if (want < minBySmem) want = minBySmem;
+  return (int)(want < 1 ? 1 : want);
+}
+
+bool skinny_ok(int64_t M, int64_t N, const void* b, int esize) {
+  return M <= 2 * kSkinnyRows && N % (16 / esize) == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0;
+}
+
+template <typename T>
+cudaError_t matmul_typed(const void* a, const void* b, const void* bias, const void* addend,
+                         void* out, int64_t M, int64_t K, int64_t N, int act, float* scratch,
+                         cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  auto* ai = static_cast<const T*>(a);
+  auto* bi = static_cast<const T*>(b);
+  auto* ci = static_cast<const T*>(bias);
+  auto* di = static_cast<const T*>(addend);
+  auto* oi = static_cast<T*>(out);
+  if (skinny_ok(M, N, b, sizeof(T))) {
+    const int64_t strips = (N + kSkinnyThreads * V - 1) / (kSkinnyThreads * V);
+    const int slices = skinny_slices(K, strips);
+    if (slices > 1 && !scratch) return cudaErrorInvalidValue;
+    const int kPerSlice = (int)((K + slices - 1) / slices);
+    const dim3 grid((unsigned)strips, (unsigned)slices);
+    float* partial = slices > 1 ? scratch : nullptr;
+    if (partial) {
+      cudaError_t e = cudaMemsetAsync(partial, 0, (size_t)M * N * sizeof(float), s);
+      if (e != cudaSuccess) return e;
+    }
+    size_t smem = (size_t)kSkinnyRows * ((kPerSlice + kSkinnyU - 1) / kSkinnyU * kSkinnyU) * 4;
+    if (smem < (size_t)kSkinnyThreads * V * 4) smem = (size_t)kSkinnyThreads * V * 4;
+    for (int m0 = 0; m0 < M; m0 += kSkinnyRows)
+      matmul_skinny_kernel<T><<<grid, kSkinnyThreads, smem, s>>>(ai, bi, ci, di, oi, partial, m0,
+                                                                (int)M, K, N, kPerSlice, act);
+    if (partial) {
+      int64_t blocks = (M * N + 255) / 256;
+      if (blocks > 148 * 8) blocks = 148 * 8;
+      matmul_skinny_finish_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(partial, ci, di, oi, M, N, act);
     }
     return cudaGetLastError();
   }
   const dim3 grid((unsigned)((N + TN - 1) / TN), (unsigned)((M + TM - 1) / TM));
   if (grid.y > 65535) return cudaErrorInvalidValue;
-  if (dtype == RT_F16)
-    matmul_tiled_kernel<__half><<<grid, 256, 0, s>>>(
-        static_cast<const __half*>(a), static_cast<const __half*>(b),
-        static_cast<const __half*>(bias), static_cast<const __half*>(addend),
-        static_cast<__half*>(out), M, K, N, act);
-  else
-    matmul_tiled_kernel<float><<<grid, 256, 0, s>>>(
-        static_cast<const float*>(a), static_cast<const float*>(b), static_cast<const float*>(bias),
-        static_cast<const float*>(addend), static_cast<float*>(out), M, K, N, act);
+  matmul_tiled_kernel<T><<<grid, 256, 0, s>>>(ai, bi, ci, di, oi, M, K, N, act);
   return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t matmul_scratch_need(int64_t M, int64_t K, int64_t N, int dtype) {
+  const int esize = dtype == RT_F16 ? 2 : 4;
+  if (M > 2 * kSkinnyRows || N % (16 / esize) != 0) return 0;
+  const int64_t strips = (N + kSkinnyThreads * (16 / esize) - 1) / (kSkinnyThreads * (16 / esize));
+  return skinny_slices(K, strips) > 1 ? (size_t)M * N * sizeof(float) : 0;
+}
+
+cudaError_t launch_matmul(const void* a, const void* b, const void* bias, const void* addend,
+                          void* out, int64_t M, int64_t K, int64_t N, int act, int dtype,
+                          float* scratch, cudaStream_t s) {
+  return dtype == RT_F16
+             ? matmul_typed<__half>(a, b, bias, addend, out, M, K, N, act, scratch, s)
+             : matmul_typed<float>(a, b, bias, addend, out, M, K, N, act, scratch, s);
 }
 
 cudaError_t launch_argmax_dot(const void* w, const void* x, float* out, int64_t V, int64_t N,
@@ -246,12 +347,15 @@ cudaError_t launch_argmax_dot(const void* w, const void* x, float* out, int64_t 
   if (e != cudaSuccess) return e;
   int64_t blocks = (V + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
+  const int vv = 16 / (dtype == RT_F16 ? 2 : 4);
+  const bool vec = N % vv == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(x) % 16 == 0;
   if (dtype == RT_F16)
     argmax_dot_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(
-        static_cast<const __half*>(w), static_cast<const __half*>(x), V, N, scratch);
+        static_cast<const __half*>(w), static_cast<const __half*>(x), V, N, scratch, vec);
   else
     argmax_dot_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(
-        static_cast<const float*>(w), static_cast<const float*>(x), V, N, scratch);
+        static_cast<const float*>(w), static_cast<const float*>(x), V, N, scratch, vec);
   argmax_finish_kernel<<<1, 1, 0, s>>>(scratch, out);
   return cudaGetLastError();
 }
