@@ -15,6 +15,7 @@
 #include <cfloat>
 #include <type_traits>
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace rt {
 namespace {
@@ -72,6 +73,7 @@ __device__ __forceinline__ void load_vec<__half>(const __half* p, float (&f)[8])
 constexpr int kSkinnyThreads = 256;
 constexpr int kSkinnyRows = 8;
 constexpr int kSkinnyU = 8;
+constexpr int kSkinnyBlocksPerSm = 2;   // measured: 2.01 TB/s against 1.85 with one
 
 template <typename T>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
@@ -136,6 +138,137 @@ matmul_skinny_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* 
       for (int c = threadIdx.x; c < kSkinnyThreads * V; c += kSkinnyThreads)
         if (n0 + c < N) atomicAdd(&partial[(int64_t)(m0 + r) * N + n0 + c], sRow[c]);
       __syncthreads();
+    }
+    return;
+  }
+  if (!inRange) return;
+#pragma unroll
+  for (int r = 0; r < kSkinnyRows; r++) {
+    if (r >= rows) continue;
+#pragma unroll
+    for (int v = 0; v < V; v++) {
+      const int64_t n = col + v;
+      float y = acc[r][v];
+      if (bias) y += to_f32<T>(bias[n]);
+      y = apply_act(y, act);
+      if (addend) y += to_f32<T>(addend[(int64_t)(m0 + r) * N + n]);
+      out[(int64_t)(m0 + r) * N + n] = from_f32<T>(y);
+    }
+  }
+}
+
+// ---- skinny, fed by a bulk-copy ring ---------------------------------------------------
+// The same decomposition (a block = 4 KB of every row of b in a slice of K), but the rows
+// arrive in shared memory through a ring of cp.async.bulk stages issued by a producer
+// warp, so that tens of kilobytes per SM are in flight however few registers the
+// consumers have; the consumers (one per sixteen-byte column group) read their piece of
+// each row from shared memory.  Needs N * sizeof(T) a multiple of 16 and aligned bases.
+constexpr int kRingRows = 4;      // rows of b per stage (16 KB)
+constexpr int kRingStages = 5;    // 80 KB of b in flight per block, two blocks per SM
+
+template <typename T>
+__global__ void __launch_bounds__(kSkinnyThreads + 32, 2)
+matmul_skinny_ring_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                          const T* __restrict__ bias, const T* __restrict__ addend,
+                          T* __restrict__ out, float* __restrict__ partial, int m0, int M, int64_t K,
+                          int64_t N, int kPerSlice, int act) {
+  using namespace sm100;
+  constexpr int V = 16 / sizeof(T), R = kRingRows, S = kRingStages;
+  constexpr int kStripBytes = kSkinnyThreads * 16;             // 4 KB of one row
+  extern __shared__ __align__(128) unsigned char smemRaw[];
+  __shared__ __align__(8) uint64_t sFull[S], sEmpty[S];
+  __shared__ int sAbort;
+  unsigned char* ring = smemRaw;                                // [S][R][kStripBytes]
+  float* sA = reinterpret_cast<float*>(smemRaw + (size_t)S * R * kStripBytes);  // [rows][kPad]
+  const int tid = threadIdx.x;
+  const int64_t col0 = (int64_t)blockIdx.x * kSkinnyThreads * V;
+  const int64_t colsHere = min((int64_t)kSkinnyThreads * V, N - col0);
+  const uint32_t rowBytes = (uint32_t)(colsHere * sizeof(T));    // a multiple of 16
+  const int rows = min(kSkinnyRows, M - m0);
+  const int64_t kBegin = (int64_t)blockIdx.y * kPerSlice;
+  const int kLen = (int)min((int64_t)kPerSlice, K - kBegin);
+  const int kPad = (kPerSlice + 3) / 4 * 4;
+  const int nTiles = (kLen + R - 1) / R;
+  if (tid == 0) {
+    sAbort = 0;
+    for (int i = 0; i < S; i++) {
+      mbar_init(smem_u32(&sFull[i]), 1);
+      mbar_init(smem_u32(&sEmpty[i]), kSkinnyThreads / 32);
+    }
+    fence_barrier_init();
+  }
+  for (int i = tid; i < kSkinnyRows * kPad; i += kSkinnyThreads + 32) {
+    const int r = i / kPad, kk = i - r * kPad;
+    sA[i] = (r < rows && kk < kLen) ? to_f32<T>(a[(int64_t)(m0 + r) * K + kBegin + kk]) : 0.f;
+  }
+  __syncthreads();
+
+  if (tid >= kSkinnyThreads) {
+    // ---------------- producer warp ----------------
+    if (tid == kSkinnyThreads) {
+      const T* src = b + kBegin * N + col0;
+      for (int it = 0; it < nTiles; it++) {
+        const int st = it % S;
+        if (it >= S && !mbar_wait(smem_u32(&sEmpty[st]), ((it / S) - 1) & 1, &sAbort)) break;
+        const int nr = min(R, kLen - it * R);
+        mbar_expect_tx(smem_u32(&sFull[st]), (uint32_t)nr * rowBytes);
+        for (int r = 0; r < nr; r++)
+          bulk_g2s(smem_u32(ring + ((size_t)st * R + r) * kStripBytes),
+                   src + (int64_t)(it * R + r) * N, rowBytes, smem_u32(&sFull[st]));
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers: one sixteen-byte column group each ----------------
+  const bool inRange = (int64_t)tid * V < colsHere;
+  float acc[kSkinnyRows][V];
+#pragma unroll
+  for (int r = 0; r < kSkinnyRows; r++)
+#pragma unroll
+    for (int v = 0; v < V; v++) acc[r][v] = 0.f;
+  bool ok = true;
+  for (int it = 0; it < nTiles; it++) {
+    const int st = it % S;
+    if (!mbar_wait(smem_u32(&sFull[st]), (it / S) & 1, &sAbort)) { ok = false; break; }
+    const int nr = min(R, kLen - it * R);
+    if (inRange) {
+#pragma unroll
+      for (int u = 0; u < R; u++) {
+        if (u < nr) {
+          float bv[V];
+          load_vec<T>(reinterpret_cast<const T*>(ring + ((size_t)st * R + u) * kStripBytes) + tid * V, bv);
+#pragma unroll
+          for (int r = 0; r < kSkinnyRows; r++) {
+            const float av = sA[r * kPad + it * R + u];  // broadcast; rows past M hold zeros
+#pragma unroll
+            for (int v = 0; v < V; v++) acc[r][v] = fmaf(av, bv[v], acc[r][v]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(smem_u32(&sEmpty[st]));
+  }
+  // Every consumer comes here, also one whose wait ran out (the others' waits then end at
+  // their next look at the abort word), so the decision below is the same for all.
+  (void)ok;
+  named_barrier_sync(1, kSkinnyThreads);
+  if (sAbort) return;          // a bounded wait ran out: leave the output untouched
+  const int64_t col = col0 + (int64_t)tid * V;
+  if (partial) {
+    // Row by row through shared memory (the ring is free now), so that the adds into the
+    // f32 accumulator are coalesced: a lane per consecutive column.
+    float* sRow = reinterpret_cast<float*>(ring);
+#pragma unroll
+    for (int r = 0; r < kSkinnyRows; r++) {
+      if (r >= rows) break;
+#pragma unroll
+      for (int v = 0; v < V; v++) sRow[tid * V + v] = acc[r][v];
+      named_barrier_sync(1, kSkinnyThreads);
+      for (int c = tid; c < colsHere; c += kSkinnyThreads)
+        atomicAdd(&partial[(int64_t)(m0 + r) * N + col0 + c], sRow[c]);
+      named_barrier_sync(1, kSkinnyThreads);
     }
     return;
   }
@@ -273,7 +406,7 @@ __global__ void argmax_finish_kernel(const unsigned long long* best, float* out)
 // K slices for the skinny kernel: enough blocks for two per SM, at least 32 rows
 // each, and few enough rows that the slice of a fits shared memory.
 int skinny_slices(int64_t K, int64_t strips) {
-  int64_t want = (2 * 148 + strips - 1) / strips;
+  int64_t want = (kSkinnyBlocksPerSm * 148 + strips - 1) / strips;
   const int64_t maxByRows = K / 32 > 0 ? K / 32 : 1;
   if (want > maxByRows) want = maxByRows;
   const int64_t minBySmem = (K + 1023) / 1024;
@@ -308,9 +441,23 @@ cudaError_t matmul_typed(const void* a, const void* b, const void* bias, const v
     }
     size_t smem = (size_t)kSkinnyRows * ((kPerSlice + kSkinnyU - 1) / kSkinnyU * kSkinnyU) * 4;
     if (smem < (size_t)kSkinnyThreads * V * 4) smem = (size_t)kSkinnyThreads * V * 4;
-    for (int m0 = 0; m0 < M; m0 += kSkinnyRows)
-      matmul_skinny_kernel<T><<<grid, kSkinnyThreads, smem, s>>>(ai, bi, ci, di, oi, partial, m0,
-                                                                (int)M, K, N, kPerSlice, act);
+    // The ring kernel when a's slice fits beside the ring (two blocks per SM).
+    const size_t ringBytes = (size_t)kRingStages * kRingRows * kSkinnyThreads * 16;
+    const size_t ringSmem = ringBytes + (size_t)kSkinnyRows * ((kPerSlice + 3) / 4 * 4) * 4;
+    const bool useRing = ringSmem <= 110 * 1024 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    if (useRing) {
+      auto kern = matmul_skinny_ring_kernel<T>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)ringSmem);
+      if (e != cudaSuccess) return e;
+      for (int m0 = 0; m0 < M; m0 += kSkinnyRows)
+        kern<<<grid, kSkinnyThreads + 32, ringSmem, s>>>(ai, bi, ci, di, oi, partial, m0, (int)M, K,
+                                                         N, kPerSlice, act);
+    } else {
+      for (int m0 = 0; m0 < M; m0 += kSkinnyRows)
+        matmul_skinny_kernel<T><<<grid, kSkinnyThreads, smem, s>>>(ai, bi, ci, di, oi, partial, m0,
+                                                                  (int)M, K, N, kPerSlice, act);
+    }
     if (partial) {
       int64_t blocks = (M * N + 255) / 256;
       if (blocks > 148 * 8) blocks = 148 * 8;
