@@ -568,6 +568,16 @@ int rt_matmul(rt_ctx* ctx, const void* a, const void* b, const void* bias, const
     return fail(ctx, RT_INVALID_ARGUMENT,
                 "unknown activation code %d — valid codes are 0..6", activation);
   const char* bp = static_cast<const char*>(b) + baseRow * n * elem_size(dtype);
+  if (ctx->useTc && rt::matmul_tc_supported(a, bp, out, m, k, n, dtype)) {
+    std::string err;
+    cudaError_t e = rt::launch_matmul_tc(a, bp, bias, addend, out, m, k, n, activation,
+                                         ctx->statusDev, ctx->stream, &err);
+    if (e != cudaSuccess)
+      return fail(ctx, RT_EXECUTION_FAILED, "matmul_tc launch: %s %s", cudaGetErrorString(e),
+                  err.c_str());
+    ctx->launches++;
+    return RT_OK;
+  }
   const size_t need = rt::matmul_scratch_need(m, k, n, dtype);
   if (need) {
     const int s = ensure_scratch(ctx, need, 1);

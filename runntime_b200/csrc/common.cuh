@@ -203,6 +203,12 @@ size_t matmul_scratch_need(int64_t M, int64_t K, int64_t N, int dtype);
 cudaError_t launch_matmul(const void* a, const void* b, const void* bias, const void* addend,
                           void* out, int64_t M, int64_t K, int64_t N, int act, int dtype,
                           float* scratch, cudaStream_t s);
+// Tensor-core path of matmul (f16, more than 16 rows, aligned shapes).
+bool matmul_tc_supported(const void* a, const void* b, const void* out, int64_t M, int64_t K,
+                         int64_t N, int dtype);
+cudaError_t launch_matmul_tc(const void* a, const void* b, const void* bias, const void* addend,
+                             void* out, int64_t M, int64_t K, int64_t N, int act, int* status,
+                             cudaStream_t s, std::string* err);
 cudaError_t launch_argmax_dot(const void* w, const void* x, float* out, int64_t V, int64_t N,
                               int dtype, unsigned long long* scratch, cudaStream_t s);
 cudaError_t launch_local_attn(const void* qkv, const float* rel, const float* qScale, void* out,

@@ -73,6 +73,25 @@ def test_matmul_shapes(ex, dtype, m, k, n):
     check(ex, m, k, n, dtype)
 
 
+TC_SHAPES = [(128, 64, 128), (129, 64, 64), (1000, 1024, 1536), (300, 520, 72), (2048, 288, 864),
+             (17, 4096, 128), (256, 200, 1000)]
+
+
+@pytest.mark.parametrize("m,k,n", TC_SHAPES)
+def test_matmul_on_the_tensor_cores(ex, m, k, n):
+    """f16, more than 16 rows, 16-byte row pitches: the tcgen05 kernel; the same shapes
+    through the FP32-pipe kernel (option off) agree with it."""
+    import runntime_b200 as rt
+    from runntime_b200._lib import OPT_PREFILL_TC
+    check(ex, m, k, n, "f16", bias=True, addend=True, act="silu")
+    check(ex, m, k, n, "f16")
+    ex.setOption(OPT_PREFILL_TC, 0)
+    try:
+        check(ex, m, k, n, "f16")
+    finally:
+        ex.setOption(OPT_PREFILL_TC, 1)
+
+
 @pytest.mark.parametrize("dtype", ["f32", "f16"])
 @pytest.mark.parametrize("m", [1, 5, 40])
 @pytest.mark.parametrize("act", [None, "tanh", "gelu", "silu", "relu", "geluTanh", "elu"])
