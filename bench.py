@@ -2,7 +2,7 @@
 """Benchmark of the attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c4|c3|c2|c1]
-    python bench.py --workload rope|softmax|local|step|gemv|argmax   # the operators beside attention
+    python bench.py --workload rope|softmax|local|step|gemv|gemm|argmax   # the operators beside attention
     python bench.py --impl reference ...        # the CPU restatement, host cores
 
 One JSON line on stdout (rank 0).  The default workload is the large causal
@@ -678,6 +678,7 @@ AUX = {
     "local": dict(name="local_attention_f16_T262144_8x128_window12", rows=262144, heads=8, hd=128,
                   window=12),
     "gemv": dict(name="decode_projection_f16_m8_k4096_n12288_bias_addend", m=8, k=4096, n=12288),
+    "gemm": dict(name="prefill_projection_f16_m32768_k1024_n3072_bias", m=32768, k=1024, n=3072),
     "argmax": dict(name="greedy_head_argmaxdot_f16_v262144_n2048", rows=262144, cols=2048),
     "step": dict(name="moonshine_tiny_decoder_layer_step_f16_batch64_rope_append_attend",
                  batch=64, heads=8, hd=36, maxPos=448),
@@ -754,6 +755,22 @@ def run_aux(args):
         rl, q1 = rel.cpu().numpy(), qs.cpu().numpy()
         cpu = lambda: oracle.local_attention_ref(xs, rl, q1, heads=H, headDim=hd, window=wn)
         cpu_work, sample = m * 4 * w * 2, f"{m} of {R} rows (f64 restatement)"
+    elif key == "gemm":
+        M, K, N = cfg["m"], cfg["k"], cfg["n"]
+        a = torch.randn(M, K, generator=g, device=dev, dtype=torch.float16)
+        b = (torch.randn(K, N, generator=g, device=dev) / 32).to(torch.float16)
+        bias = torch.randn(N, generator=g, device=dev, dtype=torch.float16)
+        out = torch.empty(M, N, device=dev, dtype=torch.float16)
+        step = lambda i: check(lib.rt_matmul(ex.ctx, ptr(a), ptr(b), ptr(bias), None, ptr(out),
+                                             M, K, N, K, 0, 0, f16), ex.ctx)
+        work = 2.0 * M * K * N          # FLOPs: this one is measured against the tensor peak
+        unit = "TFLOP/s"
+        host_in, host_out = [a], out
+        mm = 2048
+        a1 = np.random.default_rng(1).standard_normal((mm, K)).astype(np.float32)
+        b1 = np.random.default_rng(2).standard_normal((K, N)).astype(np.float32)
+        cpu = lambda: a1 @ b1
+        cpu_work, sample = 2.0 * mm * K * N, f"[{mm},{K}] x [{K},{N}] numpy f32 (BLAS)"
     elif key == "gemv":
         M, K, N = cfg["m"], cfg["k"], cfg["n"]
         a = torch.randn(M, K, generator=g, device=dev, dtype=torch.float16)
@@ -815,17 +832,20 @@ def run_aux(args):
     ms = timed(torch, None, 1, step, args.steps, args.warmup, (lambda: flushbuf.fill_(1)) if small else None)
     clocks = sampler.stop() if sampler else None
     launches = (ex.launchCount() - n0) * args.steps // (args.steps + args.warmup)
-    value = work * args.steps / (ms * 1e-3) / 1e9
+    tensor = unit == "TFLOP/s"
+    scale = 1e12 if tensor else 1e9
+    value = work * args.steps / (ms * 1e-3) / scale
+    peak = peaks["tflops"] if tensor else peaks["hbm_gbs"]
     line = {
-        "metric": f"{key}_hbm_gbs", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps,
+        "metric": f"{key}_tflops" if tensor else f"{key}_hbm_gbs", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": cfg["name"],
                    "l2": "256 MB flush between timed steps" if small else "inputs larger than L2",
                    "parallelism": "replicas only"},
-        "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": value / peaks["hbm_gbs"], "traffic": None,
-                     "peak_source": peaks["source"]},
+        "roofline": {"bound": "tensor" if tensor else "hbm", "achieved": value, "peak": peak,
+                     "unit": unit, "frac": value / peak, "traffic": None,
+                     "peak_source": peaks["source"] + (" (burst)" if tensor else "")},
         "clocks": clocks, "gpu_launches": launches,
     }
     if not args.no_e2e:
@@ -839,7 +859,7 @@ def run_aux(args):
             hout.copy_(host_out, non_blocking=True)
         ems = timed(torch, None, 1, e2e, max(2, min(args.steps, 3)), 1)
         esteps = max(2, min(args.steps, 3))
-        line["e2e"] = {"value": work * esteps / (ems * 1e-3) / 1e9, "unit": unit,
+        line["e2e"] = {"value": work * esteps / (ems * 1e-3) / scale, "unit": unit,
                        "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
                        "d2h_bytes_per_step": host_out.numel() * host_out.element_size(),
                        "ms_per_step": ems / esteps}
@@ -850,7 +870,7 @@ def run_aux(args):
             cpu()
             n += 1
         dt = (time.perf_counter() - t0) / n
-        line["cpu_baseline"] = {"value": cpu_work / dt / 1e9, "unit": unit, "cores": cores,
+        line["cpu_baseline"] = {"value": cpu_work / dt / scale, "unit": unit, "cores": cores,
                                 "kind": "port", "sample": f"{sample}; {n} passes of {dt * 1e3:.1f} ms"}
     print(json.dumps(line), flush=True)
     ex.dispose()

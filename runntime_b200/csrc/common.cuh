@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <type_traits>
 
 #include "rt_attn.h"
 
@@ -171,6 +172,46 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, float c, float s, 
                                           float& r1) {
   r0 = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
   r1 = __fmaf_rn(x1, c, __fmul_rn(x0, s));
+}
+#endif
+
+#ifdef __CUDACC__
+// The epilogue activations of matmul (codes and formulas: packages/runntime/src/core/
+// kernels/activations.ts:6-86; gelu uses the reference's erf polynomial, Abramowitz-Stegun
+// 7.1.26).  A template, so that a kernel branches on the code once per tile and not per
+// element — written as a switch in the element loop the compiler evaluates every case
+// for every element and selects.
+template <int ACT>
+__device__ __forceinline__ float act_apply(float x) {
+  if (ACT == 1) return tanhf(x);
+  if (ACT == 2) {
+    const float z = x * 0.70710678118654752f, az = fabsf(z);
+    const float t = 1.f / (1.f + az * 0.3275911f);
+    const float poly = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f +
+                       t * (-1.453152027f + t * 1.061405429f))));
+    return 0.5f * x * (1.f + copysignf(1.f - poly * __expf(-az * az), z));
+  }
+  if (ACT == 3) return x / (1.f + __expf(-x));
+  if (ACT == 4) return fmaxf(x, 0.f);
+  if (ACT == 5) {  // torch's gelu(approximate='tanh'), tanh as 1 - 2/(e^{2u} + 1)
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (2.f - 2.f / (__expf(2.f * u) + 1.f));
+  }
+  if (ACT == 6) return fmaxf(x, 0.f) + (__expf(fminf(x, 0.f)) - 1.f);
+  return x;
+}
+// Calls f(std::integral_constant<int, ACT>) for the runtime code `act` (0..6).
+template <typename F>
+__device__ __forceinline__ void act_dispatch(int act, F&& f) {
+  switch (act) {
+    case 1: f(std::integral_constant<int, 1>{}); break;
+    case 2: f(std::integral_constant<int, 2>{}); break;
+    case 3: f(std::integral_constant<int, 3>{}); break;
+    case 4: f(std::integral_constant<int, 4>{}); break;
+    case 5: f(std::integral_constant<int, 5>{}); break;
+    case 6: f(std::integral_constant<int, 6>{}); break;
+    default: f(std::integral_constant<int, 0>{}); break;
+  }
 }
 #endif
 

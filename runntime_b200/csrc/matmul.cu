@@ -20,28 +20,11 @@
 namespace rt {
 namespace {
 
-// Activation codes: packages/runntime/src/core/kernels/activations.ts:6-14,29-86.
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case 1: return tanhf(x);
-    case 2: {  // gelu with the reference's erf polynomial (Abramowitz-Stegun 7.1.26)
-      const float z = x * 0.70710678118654752f, az = fabsf(z);
-      const float t = 1.f / (1.f + az * 0.3275911f);
-      const float poly = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f +
-                         t * (-1.453152027f + t * 1.061405429f))));
-      const float erf = copysignf(1.f - poly * __expf(-az * az), z);
-      return 0.5f * x * (1.f + erf);
-    }
-    case 3: return x / (1.f + __expf(-x));
-    case 4: return fmaxf(x, 0.f);
-    case 5: {  // torch's gelu(approximate='tanh'), tanh as 1 - 2/(e^{2u} + 1)
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      const float th = 1.f - 2.f / (__expf(2.f * u) + 1.f);
-      return 0.5f * x * (1.f + th);
-    }
-    case 6: return fmaxf(x, 0.f) + (__expf(fminf(x, 0.f)) - 1.f);
-    default: return x;
-  }
+// Runtime activation code, for epilogues that touch a handful of elements per thread.
+__device__ __noinline__ float apply_act(float x, int act) {
+  float y = x;
+  act_dispatch(act, [&](auto code) { y = act_apply<decltype(code)::value>(x); });
+  return y;
 }
 
 template <typename T>

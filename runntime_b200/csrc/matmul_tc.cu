@@ -3,15 +3,16 @@
 // memory.  Same op as matmul.cu (packages/runntime/src/core/graph/ops/matmul.ts:28-99).
 //
 // One 128 x 128 output tile per CTA.  Warp 4 (one elected lane) streams K in steps of
-// 64 through a four-stage ring of TMA loads: a 128 x 64 piece of a (K-major, 128-byte
+// 64 through a three-stage ring of TMA loads: a 128 x 64 piece of a (K-major, 128-byte
 // swizzle) and a 64 x 128 piece of b as two 64-column boxes (b is [K, N] row-major, that
 // is MN-major for the MMA, the layout the V tiles of the attention kernels use).  Warp 5
 // (one elected lane) issues four tcgen05.mma (M = 128, N = 128, K = 16) per stage into a
 // 128-column accumulator and frees the stage by tcgen05.commit.  Warps 0-3 read the
 // accumulator (one row per thread), apply bias, activation and addend, and store.
 // Rows, columns and K past the matrices are zero-filled by TMA and never stored.
-// Every wait is bounded (sm100.cuh); the tile is one of M/128 x N/128, so a grid of a
-// few hundred CTAs keeps every SM busy while each CTA is latency-bound at its start and end.
+// Every wait is bounded (sm100.cuh).  Two CTAs share an SM (97 KB of shared memory and
+// 128 tensor-memory columns each), so that one's start-up and read-out overlap the
+// other's K loop.
 #include "common.cuh"
 #include "sm100.cuh"
 #include "tc_common.cuh"
@@ -22,33 +23,12 @@ namespace {
 using namespace sm100;
 using namespace tc;
 
-constexpr int GBM = 128, GBN = 128, GBK = 64, GSTAGES = 4;
+constexpr int GBM = 128, GBN = 128, GBK = 64, GSTAGES = 3;   // 97 KB of shared memory: two CTAs per SM
 constexpr int kABytes = GBM * GBK * 2, kBBytes = GBK * GBN * 2, kStageBytes = kABytes + kBBytes;
 constexpr int kGemmSmem = GSTAGES * kStageBytes + 1024;
 constexpr int kGemmThreads = 192;
 
-__device__ __forceinline__ float gemm_act(float x, int act) {
-  switch (act) {
-    case 1: return tanhf(x);
-    case 2: {
-      const float z = x * 0.70710678118654752f, az = fabsf(z);
-      const float t = 1.f / (1.f + az * 0.3275911f);
-      const float poly = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f +
-                         t * (-1.453152027f + t * 1.061405429f))));
-      return 0.5f * x * (1.f + copysignf(1.f - poly * __expf(-az * az), z));
-    }
-    case 3: return x / (1.f + __expf(-x));
-    case 4: return fmaxf(x, 0.f);
-    case 5: {
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (2.f - 2.f / (__expf(2.f * u) + 1.f));
-    }
-    case 6: return fmaxf(x, 0.f) + (__expf(fminf(x, 0.f)) - 1.f);
-    default: return x;
-  }
-}
-
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const __half* __restrict__ bias, const __half* __restrict__ addend,
                __half* __restrict__ out, int64_t M, int64_t K, int64_t N, int act, int* status) {
@@ -57,6 +37,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   __shared__ uint32_t sTmemBase;
   __shared__ int sAbort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  TC_TRACE_DECL
+  TC_TRACE(0, 0);
   const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;
   const int64_t row0 = (int64_t)blockIdx.y * GBM, col0 = (int64_t)blockIdx.x * GBN;
   const int nk = (int)((K + GBK - 1) / GBK);
@@ -78,6 +60,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sTmemBase;
+  TC_TRACE(1, 0);
 
   if (warp == 4) {
     // ------------------------------ TMA producer ------------------------------
@@ -108,6 +91,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sFull[s]), (it / GSTAGES) & 1, &sAbort)) != 0;
       if (!ok) break;
       tc_fence_after_sync();
+      TC_TRACE(2, it);
       if (elect_one()) {
         const uint32_t aLo = ((smemBase + s * kStageBytes) >> 4) | kLboA;
         const uint32_t bLo = ((smemBase + s * kStageBytes + kABytes) >> 4) | kLboB;
@@ -125,6 +109,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   } else {
     // ------------------------------ epilogue ----------------------------------
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sAcc), 0, &sAbort)) != 0;
+    TC_TRACE(4, 0);
     if (ok) {
       tc_fence_after_sync();
       const int64_t row = row0 + tid;  // thread = accumulator lane = output row
@@ -135,40 +120,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         tmem_ld32(tmem + laneBase + c, acc);
         tmem_wait_ld();
         if (row < M) {
+          const int64_t nc = col0 + c;             // first column of this 32-column piece
+          uint4 pk[4];
+          __half* h = reinterpret_cast<__half*>(pk);
+          act_dispatch(act, [&](auto code) {
 #pragma unroll
-          for (int x = 0; x < 32; x += 8) {
-            const int64_t n0 = col0 + c + x;
-            if (n0 >= N) break;
-            __half h[8];
+            for (int x = 0; x < 32; x++) {
+              float y = __uint_as_float(acc[x]);
+              const int64_t n = nc + x;
+              if (bias && n < N) y += __half2float(bias[n]);
+              y = act_apply<decltype(code)::value>(y);
+              if (addend && n < N) y += __half2float(addend[row * N + n]);
+              h[x] = __float2half_rn(y);
+            }
+          });
+          __half* dst = out + row * N + nc;
+          if (nc + 32 <= N) {
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-              float y = __uint_as_float(acc[x + e]);
-              const int64_t n = n0 + e;
-              if (n < N) {
-                if (bias) y += __half2float(bias[n]);
-                y = gemm_act(y, act);
-                if (addend) y += __half2float(addend[row * N + n]);
-              }
-              h[e] = __float2half_rn(y);
-            }
-            if (n0 + 8 <= N) {
-              *reinterpret_cast<uint4*>(out + row * N + n0) = *reinterpret_cast<const uint4*>(h);
-            } else {
-              for (int e = 0; e < 8 && n0 + e < N; e++) out[row * N + n0 + e] = h[e];
-            }
+            for (int v = 0; v < 4; v++) reinterpret_cast<uint4*>(dst)[v] = pk[v];
+          } else {
+            for (int x = 0; x < 32 && nc + x < N; x++) dst[x] = h[x];
           }
         }
       }
     }
   }
 
+  TC_TRACE(5, 0);
   tc_fence_before_sync();
   __syncthreads();
+  TC_TRACE(6, 0);
   if (tid == 0 && sAbort) atomicOr(status, kStatusWaitTimeout);
   if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, GBN);
   }
+  TC_TRACE(7, 0);
 }
 
 }  // namespace

@@ -38,7 +38,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // phase completes or the time is up, instead of returning to a spinning loop at once:
 // waiting warps then leave the issue slots to the working ones (measured: +2 % on the
 // large causal prefill).
-constexpr uint32_t kSuspendNs = 20000;
+#ifndef RT_MBAR_SUSPEND_NS
+#define RT_MBAR_SUSPEND_NS 20000
+#endif
+constexpr uint32_t kSuspendNs = RT_MBAR_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
