@@ -273,13 +273,15 @@ local_attn_tiled_kernel(const T* __restrict__ qkv, const float* __restrict__ rel
   }
 }
 
-// Rows per tile so that K, V and the bias rows fit `budget` bytes; 0 if not even 8 fit.
+// Rows per tile: the largest tile whose K, V and bias rows fit 28 KB, so that eight CTAs
+// (all 64 warps) share an SM — the kernel is a chain of dependent shuffles and small
+// shared-memory loads per row, which only occupancy hides; else the largest tile within
+// `budget`; 0 if not even 8 rows fit.
 int tile_rows_for(int hd, int window, int esize, size_t budget) {
   const size_t relBytes = (size_t)window * hd * 4;
-  for (int tr : {128, 64, 32, 16, 8}) {
-    const size_t need = 2 * (size_t)(tr + window - 1) * hd * esize + relBytes;
-    if (need <= budget) return tr;
-  }
+  auto need = [&](int tr) { return 2 * (size_t)(tr + window - 1) * hd * esize + relBytes; };
+  for (int tr : {64, 32, 16}) if (need(tr) <= 28 * 1024) return tr;
+  for (int tr : {64, 32, 16, 8}) if (need(tr) <= budget) return tr;
   return 0;
 }
 
