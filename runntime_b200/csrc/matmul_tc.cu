@@ -93,8 +93,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc_fence_after_sync();
       TC_TRACE(2, it);
       if (elect_one()) {
-        const uint32_t aLo = ((smemBase + s * kStageBytes) >> 4) | kLboA;
-        const uint32_t bLo = ((smemBase + s * kStageBytes + kABytes) >> 4) | kLboB;
+        const uint32_t aLo = (((smemBase + s * kStageBytes) >> 4) & 0x3fffu) | kLboA;
+        const uint32_t bLo = (((smemBase + s * kStageBytes + kABytes) >> 4) & 0x3fffu) | kLboB;
 #pragma unroll
         for (int kk = 0; kk < GBK / 16; kk++) {
           const uint64_t aDesc = ((uint64_t)kDescHi << 32) | (aLo + kk * 2);
@@ -158,21 +158,263 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   TC_TRACE(7, 0);
 }
 
+// ---- up to 16 rows (the projections of a decode step) -------------------------------
+// HBM-bound: the weights are read once, 2 K N bytes.  The product is computed
+// transposed, out^T [N, M] = b^T [N, K] * a^T [K, M], so that 128 columns of the weights
+// fill the 128 rows of one tcgen05.mma (A operand MN-major, exactly as TMA lays a
+// [64 k, 64 columns] box of b down) and the few rows of a are its N = 16 side.  The
+// tensor core is far from busy; it is here because it takes the weights straight from
+// shared memory, where a SIMT kernel spends 64 FMAs per 16-byte load.
+//
+// One CTA owns 128 output columns and one slice of K; the slices of a column tile form
+// a thread-block cluster (1, 2, 4 or 8 CTAs).  Each CTA streams its slice through a
+// three-stage TMA ring into a 16-column accumulator; the CTAs of rank > 0 then write
+// their accumulators into the shared memory of rank 0 (distributed shared memory),
+// one hardware cluster barrier orders that, and rank 0 adds them, applies bias,
+// activation and addend and stores.  One launch, no atomics, no scratch.
+constexpr int SKN = 128, SKM = 16, SKK = 64, SKSTAGES = 3;
+constexpr int kSkB = SKK * SKN * 2, kSkA = SKM * SKK * 2, kSkStage = kSkB + kSkA;   // 16 KB + 2 KB
+constexpr int kSkThreads = 192;
+constexpr int kSkMaxCluster = 8;
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster's shared window, of `addr` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// The hardware barrier over all threads of the cluster, in its two halves.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// rowsPad: 8 or 16, the rows of a that are exchanged and stored (M <= rowsPad).
+__global__ void __launch_bounds__(kSkThreads, 3)
+gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                      const __half* __restrict__ bias, const __half* __restrict__ addend,
+                      __half* __restrict__ out, int M, int64_t K, int64_t N, int stepsPerRank,
+                      int rowsPad, int act, int* status) {
+  extern __shared__ unsigned char smemRaw[];
+  __shared__ __align__(8) uint64_t sFull[SKSTAGES], sEmpty[SKSTAGES], sAcc;
+  __shared__ uint32_t sTmemBase;
+  __shared__ int sAbort;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;
+  const uint32_t redBase = smemBase + SKSTAGES * kSkStage;   // [rank - 1][rowsPad][128] f32, rank 0 only
+  const uint32_t rank = cluster_rank(), ranks = cluster_size();
+  const int64_t col0 = (int64_t)blockIdx.x * SKN;
+  const int nkAll = (int)((K + SKK - 1) / SKK);
+  const int it0 = (int)rank * stepsPerRank;
+  const int nk = max(0, min(stepsPerRank, nkAll - it0));     // K steps of this CTA; may be none
+
+  if (tid == 0) {
+    sAbort = 0;
+    for (int s = 0; s < SKSTAGES; s++) {
+      mbar_init(smem_u32(&sFull[s]), 1);
+      mbar_init(smem_u32(&sEmpty[s]), 1);
+    }
+    mbar_init(smem_u32(&sAcc), 1);
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sTmemBase), 32);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sTmemBase;
+  cluster_arrive();   // first barrier: every CTA of the cluster is running (waited on below)
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      prefetch_tensormap(&mapA);
+      prefetch_tensormap(&mapB);
+      for (int it = 0; it < nk; it++) {
+        const int s = it % SKSTAGES;
+        if (it >= SKSTAGES && !mbar_wait(smem_u32(&sEmpty[s]), ((it / SKSTAGES) - 1) & 1, &sAbort))
+          break;
+        const uint32_t bar = smem_u32(&sFull[s]);
+        const uint32_t dB = smemBase + s * kSkStage, dA = dB + kSkB;
+        const int k0 = (it0 + it) * SKK;
+        mbar_expect_tx(bar, kSkStage);
+        tma_load_2d(dB, &mapB, (int)col0, k0, bar);                  // 64 columns x 64 k
+        tma_load_2d(dB + SKK * 128, &mapB, (int)col0 + 64, k0, bar);
+        tma_load_2d(dA, &mapA, k0, 0, bar);                          // 64 k x 16 rows of a
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer --------------------------------
+    // D [128 columns of b, 16 rows of a]: A = b^T (MN-major), B = a (K-major), f32 D.
+    constexpr uint32_t idesc = (1u << 4) | (1u << 15) | ((uint32_t)(SKM >> 3) << 17) |
+                               ((uint32_t)(SKN >> 4) << 24);
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO, version, SW128
+    constexpr uint32_t kLboMn = ((uint32_t)(SKK * 128) >> 4) << 16;       // next 64 columns of b
+    constexpr uint32_t kLboK = (16u >> 4) << 16;
+    bool ok = true;
+    for (int it = 0; it < nk && ok; it++) {
+      const int s = it % SKSTAGES;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sFull[s]), (it / SKSTAGES) & 1, &sAbort)) != 0;
+      if (!ok) break;
+      tc_fence_after_sync();
+      if (elect_one()) {
+        // In a cluster the shared-window address of a CTA carries its rank above the
+        // offset; the descriptor's address field takes the 14 offset bits only (left
+        // in, the rank lands in the leading-dimension field beside it).
+        const uint32_t wLo = (((smemBase + s * kSkStage) >> 4) & 0x3fffu) | kLboMn;
+        const uint32_t xLo = (((smemBase + s * kSkStage + kSkB) >> 4) & 0x3fffu) | kLboK;
+#pragma unroll
+        for (int kk = 0; kk < SKK / 16; kk++) {
+          const uint64_t wDesc = ((uint64_t)kDescHi << 32) | (wLo + kk * (2048 >> 4));
+          const uint64_t xDesc = ((uint64_t)kDescHi << 32) | (xLo + kk * 2);
+          mma_f16_ss(tmem, wDesc, xDesc, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&sEmpty[s]));
+        if (it == nk - 1) tc_commit(smem_u32(&sAcc));
+      }
+      __syncwarp();
+    }
+  }
+
+  // Accumulator of this CTA: thread = column, 16 values = rows of a.
+  float acc[SKM];
+#pragma unroll
+  for (int m = 0; m < SKM; m++) acc[m] = 0.f;
+  if (warp < 4 && nk > 0) {
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sAcc), 0, &sAbort)) != 0;
+    if (ok) {
+      tc_fence_after_sync();
+      uint32_t raw[SKM];
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16), raw);
+      tmem_wait_ld();
+#pragma unroll
+      for (int m = 0; m < SKM; m++) acc[m] = __uint_as_float(raw[m]);
+    }
+  }
+  __syncwarp();
+  cluster_wait();
+  if (warp < 4 && rank > 0) {
+    const uint32_t dst = map_to_rank(redBase, 0) + (((rank - 1) * rowsPad) * SKN + tid) * 4;
+#pragma unroll
+    for (int m = 0; m < SKM; m++)
+      if (m < rowsPad) st_cluster_f32(dst + m * SKN * 4, acc[m]);
+  }
+  // Second barrier: the partial sums are in rank 0's shared memory.  Every thread of every
+  // CTA of the cluster reaches both barriers whatever happened above.
+  __syncwarp();
+  cluster_arrive();
+  cluster_wait();
+
+  if (warp < 4 && rank == 0) {
+    const float* red = reinterpret_cast<const float*>(smemRaw + (redBase - smem_u32(smemRaw)));
+    for (uint32_t r = 1; r < ranks; r++)
+#pragma unroll
+      for (int m = 0; m < SKM; m++)
+        if (m < rowsPad) acc[m] += red[((r - 1) * rowsPad + m) * SKN + tid];
+    const int64_t n = col0 + tid;
+    if (n < N) {
+      const float bv = bias ? __half2float(bias[n]) : 0.f;
+      act_dispatch(act, [&](auto code) {
+#pragma unroll
+        for (int m = 0; m < SKM; m++) {
+          if (m < M) {
+            float y = act_apply<decltype(code)::value>(acc[m] + bv);
+            if (addend) y += __half2float(addend[(int64_t)m * N + n]);
+            out[(int64_t)m * N + n] = __float2half_rn(y);
+          }
+        }
+      });
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && sAbort) atomicOr(status, kStatusWaitTimeout);
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 32);
+  }
+}
+
 }  // namespace
 
-// f16, more rows than the skinny kernel takes, whole 16-byte row pitches, at least one
-// box of every operand.
+// f16, whole 16-byte row pitches, at least one box of every operand.  Up to 16 rows go
+// to the cluster kernel (which wants a full tile of columns), more to the tiled one.
 bool matmul_tc_supported(const void* a, const void* b, const void* out, int64_t M, int64_t K,
                          int64_t N, int dtype) {
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  return dtype == RT_F16 && M > 16 && K >= 64 && N >= 64 && K % 8 == 0 && N % 8 == 0 && al(a) &&
-         al(b) && al(out) && M < (1ll << 31) - 256 && N < (1ll << 31) - 256 &&
+  return dtype == RT_F16 && M >= 1 && K >= 64 && N >= (M <= SKM ? SKN : 64) && K % 8 == 0 &&
+         N % 8 == 0 && al(a) && al(b) && al(out) && M < (1ll << 31) - 256 && N < (1ll << 31) - 256 &&
          K < (1ll << 31) - 256 && (M + GBM - 1) / GBM <= 65535 && encode_fn() != nullptr;
 }
+
+namespace {
+cudaError_t launch_skinny(const void* a, const void* b, const void* bias, const void* addend,
+                          void* out, int64_t M, int64_t K, int64_t N, int act, int* status,
+                          cudaStream_t s, std::string* err) {
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a, M, K, K, SKM, err) || !make_map(&mb, b, K, N, N, SKK, err))
+    return cudaErrorInvalidValue;
+  // Slices of K: enough CTAs for two per SM, at least two K steps each.
+  const int64_t tiles = (N + SKN - 1) / SKN;
+  const int nkAll = (int)((K + SKK - 1) / SKK);
+  int cluster = 1;
+  while (cluster < kSkMaxCluster && tiles * cluster < 2 * 148 && nkAll / (cluster * 2) >= 2) cluster *= 2;
+  const int stepsPerRank = (nkAll + cluster - 1) / cluster;
+  const int rowsPad = M <= 8 ? 8 : 16;
+  const int smem = SKSTAGES * kSkStage + 1024 + (cluster - 1) * rowsPad * SKN * 4;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_skinny_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)tiles, (unsigned)cluster);
+  cfg.blockDim = dim3(kSkThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)cluster;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel, ma, mb, static_cast<const __half*>(bias),
+                            static_cast<const __half*>(addend), static_cast<__half*>(out), (int)M,
+                            K, N, stepsPerRank, rowsPad, act, status);
+}
+}  // namespace
 
 cudaError_t launch_matmul_tc(const void* a, const void* b, const void* bias, const void* addend,
                              void* out, int64_t M, int64_t K, int64_t N, int act, int* status,
                              cudaStream_t s, std::string* err) {
+  if (M <= SKM) return launch_skinny(a, b, bias, addend, out, M, K, N, act, status, s, err);
   CUtensorMap ma, mb;
   if (!make_map(&ma, a, M, K, K, GBM, err) || !make_map(&mb, b, K, N, N, GBK, err))
     return cudaErrorInvalidValue;

@@ -92,6 +92,26 @@ def test_matmul_on_the_tensor_cores(ex, m, k, n):
         ex.setOption(OPT_PREFILL_TC, 1)
 
 
+# (m, k, n): one to eight K slices per column tile, ragged last K step and column tile,
+# a K that leaves the last slice empty (k = 576: nine steps over four slices of three).
+SKINNY_TC_SHAPES = [(1, 64, 128), (8, 4096, 12288), (9, 1024, 4096), (16, 4096, 1024), (3, 200, 136),
+                    (8, 576, 2048), (5, 8192, 128), (16, 72, 40000), (2, 2048, 6144)]
+
+
+@pytest.mark.parametrize("m,k,n", SKINNY_TC_SHAPES)
+def test_decode_step_matmul_on_the_tensor_cores(ex, m, k, n):
+    """f16, up to 16 rows, at least 128 columns: the cluster kernel (K slices reduced
+    through distributed shared memory); the FP32-pipe kernel (option off) agrees."""
+    from runntime_b200._lib import OPT_PREFILL_TC
+    check(ex, m, k, n, "f16", bias=True, addend=True, act="gelu")
+    check(ex, m, k, n, "f16")
+    ex.setOption(OPT_PREFILL_TC, 0)
+    try:
+        check(ex, m, k, n, "f16")
+    finally:
+        ex.setOption(OPT_PREFILL_TC, 1)
+
+
 @pytest.mark.parametrize("dtype", ["f32", "f16"])
 @pytest.mark.parametrize("m", [1, 5, 40])
 @pytest.mark.parametrize("act", [None, "tanh", "gelu", "silu", "relu", "geluTanh", "elu"])
