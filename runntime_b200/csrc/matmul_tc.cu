@@ -172,7 +172,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 // their accumulators into the shared memory of rank 0 (distributed shared memory),
 // one hardware cluster barrier orders that, and rank 0 adds them, applies bias,
 // activation and addend and stores.  One launch, no atomics, no scratch.
-constexpr int SKN = 128, SKM = 16, SKK = 64, SKSTAGES = 3;
+#ifndef RT_SK_STAGES
+#define RT_SK_STAGES 3
+#endif
+#ifndef RT_SK_CTAS_PER_SM
+#define RT_SK_CTAS_PER_SM 2
+#endif
+#ifndef RT_SK_MIN_CTAS
+#define RT_SK_MIN_CTAS 3
+#endif
+constexpr int SKN = 128, SKM = 16, SKK = 64, SKSTAGES = RT_SK_STAGES;
 constexpr int kSkB = SKK * SKN * 2, kSkA = SKM * SKK * 2, kSkStage = kSkB + kSkA;   // 16 KB + 2 KB
 constexpr int kSkThreads = 192;
 constexpr int kSkMaxCluster = 8;
@@ -206,6 +215,16 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+// Programmatic dependent launch: a grid launched with the stream-serialization attribute
+// may start while the grid before it in the stream drains; grid_dependency_wait() returns
+// once that grid has completed and its writes are visible (at once if there is none);
+// grid_launch_dependents() lets the next such grid start its prologue.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 // The hardware barrier over all threads of the cluster, in its two halves.
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -214,8 +233,27 @@ __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Optional per-CTA timeline for kernel development (off unless the translation unit is
+// compiled with RT_SK_TRACE): thread 0 of every CTA stores the GPU-wide nanosecond timer at
+// eight points of the kernel.
+#ifdef RT_SK_TRACE
+__device__ unsigned long long gSkTrace[4096 * 8];
+#define SK_MARK(i)                                                                        \
+  do {                                                                                    \
+    if (threadIdx.x == (i == 2 ? 160 : 0)) {                                              \
+      unsigned long long t_;                                                              \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+      gSkTrace[((blockIdx.y * gridDim.x + blockIdx.x) & 4095) * 8 + (i)] = t_;            \
+    }                                                                                     \
+  } while (0)
+#else
+#define SK_MARK(i) \
+  do {             \
+  } while (0)
+#endif
+
 // rowsPad: 8 or 16, the rows of a that are exchanged and stored (M <= rowsPad).
-__global__ void __launch_bounds__(kSkThreads, 3)
+__global__ void __launch_bounds__(kSkThreads, RT_SK_MIN_CTAS)
 gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                       const __half* __restrict__ bias, const __half* __restrict__ addend,
                       __half* __restrict__ out, int M, int64_t K, int64_t N, int stepsPerRank,
@@ -225,6 +263,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
   __shared__ uint32_t sTmemBase;
   __shared__ int sAbort;
   const int tid = threadIdx.x, warp = tid >> 5;
+  SK_MARK(0);
   const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;
   const uint32_t redBase = smemBase + SKSTAGES * kSkStage;   // [rank - 1][rowsPad][128] f32, rank 0 only
   const uint32_t rank = cluster_rank(), ranks = cluster_size();
@@ -250,6 +289,10 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sTmemBase;
+  SK_MARK(1);
+  // Everything above touched no global memory; what follows reads tensors the grid before
+  // this one may have written (a, addend) and overwrites out, which it may still read.
+  grid_dependency_wait();
   cluster_arrive();   // first barrier: every CTA of the cluster is running (waited on below)
 
   if (warp == 4) {
@@ -284,6 +327,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sFull[s]), (it / SKSTAGES) & 1, &sAbort)) != 0;
       if (!ok) break;
       tc_fence_after_sync();
+      if (it == 0) SK_MARK(2);
       if (elect_one()) {
         // In a cluster the shared-window address of a CTA carries its rank above the
         // offset; the descriptor's address field takes the 14 offset bits only (left
@@ -318,6 +362,8 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
       for (int m = 0; m < SKM; m++) acc[m] = __uint_as_float(raw[m]);
     }
   }
+  SK_MARK(3);
+  grid_launch_dependents();   // the weights of this CTA are in: the next grid may set itself up
   __syncwarp();
   cluster_wait();
   if (warp < 4 && rank > 0) {
@@ -331,6 +377,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
   __syncwarp();
   cluster_arrive();
   cluster_wait();
+  SK_MARK(4);
 
   if (warp < 4 && rank == 0) {
     const float* red = reinterpret_cast<const float*>(smemRaw + (redBase - smem_u32(smemRaw)));
@@ -354,6 +401,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     }
   }
 
+  SK_MARK(5);
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && sAbort) atomicOr(status, kStatusWaitTimeout);
@@ -361,6 +409,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
     tc_fence_after_sync();
     tmem_dealloc(tmem, 32);
   }
+  SK_MARK(6);
 }
 
 }  // namespace
@@ -386,7 +435,7 @@ cudaError_t launch_skinny(const void* a, const void* b, const void* bias, const 
   const int64_t tiles = (N + SKN - 1) / SKN;
   const int nkAll = (int)((K + SKK - 1) / SKK);
   int cluster = 1;
-  while (cluster < kSkMaxCluster && tiles * cluster < 2 * 148 && nkAll / (cluster * 2) >= 2) cluster *= 2;
+  while (cluster < kSkMaxCluster && tiles * cluster < RT_SK_CTAS_PER_SM * 148 && nkAll / (cluster * 2) >= 2) cluster *= 2;
   const int stepsPerRank = (nkAll + cluster - 1) / cluster;
   const int rowsPad = M <= 8 ? 8 : 16;
   const int smem = SKSTAGES * kSkStage + 1024 + (cluster - 1) * rowsPad * SKN * 4;
@@ -398,13 +447,15 @@ cudaError_t launch_skinny(const void* a, const void* b, const void* bias, const 
   cfg.blockDim = dim3(kSkThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = (unsigned)cluster;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel, ma, mb, static_cast<const __half*>(bias),
                             static_cast<const __half*>(addend), static_cast<__half*>(out), (int)M,
                             K, N, stepsPerRank, rowsPad, act, status);
