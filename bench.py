@@ -851,7 +851,7 @@ def run_aux(args):
                    "l2": rotating or ("256 MB read between timed steps" if small else "inputs larger than L2"),
                    "parallelism": "replicas only"},
         "roofline": {"bound": "tensor" if tensor else "hbm", "achieved": value, "peak": peak,
-                     "unit": unit, "frac": value / peak, "traffic": None,
+                     "unit": unit, "frac": value / peak, "traffic": load_traffic().get(key),
                      "peak_source": peaks["source"] + (" (burst)" if tensor else "")},
         "clocks": clocks, "gpu_launches": launches,
     }
