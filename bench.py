@@ -2,7 +2,7 @@
 """Benchmark of the attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c4|c3|c2|c1]
-    python bench.py --workload rope|softmax|local|step|gemv|gemm|argmax   # the operators beside attention
+    python bench.py --workload rope|softmax|local|step|layer|gemv|gemm|argmax   # the operators beside attention
     python bench.py --impl reference ...        # the CPU restatement, host cores
 
 One JSON line on stdout (rank 0).  The default workload is the large causal
@@ -684,6 +684,8 @@ AUX = {
     "argmax": dict(name="greedy_head_argmaxdot_f16_v262144_n2048", rows=262144, cols=2048),
     "step": dict(name="moonshine_tiny_decoder_layer_step_f16_batch64_rope_append_attend",
                  batch=64, heads=8, hd=36, maxPos=448),
+    "layer": dict(name="decoder_layer_attention_block_f16_b8_dim4096_h32x128_kv4096_qkv_rope_append_attend_oproj",
+                  batch=8, heads=32, hd=128, maxPos=4096, layers=4),
 }
 
 
@@ -807,6 +809,44 @@ def run_aux(args):
         x1 = np.random.default_rng(2).standard_normal(W).astype(np.float32)
         cpu = lambda: int(np.argmax(w1 @ x1))
         cpu_work, sample = r1 * W * 2, f"{r1} of {R} rows, numpy f32 gemv + argmax"
+    elif key == "layer":
+        # The attention block of a decoder layer for one new token per sequence, on device from
+        # the hidden state to the residual sum: fused qkv projection (+ bias), rope of q and k
+        # + append + attention in one launch, output projection with the residual as addend.
+        # Three launches per layer; the steps walk through `layers` sets of weights and caches.
+        from runntime_b200.engine import decode_batched
+        B, H, hd, P, NL = cfg["batch"], cfg["heads"], cfg["hd"], cfg["maxPos"], cfg["layers"]
+        D = H * hd
+        x = torch.randn(B, D, generator=g, device=dev, dtype=torch.float16)
+        wqkv = [(torch.randn(D, 3 * D, generator=g, device=dev) / 64).to(torch.float16) for _ in range(NL)]
+        bqkv = torch.randn(3 * D, generator=g, device=dev, dtype=torch.float16)
+        wo = [(torch.randn(D, D, generator=g, device=dev) / 64).to(torch.float16) for _ in range(NL)]
+        kc = [torch.randn(B, P, D, generator=g, device=dev, dtype=torch.float16) for _ in range(NL)]
+        vc = [torch.randn(B, P, D, generator=g, device=dev, dtype=torch.float16) for _ in range(NL)]
+        kvLens = torch.full((B,), P, dtype=torch.int32, device=dev)   # the appended row is the last
+        tab = torch.rand(P, hd // 2, generator=g, device=dev) * 6.28
+        cos = (tab.cos().repeat_interleave(2, 1) * hd ** -0.25).contiguous()
+        sin = (tab.sin().repeat_interleave(2, 1) * hd ** -0.25).contiguous()
+        qkv = torch.empty(B, 3 * D, device=dev, dtype=torch.float16)
+        att = torch.empty(B, D, device=dev, dtype=torch.float16)
+        out = torch.empty(B, D, device=dev, dtype=torch.float16)
+        base = qkv.data_ptr()
+
+        def step(i):
+            L = i % NL
+            check(lib.rt_matmul(ex.ctx, ptr(x), ptr(wqkv[L]), ptr(bqkv), None, ptr(qkv), B, D, 3 * D,
+                                D, 0, 0, f16), ex.ctx)
+            decode_batched(ex, base, att, kc[L], vc[L], dtype="f16", batch=B, cacheRows=P, qHeads=H,
+                           kvHeads=H, headDim=hd, kvLen=P, kvLens=kvLens, kNew=base + D * 2,
+                           vNew=base + 2 * D * 2, ropeCos=cos, ropeSin=sin, ropeByPosition=True,
+                           qRowStride=3 * D, kNewRowStride=3 * D, vNewRowStride=3 * D)
+            check(lib.rt_matmul(ex.ctx, ptr(att), ptr(wo[L]), None, ptr(x), ptr(out), B, D, D,
+                                D, 0, 0, f16), ex.ctx)
+        # weights and the visible cache rows read once; activations are noise beside them
+        work = (D * 3 * D + D * D + 2 * B * P * D) * 2 + (B * D * 4 + B * 3 * D * 2 + 3 * D) * 2
+        rotating = f"{NL} layers' weights and caches in rotation ({NL * (4 * D * D + 2 * B * P * D) * 2 >> 20} MB), larger than L2"
+        host_in, host_out = [x], out
+        cpu, cpu_work, sample = None, 0, ""
     else:  # step: rope x2 + slice + writeRows x2 + attention of one decoder layer, batch of sequences
         from runntime_b200.engine import decode_batched
         B, H, hd, P = cfg["batch"], cfg["heads"], cfg["hd"], cfg["maxPos"]

@@ -79,25 +79,57 @@ struct Loader<T, 1> {
   static __device__ __forceinline__ void load(const T* p, float (&f)[1]) { f[0] = to_f32<T>(*p); }
 };
 
+// Rows whose pitch is a multiple of 128 bytes (head size 64 or 128) put the same column of
+// every key into the same bank: threads that walk their rows in step would collide on every
+// load (eight ways for 16-byte loads; measured 1.0 TB/s at head size 128).  Such a thread
+// starts at chunk `rot` of its row and wraps around instead: a dot product does not care
+// about the order, q is fetched from the same rotated position, and the accumulator keeps
+// its chunks in rotated order until it is written out (acc chunk i = row chunk
+// (i + rot) mod chunks).
+template <int HDP, bool EXACT, int VEC>
+struct Rotated {
+  static constexpr bool value = EXACT && VEC > 1 && (HDP == 64 || HDP == 128);
+};
+
 // One key for one head: score, online-softmax update, accumulate p*v.
 // kp/vp may point at shared memory (cache tile) or global memory (appended row).
 template <typename T, int HDP, bool EXACT, int VEC, bool QSMEM>
 __device__ __forceinline__ void process_key(const T* kp, const T* vp, const float* qv, int hd,
-                                            float& m, float& l, float (&acc)[HDP]) {
-  float s0 = 0.f, s1 = 0.f;
+                                            float& m, float& l, float (&acc)[HDP], int rot) {
+  constexpr bool ROT = Rotated<HDP, EXACT, VEC>::value;
+  constexpr int NCH = HDP / VEC;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
   for (int i = 0; i < HDP / VEC; i++) {
     if (EXACT || i * VEC < hd) {
+      const int ci = ROT ? ((i + rot) & (NCH - 1)) : i;
       float f[VEC];
-      Loader<T, VEC>::load(kp + i * VEC, f);
+      Loader<T, VEC>::load(kp + ci * VEC, f);
+      if (ROT) {
+        // q chunk from the same position: 16-byte loads (the q rows are 16-byte aligned)
+        float qf[VEC];
 #pragma unroll
-      for (int e = 0; e < VEC; e++) {
-        if ((i * VEC + e) & 1) s1 = fmaf(qv[i * VEC + e], f[e], s1);
-        else s0 = fmaf(qv[i * VEC + e], f[e], s0);
+        for (int e = 0; e < VEC; e += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(qv + ci * VEC + e);
+          qf[e] = t.x, qf[e + 1] = t.y, qf[e + 2] = t.z, qf[e + 3] = t.w;
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4) {
+          s0 = fmaf(qf[e], f[e], s0);
+          s1 = fmaf(qf[e + 1], f[e + 1], s1);
+          s2 = fmaf(qf[e + 2], f[e + 2], s2);
+          s3 = fmaf(qf[e + 3], f[e + 3], s3);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+          if ((i * VEC + e) & 1) s1 = fmaf(qv[i * VEC + e], f[e], s1);
+          else s0 = fmaf(qv[i * VEC + e], f[e], s0);
+        }
       }
     }
   }
-  const float s = (s0 + s1) * kLog2e;  // log2 domain
+  const float s = ((s0 + s1) + (s2 + s3)) * kLog2e;  // log2 domain
   if (s > m) {
     const float c = fast_exp2(m - s);
     l *= c;
@@ -110,8 +142,9 @@ __device__ __forceinline__ void process_key(const T* kp, const T* vp, const floa
 #pragma unroll
   for (int i = 0; i < HDP / VEC; i++) {
     if (EXACT || i * VEC < hd) {
+      const int ci = ROT ? ((i + rot) & (NCH - 1)) : i;
       float f[VEC];
-      Loader<T, VEC>::load(vp + i * VEC, f);
+      Loader<T, VEC>::load(vp + ci * VEC, f);
 #pragma unroll
       for (int e = 0; e < VEC; e++) acc[i * VEC + e] = fmaf(pe, f[e], acc[i * VEC + e]);
     }
@@ -319,6 +352,8 @@ decode_kernel(const DecodeParams p) {
 
   float m = kNegSeed, l = 0.f;
   float acc[HDP];
+  constexpr bool ROT = Rotated<HDP, EXACT, VEC>::value;
+  const int rot = ROT ? (tid & (HDP / VEC - 1)) : 0;   // see Rotated
 #pragma unroll
   for (int x = 0; x < HDP; x++) acc[x] = 0.f;
   if (active && slot == 0 && split == 0 && p.sinks) {
@@ -346,7 +381,7 @@ decode_kernel(const DecodeParams p) {
     }
     if (active && slot < nk) {
       const int off = slot * sliceElems + kvl * hd;
-      process_key<T, HDP, EXACT, VEC, QSMEM>(tK + off, tV + off, qv, hd, m, l, acc);
+      process_key<T, HDP, EXACT, VEC, QSMEM>(tK + off, tV + off, qv, hd, m, l, acc, rot);
     }
     if (BULK) {
       __syncwarp();
@@ -356,7 +391,7 @@ decode_kernel(const DecodeParams p) {
 
   // Fused append: split 0 attends to the new row it staged (and stored) above.
   if (appendHere && active && slot == 0)
-    process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + kvl * hd, sVn + kvl * hd, qv, hd, m, l, acc);
+    process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + kvl * hd, sVn + kvl * hd, qv, hd, m, l, acc, rot);
 
   if (!ok || sAbort) {
     // A wait ran out: record it, let copies in flight land, leave.
@@ -373,8 +408,17 @@ decode_kernel(const DecodeParams p) {
     float* r = sM + (slot * hqMax + hl) * MS;
     r[0] = m;
     r[1] = l;
+    if (ROT) {
 #pragma unroll
-    for (int x = 0; x < HDP; x++) r[2 + x] = acc[x];
+      for (int i = 0; i < HDP / VEC; i++) {
+        float* dst = r + 2 + ((i + rot) & (HDP / VEC - 1)) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; e++) dst[e] = acc[i * VEC + e];
+      }
+    } else {
+#pragma unroll
+      for (int x = 0; x < HDP; x++) r[2 + x] = acc[x];
+    }
   }
   named_barrier_sync(1, kConsumers);
 
@@ -531,30 +575,34 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
   int kvPerCta = p.kvHeads;
   while (kvPerCta * group > kConsumers) kvPerCta = (kvPerCta + 1) / 2;
   const int hdp = padded_hd(p.hd);
-  const size_t qBytes = (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128 +
-                        (p.kNew ? 2 * ((size_t)kvPerCta * p.hd * esize + 128) : 0);
-  const size_t budget = (hdp <= 64 ? kSmemBudgetTwoPerSm : kSmemBudget) - qBytes;
+  // Key slots per tile: 256 threads' worth, fewer when two stages of that many keys do not
+  // fit.  The heads stay together as long as a handful of key slots fit (wide heads then
+  // leave some threads idle): a CTA that owns all the heads fetches a tile with one bulk
+  // copy per tensor, while one that owns a single head needs a copy of hd elements per
+  // key — measured 1.0 TB/s at 32 heads x 128, the copy engine's rate for 256-byte copies.
+  constexpr int kMinKeySlots = 4;
   int keySlots;
+  size_t budget;
   for (;;) {
+    const size_t qBytes = (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128 +
+                          (p.kNew ? 2 * ((size_t)kvPerCta * p.hd * esize + 128) : 0);
+    budget = (hdp <= 64 ? kSmemBudgetTwoPerSm : kSmemBudget) - qBytes;
     keySlots = kConsumers / (kvPerCta * group);
-    const size_t tile = 2ull * keySlots * kvPerCta * p.hd * esize + 256;
-    if (2 * tile > budget && kvPerCta > 1) {
-      kvPerCta = (kvPerCta + 1) / 2;
-      continue;
-    }
-    break;
-  }
-  {
     const size_t perSlot = 2ull * kvPerCta * p.hd * esize;            // K+V bytes of one key
     const size_t mergePerSlot = (size_t)kvPerCta * group * (2 + hdp) * 4;
     const size_t capTile = (budget / 2 - 256) / perSlot;               // two stages must fit
     const size_t capMerge = budget / mergePerSlot;
-    size_t cap = capTile < capMerge ? capTile : capMerge;
+    const size_t cap = capTile < capMerge ? capTile : capMerge;
+    if (cap < (size_t)(keySlots < kMinKeySlots ? keySlots : kMinKeySlots) && kvPerCta > 1) {
+      kvPerCta = (kvPerCta + 1) / 2;
+      continue;
+    }
     if (cap < 1) {
       *err = "decode: heads too wide for shared memory";
       return false;
     }
     if ((size_t)keySlots > cap) keySlots = (int)cap;
+    break;
   }
   p.kvPerCta = kvPerCta;
   p.keySlots = keySlots;

@@ -105,7 +105,9 @@ def _batched_inputs(batch, cacheRows, heads, kvHeads, hd, dtype, lens, seed=11):
 
 
 @pytest.mark.parametrize("dtype", ["f16", "f32"])
-@pytest.mark.parametrize("heads,kvHeads,hd", [(8, 8, 36), (8, 8, 52), (6, 2, 64), (4, 4, 20)])
+# the last three: wide models, where a tile holds only a few keys of all the heads
+@pytest.mark.parametrize("heads,kvHeads,hd", [(8, 8, 36), (8, 8, 52), (6, 2, 64), (4, 4, 20),
+                                              (32, 32, 128), (32, 8, 128), (16, 16, 64)])
 def test_batched_decode_with_append_matches_per_sequence_oracle(ex, dtype, heads, kvHeads, hd):
     import torch
     from runntime_b200.engine import decode_batched
