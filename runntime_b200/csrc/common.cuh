@@ -91,6 +91,7 @@ struct DecodeParams {
   int32_t kvPerCta;     // kv heads handled by one CTA
   int32_t keySlots;     // keys processed concurrently by one CTA
   int32_t stages;       // smem ring depth (bulk path)
+  int32_t lanesPerRow;  // threads that share one (key, head) pair, each a slice of the head (1, 2, 4)
   // fused rope (null tables = off) and row strides of q / kNew / vNew, in elements
   const float* ropeCos;
   const float* ropeSin;

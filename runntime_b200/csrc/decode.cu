@@ -151,6 +151,53 @@ __device__ __forceinline__ void process_key(const T* kp, const T* vp, const floa
   }
 }
 
+// The same for a thread that owns W = hd / R columns of the (key, head) pair, R = 2 or 4
+// adjacent lanes sharing the pair (head size 64 and 128: a whole 128-wide row per thread
+// costs 512 bytes of every stage and 128 accumulator registers, so few keys fit a tile
+// and the threads' long dependent chains leave the SM idle — measured 2.5 TB/s).  The
+// partial scores are added across the R lanes by shuffles restricted to the group; m
+// and l then evolve identically in all of them.  q lives in registers, loaded once in
+// the same rotated chunk order as the row is walked (see Rotated).
+template <typename T, int W, int VEC, int R>
+__device__ __forceinline__ void process_key_sub(const T* kp, const T* vp, const float (&q)[W],
+                                                float& m, float& l, float (&acc)[W], int rot,
+                                                unsigned groupMask) {
+  constexpr int NCH = W / VEC;
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; i++) {
+    const int ci = (i + rot) & (NCH - 1);
+    float f[VEC];
+    Loader<T, VEC>::load(kp + ci * VEC, f);
+#pragma unroll
+    for (int e = 0; e < VEC; e += 2) {
+      s0 = fmaf(q[i * VEC + e], f[e], s0);
+      s1 = fmaf(q[i * VEC + e + 1], f[e + 1], s1);
+    }
+  }
+  float s = s0 + s1;
+#pragma unroll
+  for (int o = 1; o < R; o <<= 1) s += __shfl_xor_sync(groupMask, s, o);
+  s *= kLog2e;  // log2 domain
+  if (s > m) {
+    const float c = fast_exp2(m - s);
+    l *= c;
+#pragma unroll
+    for (int x = 0; x < W; x++) acc[x] *= c;
+    m = s;
+  }
+  const float pe = fast_exp2(s - m);
+  l += pe;
+#pragma unroll
+  for (int i = 0; i < NCH; i++) {
+    const int ci = (i + rot) & (NCH - 1);
+    float f[VEC];
+    Loader<T, VEC>::load(vp + ci * VEC, f);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) acc[i * VEC + e] = fmaf(pe, f[e], acc[i * VEC + e]);
+  }
+}
+
 // Cross-GPU hand-over, called by the consumer threads of the block that wrote the final
 // rows of (sequence b, head block zb) into this rank's slot: copies those rows into the
 // same slot of every peer's buffer (plain stores to peer memory).  The ranks are told by
@@ -173,10 +220,12 @@ __device__ __forceinline__ void exchange_rows(const DecodeParams& p, float* mySl
   }
 }
 
-template <typename T, int HDP, bool EXACT, int VEC, bool BULK>
-__global__ void __launch_bounds__(BULK ? kConsumers + 32 : kConsumers, HDP <= 64 ? 2 : 1)
+template <typename T, int HDP, bool EXACT, int VEC, bool BULK, int R = 1>
+__global__ void __launch_bounds__(BULK ? kConsumers + 32 : kConsumers, HDP / R <= 64 ? 2 : 1)
 decode_kernel(const DecodeParams p) {
   constexpr bool QSMEM = true;
+  constexpr int W = HDP / R;   // columns of a head per thread (R lanes share a (key, head) pair)
+  static_assert(R == 1 || (EXACT && BULK && VEC > 1 && (W % VEC) == 0), "sub-row threads: exact bulk path only");
   constexpr int QS = q_stride(HDP);
   extern __shared__ __align__(128) unsigned char smemRaw[];
   __shared__ int sAbort;
@@ -189,8 +238,9 @@ decode_kernel(const DecodeParams p) {
   const int group = p.qHeads / p.kvHeads;
   const int kvh0 = zb * p.kvPerCta;
   const int nkv = min(p.kvPerCta, p.kvHeads - kvh0);
-  const int hqMax = p.kvPerCta * group;
-  const int hq = nkv * group;
+  const int hqReal = nkv * group;           // query heads of this CTA
+  const int hqMax = p.kvPerCta * group * R;  // thread columns: (head, lane of the head's group)
+  const int hq = hqReal * R;
   const int KS = p.keySlots;
   const int sliceElems = nkv * hd;
   const int rowElems = p.kvHeads * hd;
@@ -232,7 +282,7 @@ decode_kernel(const DecodeParams p) {
   // Shared-memory carve-up: [q][appended K, V slices][ring: stages x (K tile, V tile)];
   // the ring is reused for the slot merge at the end.
   float* sQ = reinterpret_cast<float*>(smemRaw);
-  const int qBytes = QSMEM ? ((hqMax * QS * 4 + 127) / 128) * 128 : 0;
+  const int qBytes = QSMEM ? ((hqMax / R * QS * 4 + 127) / 128) * 128 : 0;
   const int newBytes = hasNew ? ((p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128 : 0;
   T* sKn = reinterpret_cast<T*>(smemRaw + qBytes);           // appended K slice
   T* sVn = reinterpret_cast<T*>(smemRaw + qBytes + newBytes);  // appended V slice
@@ -286,11 +336,14 @@ decode_kernel(const DecodeParams p) {
   }
 
   // ---------------- consumers ----------------
-  const int hl = tid % hqMax;
+  const int hv = tid % hqMax;        // thread column
+  const int hl = hv / R;             // query head within the CTA
+  const int sub = hv % R;            // which W columns of the head
   const int slot = tid / hqMax;
-  const bool active = slot < KS && hl < hq;
+  const bool active = slot < KS && hv < hq;
   const int h = kvh0 * group + hl;   // query head
   const int kvl = hl / group;        // kv head within the CTA's slice
+  const unsigned groupMask = R == 1 ? 0u : (((1u << R) - 1u) << ((tid & 31) & ~(R - 1)));
 
   // Stage q (f32) and, in split 0, the appended K/V slices; with rope tables q and
   // the new K row are rotated here and rounded to T as the separate rope dispatch
@@ -306,7 +359,7 @@ decode_kernel(const DecodeParams p) {
     const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
     if (roped) {
       const int hp = hd >> 1;
-      for (int idx = tid; idx < hq * hp; idx += kConsumers) {
+      for (int idx = tid; idx < hqReal * hp; idx += kConsumers) {
         const int hh = idx / hp, x = (idx - hh * hp) * 2;
         const T* src = qg + (kvh0 * group + hh) * hd + x;
         float r0, r1;
@@ -315,7 +368,7 @@ decode_kernel(const DecodeParams p) {
         sQ[hh * QS + x + 1] = to_f32<T>(from_f32<T>(r1));
       }
     } else {
-      for (int idx = tid; idx < hq * hd; idx += kConsumers) {
+      for (int idx = tid; idx < hqReal * hd; idx += kConsumers) {
         const int hh = idx / hd, x = idx - hh * hd;
         sQ[hh * QS + x] = to_f32<T>(qg[(kvh0 * group + hh) * hd + x]);
       }
@@ -351,11 +404,23 @@ decode_kernel(const DecodeParams p) {
   }
 
   float m = kNegSeed, l = 0.f;
-  float acc[HDP];
-  constexpr bool ROT = Rotated<HDP, EXACT, VEC>::value;
-  const int rot = ROT ? (tid & (HDP / VEC - 1)) : 0;   // see Rotated
+  float acc[W];
+  constexpr bool ROT = R > 1 || Rotated<HDP, EXACT, VEC>::value;
+  // Threads whose rows start in the same bank take different rotations (see Rotated):
+  // with 64-byte slices every second thread does.
+  constexpr int kSameBank = (W * (int)sizeof(T) >= 128) ? 1 : 128 / (W * (int)sizeof(T));
+  const int rot = ROT ? ((tid / kSameBank) & (W / VEC - 1)) : 0;
 #pragma unroll
-  for (int x = 0; x < HDP; x++) acc[x] = 0.f;
+  for (int x = 0; x < W; x++) acc[x] = 0.f;
+  float qr[R > 1 ? W : 1];
+  if (R > 1) {
+#pragma unroll
+    for (int i = 0; i < W / VEC; i++) {
+      const int ci = (i + rot) & (W / VEC - 1);
+#pragma unroll
+      for (int e = 0; e < VEC; e++) qr[(i * VEC + e) % (R > 1 ? W : 1)] = qv[sub * W + ci * VEC + e];
+    }
+  }
   if (active && slot == 0 && split == 0 && p.sinks) {
     m = p.sinks[h];  // sinks are log2-space: sink * ln2 * log2e
     l = 1.f;
@@ -380,8 +445,9 @@ decode_kernel(const DecodeParams p) {
       named_barrier_sync(1, kConsumers);
     }
     if (active && slot < nk) {
-      const int off = slot * sliceElems + kvl * hd;
-      process_key<T, HDP, EXACT, VEC, QSMEM>(tK + off, tV + off, qv, hd, m, l, acc, rot);
+      const int off = slot * sliceElems + kvl * hd + sub * W;
+      if constexpr (R > 1) process_key_sub<T, W, VEC, R>(tK + off, tV + off, qr, m, l, acc, rot, groupMask);
+      else process_key<T, HDP, EXACT, VEC, QSMEM>(tK + off, tV + off, qv, hd, m, l, acc, rot);
     }
     if (BULK) {
       __syncwarp();
@@ -390,8 +456,11 @@ decode_kernel(const DecodeParams p) {
   }
 
   // Fused append: split 0 attends to the new row it staged (and stored) above.
-  if (appendHere && active && slot == 0)
-    process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + kvl * hd, sVn + kvl * hd, qv, hd, m, l, acc, rot);
+  if (appendHere && active && slot == 0) {
+    const int off = kvl * hd + sub * W;
+    if constexpr (R > 1) process_key_sub<T, W, VEC, R>(sKn + off, sVn + off, qr, m, l, acc, rot, groupMask);
+    else process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + off, sVn + off, qv, hd, m, l, acc, rot);
+  }
 
   if (!ok || sAbort) {
     // A wait ran out: record it, let copies in flight land, leave.
@@ -402,67 +471,69 @@ decode_kernel(const DecodeParams p) {
 
   // ---- merge the key slots of each head (log-sum-exp) ----
   named_barrier_sync(1, kConsumers);  // every tile consumed: the ring is free
-  float* sM = reinterpret_cast<float*>(ring);  // [KS][hqMax][2 + HDP]
-  constexpr int MS = 2 + HDP;
+  float* sM = reinterpret_cast<float*>(ring);  // [KS][hqMax][2 + W]
+  constexpr int MS = 2 + W;
   if (active) {
-    float* r = sM + (slot * hqMax + hl) * MS;
+    float* r = sM + (slot * hqMax + hv) * MS;
     r[0] = m;
     r[1] = l;
     if (ROT) {
 #pragma unroll
-      for (int i = 0; i < HDP / VEC; i++) {
-        float* dst = r + 2 + ((i + rot) & (HDP / VEC - 1)) * VEC;
+      for (int i = 0; i < W / VEC; i++) {
+        float* dst = r + 2 + ((i + rot) & (W / VEC - 1)) * VEC;
 #pragma unroll
         for (int e = 0; e < VEC; e++) dst[e] = acc[i * VEC + e];
       }
     } else {
 #pragma unroll
-      for (int x = 0; x < HDP; x++) r[2 + x] = acc[x];
+      for (int x = 0; x < W; x++) r[2 + x] = acc[x];
     }
   }
   named_barrier_sync(1, kConsumers);
 
   const int stride = 2 + hd;  // partials row in global memory
+  const int wd = R == 1 ? hd : W;   // columns this thread column owns ...
+  const int col0 = sub * W;         // ... starting here in the head
   if (active) {
     float M = kNegSeed;
-    for (int s = 0; s < KS; s++) M = fmaxf(M, sM[(s * hqMax + hl) * MS]);
+    for (int s = 0; s < KS; s++) M = fmaxf(M, sM[(s * hqMax + hv) * MS]);
     float L = 0.f;
-    float o[HDP];  // entry c holds output column slot + c*KS
-    for (int c = 0, x = slot; x < hd; x += KS, c++) o[c] = 0.f;
+    float o[W];  // entry c holds output column col0 + slot + c*KS
+    for (int c = 0, x = slot; x < wd; x += KS, c++) o[c] = 0.f;
     for (int s = 0; s < KS; s++) {
-      const float* r = sM + (s * hqMax + hl) * MS;
+      const float* r = sM + (s * hqMax + hv) * MS;
       const float w = fast_exp2(r[0] - M);
       L = fmaf(r[1], w, L);
-      for (int c = 0, x = slot; x < hd; x += KS, c++) o[c] = fmaf(r[2 + x], w, o[c]);
+      for (int c = 0, x = slot; x < wd; x += KS, c++) o[c] = fmaf(r[2 + x], w, o[c]);
     }
     const bool toPartials = partialsOut != nullptr;
     if (p.splits == 1) {
       if (toPartials) {
         float* dst = partialsOut + ((int64_t)b * p.qHeads + h) * stride;
-        if (slot == 0) {
+        if (slot == 0 && sub == 0) {
           dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
           dst[1] = L;
         }
         int c = 0;
-        for (int x = slot; x < hd; x += KS) dst[2 + x] = o[c++];
+        for (int x = slot; x < wd; x += KS) dst[2 + col0 + x] = o[c++];
       } else {
         const float invL = L > 0.f ? 1.f / L : 0.f;
-        T* dst = static_cast<T*>(p.out) + ((int64_t)b * p.qHeads + h) * hd;
+        T* dst = static_cast<T*>(p.out) + ((int64_t)b * p.qHeads + h) * hd + col0;
         int c = 0;
-        for (int x = slot; x < hd; x += KS) dst[x] = from_f32<T>(o[c++] * invL);
+        for (int x = slot; x < wd; x += KS) dst[x] = from_f32<T>(o[c++] * invL);
       }
     } else {
       float* dst = p.scratch + (((int64_t)b * p.splits + split) * p.qHeads + h) * stride;
-      if (slot == 0) {
+      if (slot == 0 && sub == 0) {
         dst[0] = M;
         dst[1] = L;
       }
       int c = 0;
-      for (int x = slot; x < hd; x += KS) dst[2 + x] = o[c++];
+      for (int x = slot; x < wd; x += KS) dst[2 + col0 + x] = o[c++];
     }
   }
   if (p.splits == 1) {
-    if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hq, kvh0 * group, tid);
+    if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hqReal, kvh0 * group, tid);
     return;
   }
 
@@ -486,7 +557,8 @@ decode_kernel(const DecodeParams p) {
       L = fmaf(__ldcg(base + s * ss + 1), fast_exp2(__ldcg(base + s * ss) - M), L);
     const bool toPartials = partialsOut != nullptr;
     const float invL = L > 0.f ? 1.f / L : 0.f;
-    for (int x = slot; x < hd; x += KS) {
+    for (int xx = slot; xx < wd; xx += KS) {
+      const int x = col0 + xx;
       float o = 0.f;
       for (int s = 0; s < p.splits; s++)
         o = fmaf(__ldcg(base + s * ss + 2 + x), fast_exp2(__ldcg(base + s * ss) - M), o);
@@ -495,14 +567,14 @@ decode_kernel(const DecodeParams p) {
       else
         static_cast<T*>(p.out)[((int64_t)b * p.qHeads + h) * hd + x] = from_f32<T>(o * invL);
     }
-    if (toPartials && slot == 0) {
+    if (toPartials && slot == 0 && sub == 0) {
       float* dst = partialsOut + ((int64_t)b * p.qHeads + h) * stride;
       dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
       dst[1] = L;
     }
   }
   if (tid == 0) p.counters[b * gridDim.z + zb] = 0;  // ready for the next launch
-  if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hq, kvh0 * group, tid);
+  if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hqReal, kvh0 * group, tid);
 }
 
 size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
@@ -511,7 +583,8 @@ size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
   const size_t qBytes = (((size_t)hqMax * q_stride(hdp) * 4 + 127) / 128) * 128;
   const size_t tileBytes = (((size_t)p.keySlots * p.kvPerCta * p.hd * esize + 127) / 128) * 128;
   const size_t ringBytes = (size_t)(bulk ? p.stages : 1) * 2 * tileBytes;
-  const size_t mergeBytes = (size_t)p.keySlots * hqMax * (2 + hdp) * 4;
+  const int lanes = p.lanesPerRow > 1 ? p.lanesPerRow : 1;
+  const size_t mergeBytes = (size_t)p.keySlots * hqMax * lanes * (2 + hdp / lanes) * 4;
   const size_t newBytes = p.kNew ? 2 * ((((size_t)p.kvPerCta * p.hd * esize) + 127) / 128) * 128 : 0;
   return qBytes + newBytes + (ringBytes > mergeBytes ? ringBytes : mergeBytes);
 }
@@ -532,9 +605,9 @@ bool bulk_ok(const DecodeParams& p, int esize) {
   return true;
 }
 
-template <typename T, int HDP, bool EXACT, int VEC, bool BULK>
+template <typename T, int HDP, bool EXACT, int VEC, bool BULK, int R = 1>
 cudaError_t launch_one(const DecodeParams& p, size_t smem, cudaStream_t s) {
-  auto kern = decode_kernel<T, HDP, EXACT, VEC, BULK>;
+  auto kern = decode_kernel<T, HDP, EXACT, VEC, BULK, R>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int zBlocks = (p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
@@ -552,10 +625,15 @@ cudaError_t launch_typed(const DecodeParams& p, cudaStream_t s) {
     switch (p.hd) {
       case 36: return launch_one<T, 36, true, 4, true>(p, smem, s);
       case 52: return launch_one<T, 52, true, 4, true>(p, smem, s);
-      case 64: return launch_one<T, 64, true, V, true>(p, smem, s);
-      case 128: return launch_one<T, 128, true, V, true>(p, smem, s);
+      case 64:
+        return p.lanesPerRow == 2 ? launch_one<T, 64, true, V, true, 2>(p, smem, s)
+                                  : launch_one<T, 64, true, V, true>(p, smem, s);
+      case 128:
+        return p.lanesPerRow == 4 ? launch_one<T, 128, true, V, true, 4>(p, smem, s)
+                                  : launch_one<T, 128, true, V, true>(p, smem, s);
     }
   }
+  if (p.lanesPerRow > 1) return cudaErrorInvalidValue;   // the plan promised the bulk path
   const int hdp = padded_hd(p.hd);
   const size_t smem = smem_bytes(p, esize, hdp, false);
   if (hdp == 32) return launch_one<T, 32, false, 1, false>(p, smem, s);
@@ -572,43 +650,86 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     *err = "decode: more than 256 query heads per kv head";
     return false;
   }
-  int kvPerCta = p.kvHeads;
-  while (kvPerCta * group > kConsumers) kvPerCta = (kvPerCta + 1) / 2;
   const int hdp = padded_hd(p.hd);
-  // Key slots per tile: 256 threads' worth, fewer when two stages of that many keys do not
-  // fit.  The heads stay together as long as a handful of key slots fit (wide heads then
-  // leave some threads idle): a CTA that owns all the heads fetches a tile with one bulk
-  // copy per tensor, while one that owns a single head needs a copy of hd elements per
-  // key — measured 1.0 TB/s at 32 heads x 128, the copy engine's rate for 256-byte copies.
-  constexpr int kMinKeySlots = 4;
-  int keySlots;
-  size_t budget;
-  for (;;) {
-    const size_t qBytes = (size_t)kvPerCta * group * q_stride(hdp) * 4 + 128 +
-                          (p.kNew ? 2 * ((size_t)kvPerCta * p.hd * esize + 128) : 0);
-    budget = (hdp <= 64 ? kSmemBudgetTwoPerSm : kSmemBudget) - qBytes;
-    keySlots = kConsumers / (kvPerCta * group);
-    const size_t perSlot = 2ull * kvPerCta * p.hd * esize;            // K+V bytes of one key
-    const size_t mergePerSlot = (size_t)kvPerCta * group * (2 + hdp) * 4;
-    const size_t capTile = (budget / 2 - 256) / perSlot;               // two stages must fit
-    const size_t capMerge = budget / mergePerSlot;
-    const size_t cap = capTile < capMerge ? capTile : capMerge;
-    if (cap < (size_t)(keySlots < kMinKeySlots ? keySlots : kMinKeySlots) && kvPerCta > 1) {
-      kvPerCta = (kvPerCta + 1) / 2;
-      continue;
+  // Head size 64 and 128: 2 or 4 threads share a (key, head) pair, 32 columns each (see
+  // process_key_sub); that needs the bulk path, so fall back to whole rows without it.
+  int lanes = p.hd == 128 ? 4 : p.hd == 64 ? 2 : 1;
+  if (group * lanes > kConsumers) lanes = 1;
+  // One geometry for a given shared-memory budget per CTA.
+  struct Geom {
+    int kvPerCta, keySlots, stages;
+    size_t tile;
+    bool fits;
+  };
+  auto geometry = [&](size_t budgetTotal, int lanesNow) {
+    const int wdp = hdp / lanesNow;   // columns per thread
+    Geom g{};
+    g.kvPerCta = p.kvHeads;
+    while (g.kvPerCta * group * lanesNow > kConsumers) g.kvPerCta = (g.kvPerCta + 1) / 2;
+    // Key slots per tile: 256 threads' worth, fewer when two stages of that many keys do not
+    // fit.  The heads stay together as long as a handful of key slots fit (wide heads then
+    // leave some threads idle): a CTA that owns all the heads fetches a tile with one bulk
+    // copy per tensor, while one that owns a single head needs a copy of hd elements per
+    // key — measured 1.0 TB/s at 32 heads x 128, the copy engine's rate for 256-byte copies.
+    constexpr int kMinKeySlots = 4;
+    size_t budget;
+    for (;;) {
+      const size_t qBytes = (size_t)g.kvPerCta * group * q_stride(hdp) * 4 + 128 +
+                            (p.kNew ? 2 * ((size_t)g.kvPerCta * p.hd * esize + 128) : 0);
+      budget = budgetTotal > qBytes ? budgetTotal - qBytes : 0;
+      g.keySlots = kConsumers / (g.kvPerCta * group * lanesNow);
+      const size_t perSlot = 2ull * g.kvPerCta * p.hd * esize;            // K+V bytes of one key
+      const size_t mergePerSlot = (size_t)g.kvPerCta * group * lanesNow * (2 + wdp) * 4;
+      const size_t capTile = budget / 2 > 256 ? (budget / 2 - 256) / perSlot : 0;   // two stages must fit
+      const size_t capMerge = budget / mergePerSlot;
+      const size_t cap = capTile < capMerge ? capTile : capMerge;
+      if (cap < (size_t)(g.keySlots < kMinKeySlots ? g.keySlots : kMinKeySlots) && g.kvPerCta > 1) {
+        g.kvPerCta = (g.kvPerCta + 1) / 2;
+        continue;
+      }
+      g.fits = cap >= 1;
+      if (g.fits && (size_t)g.keySlots > cap) g.keySlots = (int)cap;
+      break;
     }
-    if (cap < 1) {
+    g.tile = ((2ull * g.keySlots * g.kvPerCta * p.hd * esize + 255) / 256) * 256 + 256;
+    const int stages = g.fits ? (int)(budget / g.tile) : 0;
+    g.stages = stages < 2 ? 2 : stages > kMaxStages ? kMaxStages : stages;
+    return g;
+  };
+  // Up to 64 columns per thread, two CTAs fit an SM (registers); whether to give each half
+  // of the shared memory or one all of it is decided by the bytes the rings then keep in
+  // flight per SM (every stage but the one being consumed): a 100-byte row fills two half
+  // rings well, 32 heads x 128 leave a half ring two 32 KB stages (measured 2.7 TB/s).
+  Geom g{};
+  int ctasPerSm = 1;
+  for (;; lanes = 1) {
+    const bool twoFit = hdp / lanes <= 64;
+    const Geom one = geometry(kSmemBudget, lanes);
+    g = one;
+    ctasPerSm = 1;
+    if (twoFit) {
+      const Geom two = geometry(kSmemBudgetTwoPerSm, lanes);
+      const size_t flightOne = one.fits ? (size_t)(one.stages - 1) * one.tile : 0;
+      const size_t flightTwo = two.fits ? 2 * (size_t)(two.stages - 1) * two.tile : 0;
+      // (whole-row threads, head sizes up to 64: two, as measured on the Moonshine shapes)
+      if (two.fits && (lanes == 1 || 3 * flightTwo >= 2 * flightOne)) {
+        g = two;
+        ctasPerSm = 2;
+      }
+    }
+    p.kvPerCta = g.kvPerCta;
+    p.lanesPerRow = lanes;
+    if (lanes > 1 && !(g.fits && bulk_ok(p, esize))) continue;   // once more with whole rows
+    if (!g.fits) {
       *err = "decode: heads too wide for shared memory";
       return false;
     }
-    if ((size_t)keySlots > cap) keySlots = (int)cap;
     break;
   }
+  const int kvPerCta = g.kvPerCta, keySlots = g.keySlots;
   p.kvPerCta = kvPerCta;
   p.keySlots = keySlots;
-  const size_t tile = ((2ull * keySlots * kvPerCta * p.hd * esize + 255) / 256) * 256 + 256;
-  int stages = (int)(budget / tile);
-  p.stages = stages < 2 ? 2 : stages > kMaxStages ? kMaxStages : stages;
+  p.stages = g.stages;
 
   if (p.splits <= 0) {
     const int zBlocks = (p.kvHeads + kvPerCta - 1) / kvPerCta;
@@ -622,7 +743,7 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     // pipeline-fill and merge cost (about three tiles' worth, measured), CTAs run in
     // waves of `resident` at a time, and splitting adds the partials pass.  Measured
     // on B200: with at least one wave of sequences, not splitting is fastest.
-    const int64_t resident = (int64_t)smCount * (hdp <= 64 ? 2 : 1);
+    const int64_t resident = (int64_t)smCount * ctasPerSm;
     int best = 1;
     int64_t bestCost = INT64_MAX;
     for (int s = 1; s <= maxS; s++) {
