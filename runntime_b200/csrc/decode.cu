@@ -198,6 +198,57 @@ __device__ __forceinline__ void process_key_sub(const T* kp, const T* vp, const 
   }
 }
 
+// Two keys at once for the same thread: the two dot products, their shuffles and the two
+// accumulations are independent instruction streams, which a thread with one key at a time
+// does not have (nine warps per SM hide little latency).
+template <typename T, int W, int VEC, int R>
+__device__ __forceinline__ void process_key_pair(const T* ka, const T* va, const T* kb, const T* vb,
+                                                 const float (&q)[W], float& m, float& l,
+                                                 float (&acc)[W], int rot, unsigned groupMask) {
+  constexpr int NCH = W / VEC;
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; i++) {
+    const int ci = (i + rot) & (NCH - 1);
+    float fa[VEC], fb[VEC];
+    Loader<T, VEC>::load(ka + ci * VEC, fa);
+    Loader<T, VEC>::load(kb + ci * VEC, fb);
+#pragma unroll
+    for (int e = 0; e < VEC; e += 2) {
+      a0 = fmaf(q[i * VEC + e], fa[e], a0);
+      a1 = fmaf(q[i * VEC + e + 1], fa[e + 1], a1);
+      b0 = fmaf(q[i * VEC + e], fb[e], b0);
+      b1 = fmaf(q[i * VEC + e + 1], fb[e + 1], b1);
+    }
+  }
+  float sa = a0 + a1, sb = b0 + b1;
+#pragma unroll
+  for (int o = 1; o < R; o <<= 1) {
+    sa += __shfl_xor_sync(groupMask, sa, o);
+    sb += __shfl_xor_sync(groupMask, sb, o);
+  }
+  sa *= kLog2e, sb *= kLog2e;  // log2 domain
+  const float mn = fmaxf(sa, sb);
+  if (mn > m) {
+    const float c = fast_exp2(m - mn);
+    l *= c;
+#pragma unroll
+    for (int x = 0; x < W; x++) acc[x] *= c;
+    m = mn;
+  }
+  const float pa = fast_exp2(sa - m), pb = fast_exp2(sb - m);
+  l += pa + pb;
+#pragma unroll
+  for (int i = 0; i < NCH; i++) {
+    const int ci = (i + rot) & (NCH - 1);
+    float fa[VEC], fb[VEC];
+    Loader<T, VEC>::load(va + ci * VEC, fa);
+    Loader<T, VEC>::load(vb + ci * VEC, fb);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) acc[i * VEC + e] = fmaf(pa, fa[e], fmaf(pb, fb[e], acc[i * VEC + e]));
+  }
+}
+
 // Cross-GPU hand-over, called by the consumer threads of the block that wrote the final
 // rows of (sequence b, head block zb) into this rank's slot: copies those rows into the
 // same slot of every peer's buffer (plain stores to peer memory).  The ranks are told by
@@ -427,7 +478,38 @@ decode_kernel(const DecodeParams p) {
   }
 
   bool ok = true;
-  for (int it = 0; it < ntiles; it++) {
+  int it = 0;
+  if constexpr (R > 1) {
+    // Tiles two at a time while the ring is deep enough to keep copies in flight behind them.
+    if (stages >= 4) {
+      for (; it + 1 < ntiles; it += 2) {
+        const int sa = it % stages, sb = (it + 1) % stages;
+        if (!mbar_wait(smem_u32(&sFull[sa]), (it / stages) & 1, &sAbort) ||
+            !mbar_wait(smem_u32(&sFull[sb]), ((it + 1) / stages) & 1, &sAbort)) {
+          ok = false;
+          break;
+        }
+        const T* aK = reinterpret_cast<const T*>(ring + (size_t)sa * 2 * tileBytes);
+        const T* bK = reinterpret_cast<const T*>(ring + (size_t)sb * 2 * tileBytes);
+        const int nkb = (int)min((int64_t)KS, s1 - (s0 + (int64_t)(it + 1) * KS));  // tile `it` is full
+        if (active) {
+          const int off = slot * sliceElems + kvl * hd + sub * W;
+          const int vOff = tileBytes / (int)sizeof(T);
+          if (slot < nkb)
+            process_key_pair<T, W, VEC, R>(aK + off, aK + vOff + off, bK + off, bK + vOff + off, qr, m,
+                                           l, acc, rot, groupMask);
+          else
+            process_key_sub<T, W, VEC, R>(aK + off, aK + vOff + off, qr, m, l, acc, rot, groupMask);
+        }
+        __syncwarp();
+        if ((tid & 31) == 0) {
+          mbar_arrive(smem_u32(&sEmpty[sa]));
+          mbar_arrive(smem_u32(&sEmpty[sb]));
+        }
+      }
+    }
+  }
+  for (; it < ntiles && ok; it++) {
     const int64_t k0 = s0 + (int64_t)it * KS;
     const int nk = (int)min((int64_t)KS, s1 - k0);
     const int s = BULK ? it % stages : 0;
