@@ -333,8 +333,10 @@ decode_kernel(const DecodeParams p) {
   // Shared-memory carve-up: [q][appended K, V slices][ring: stages x (K tile, V tile)];
   // the ring is reused for the slot merge at the end.
   float* sQ = reinterpret_cast<float*>(smemRaw);
-  const int qBytes = QSMEM ? ((hqMax / R * QS * 4 + 127) / 128) * 128 : 0;
-  const int newBytes = hasNew ? ((p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128 : 0;
+  // (threads that own a slice of a head keep q in registers and read the appended row back
+  // from the cache: no staging areas)
+  const int qBytes = R == 1 ? ((hqMax * QS * 4 + 127) / 128) * 128 : 0;
+  const int newBytes = (R == 1 && hasNew) ? ((p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128 : 0;
   T* sKn = reinterpret_cast<T*>(smemRaw + qBytes);           // appended K slice
   T* sVn = reinterpret_cast<T*>(smemRaw + qBytes + newBytes);  // appended V slice
   unsigned char* ring = smemRaw + qBytes + 2 * newBytes;
@@ -402,13 +404,15 @@ decode_kernel(const DecodeParams p) {
   // writeRows would do) and is attended from shared memory after the cache keys.
   const bool appendHere = hasNew && split == 0 && !p.useRange && L >= 1;
   const float* qv = sQ + hl * QS;
+  const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qRowStride;
+  const bool roped = p.ropeCos != nullptr && !p.useRange;
+  const int64_t ropeRow = p.ropeByPos ? (L >= 1 ? L - 1 : 0) : b;
+  const float* rc = roped ? p.ropeCos + ropeRow * hd : nullptr;
+  const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
   {
-    const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qRowStride;
-    const bool roped = p.ropeCos != nullptr && !p.useRange;
-    const int64_t ropeRow = p.ropeByPos ? (L >= 1 ? L - 1 : 0) : b;
-    const float* rc = roped ? p.ropeCos + ropeRow * hd : nullptr;
-    const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
-    if (roped) {
+    if (R > 1) {
+      // q goes straight to registers below
+    } else if (roped) {
       const int hp = hd >> 1;
       for (int idx = tid; idx < hqReal * hp; idx += kConsumers) {
         const int hh = idx / hp, x = (idx - hh * hp) * 2;
@@ -436,18 +440,18 @@ decode_kernel(const DecodeParams p) {
           float r0, r1;
           rope_pair(to_f32<T>(kn[hh * hd + x]), to_f32<T>(kn[hh * hd + x + 1]), rc[x], rs[x], r0, r1);
           const T t0 = from_f32<T>(r0), t1 = from_f32<T>(r1);
-          sKn[hh * hd + x] = t0, sKn[hh * hd + x + 1] = t1;
+          if (R == 1) sKn[hh * hd + x] = t0, sKn[hh * hd + x + 1] = t1;
           kc[hh * hd + x] = t0, kc[hh * hd + x + 1] = t1;
         }
       }
       for (int x = tid; x < sliceElems; x += kConsumers) {
         if (!roped) {
           const T t = kn[x];
-          sKn[x] = t;
+          if (R == 1) sKn[x] = t;
           kc[x] = t;
         }
         const T u = vn[x];
-        sVn[x] = u;
+        if (R == 1) sVn[x] = u;
         vc[x] = u;
       }
     }
@@ -465,11 +469,30 @@ decode_kernel(const DecodeParams p) {
   for (int x = 0; x < W; x++) acc[x] = 0.f;
   float qr[R > 1 ? W : 1];
   if (R > 1) {
+    // This thread's W columns of q, rotated like the rows it will walk, with the rope applied
+    // and rounded to T as the separate rope dispatch would store them.
 #pragma unroll
-    for (int i = 0; i < W / VEC; i++) {
-      const int ci = (i + rot) & (W / VEC - 1);
+    for (int x = 0; x < (R > 1 ? W : 1); x++) qr[x] = 0.f;
+    if (hv < hq) {
+      const T* src = qg + (int64_t)h * hd + sub * W;
 #pragma unroll
-      for (int e = 0; e < VEC; e++) qr[(i * VEC + e) % (R > 1 ? W : 1)] = qv[sub * W + ci * VEC + e];
+      for (int i = 0; i < W / VEC; i++) {
+        const int ci = (i + rot) & (W / VEC - 1);
+        float f[VEC];
+        Loader<T, VEC>::load(src + ci * VEC, f);
+#pragma unroll
+        for (int e = 0; e < VEC; e += 2) {
+          float r0 = f[e], r1 = f[e + 1];
+          if (roped) {
+            const int x = sub * W + ci * VEC + e;
+            rope_pair(f[e], f[e + 1], rc[x], rs[x], r0, r1);
+            r0 = to_f32<T>(from_f32<T>(r0));
+            r1 = to_f32<T>(from_f32<T>(r1));
+          }
+          qr[(i * VEC + e) % (R > 1 ? W : 1)] = r0;
+          qr[(i * VEC + e + 1) % (R > 1 ? W : 1)] = r1;
+        }
+      }
     }
   }
   if (active && slot == 0 && split == 0 && p.sinks) {
@@ -540,7 +563,10 @@ decode_kernel(const DecodeParams p) {
   // Fused append: split 0 attends to the new row it staged (and stored) above.
   if (appendHere && active && slot == 0) {
     const int off = kvl * hd + sub * W;
-    if constexpr (R > 1) process_key_sub<T, W, VEC, R>(sKn + off, sVn + off, qr, m, l, acc, rot, groupMask);
+    // (sub-row threads read the row this block stored to the cache before the barrier above)
+    if constexpr (R > 1)
+      process_key_sub<T, W, VEC, R>(kBase + (L - 1) * rowElems + off, vBase + (L - 1) * rowElems + off, qr,
+                                    m, l, acc, rot, groupMask);
     else process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + off, sVn + off, qv, hd, m, l, acc, rot);
   }
 
@@ -662,12 +688,13 @@ decode_kernel(const DecodeParams p) {
 size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
   const int group = p.qHeads / p.kvHeads;
   const int hqMax = p.kvPerCta * group;
-  const size_t qBytes = (((size_t)hqMax * q_stride(hdp) * 4 + 127) / 128) * 128;
+  const bool staged = p.lanesPerRow <= 1;   // see the kernel's carve-up
+  const size_t qBytes = staged ? (((size_t)hqMax * q_stride(hdp) * 4 + 127) / 128) * 128 : 0;
   const size_t tileBytes = (((size_t)p.keySlots * p.kvPerCta * p.hd * esize + 127) / 128) * 128;
   const size_t ringBytes = (size_t)(bulk ? p.stages : 1) * 2 * tileBytes;
   const int lanes = p.lanesPerRow > 1 ? p.lanesPerRow : 1;
   const size_t mergeBytes = (size_t)p.keySlots * hqMax * lanes * (2 + hdp / lanes) * 4;
-  const size_t newBytes = p.kNew ? 2 * ((((size_t)p.kvPerCta * p.hd * esize) + 127) / 128) * 128 : 0;
+  const size_t newBytes = (staged && p.kNew) ? 2 * ((((size_t)p.kvPerCta * p.hd * esize) + 127) / 128) * 128 : 0;
   return qBytes + newBytes + (ringBytes > mergeBytes ? ringBytes : mergeBytes);
 }
 
@@ -756,7 +783,8 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     constexpr int kMinKeySlots = 4;
     size_t budget;
     for (;;) {
-      const size_t qBytes = (size_t)g.kvPerCta * group * q_stride(hdp) * 4 + 128 +
+      const size_t qBytes = lanesNow > 1 ? 128 :   // sub-row threads stage neither q nor the new row
+                            (size_t)g.kvPerCta * group * q_stride(hdp) * 4 + 128 +
                             (p.kNew ? 2 * ((size_t)g.kvPerCta * p.hd * esize + 128) : 0);
       budget = budgetTotal > qBytes ? budgetTotal - qBytes : 0;
       g.keySlots = kConsumers / (g.kvPerCta * group * lanesNow);
@@ -778,10 +806,12 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     g.stages = stages < 2 ? 2 : stages > kMaxStages ? kMaxStages : stages;
     return g;
   };
-  // Up to 64 columns per thread, two CTAs fit an SM (registers); whether to give each half
-  // of the shared memory or one all of it is decided by the bytes the rings then keep in
-  // flight per SM (every stage but the one being consumed): a 100-byte row fills two half
-  // rings well, 32 heads x 128 leave a half ring two 32 KB stages (measured 2.7 TB/s).
+  // Up to 64 columns per thread, two CTAs fit an SM (registers), each with half of the
+  // shared memory: one's set-up and merge overlap the other's streaming.  Sub-row threads
+  // with only a few sequences to work on do better with one CTA per SM and a deep ring
+  // (fewer, longer key splits; two tiles per barrier round): measured at 32 heads x 128,
+  // KV 4096, 8 / 16 / 32 / 64 sequences: 147 / 195 / 261 / 249 us with one against
+  // 270 / 286 / 234 / 248 us with two; the same crossing at 8 heads and at head size 64.
   Geom g{};
   int ctasPerSm = 1;
   for (;; lanes = 1) {
@@ -791,10 +821,9 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     ctasPerSm = 1;
     if (twoFit) {
       const Geom two = geometry(kSmemBudgetTwoPerSm, lanes);
-      const size_t flightOne = one.fits ? (size_t)(one.stages - 1) * one.tile : 0;
-      const size_t flightTwo = two.fits ? 2 * (size_t)(two.stages - 1) * two.tile : 0;
-      // (whole-row threads, head sizes up to 64: two, as measured on the Moonshine shapes)
-      if (two.fits && (lanes == 1 || 3 * flightTwo >= 2 * flightOne)) {
+      const int64_t seqCtas = (int64_t)p.batch * ((p.kvHeads + one.kvPerCta - 1) / one.kvPerCta);
+      const bool fewSequences = lanes > 1 && one.fits && seqCtas * 8 <= smCount;
+      if (two.fits && !fewSequences) {
         g = two;
         ctasPerSm = 2;
       }
