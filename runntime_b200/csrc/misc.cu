@@ -206,16 +206,27 @@ __global__ void rope_vec_kernel(const T* __restrict__ x, const float* __restrict
     }
     const T* src = x + row * srcCols + srcStart + c0;
     T* dst = out + row * width + c0;
-    for (int h = 0; h < nHeads; h++) {
-      Word raw = *reinterpret_cast<const Word*>(src + (int64_t)h * hd);
-      T* v = reinterpret_cast<T*>(&raw);
+    // Four heads per round, their loads issued together: one 16-byte load in flight per
+    // thread does not cover the DRAM latency (measured 4.4 TB/s against 5.x with four).
+    constexpr int U = 4;
+    for (int h0 = 0; h0 < nHeads; h0 += U) {
+      Word raw[U];
 #pragma unroll
-      for (int e = 0; e < V / 2; e++) {
-        float r0, r1;
-        rope_pair(to_f32<T>(v[2 * e]), to_f32<T>(v[2 * e + 1]), c[e], sn[e], r0, r1);
-        v[2 * e] = from_f32<T>(r0), v[2 * e + 1] = from_f32<T>(r1);
+      for (int u = 0; u < U; u++)
+        if (h0 + u < nHeads) raw[u] = *reinterpret_cast<const Word*>(src + (int64_t)(h0 + u) * hd);
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        if (h0 + u < nHeads) {
+          T* v = reinterpret_cast<T*>(&raw[u]);
+#pragma unroll
+          for (int e = 0; e < V / 2; e++) {
+            float r0, r1;
+            rope_pair(to_f32<T>(v[2 * e]), to_f32<T>(v[2 * e + 1]), c[e], sn[e], r0, r1);
+            v[2 * e] = from_f32<T>(r0), v[2 * e + 1] = from_f32<T>(r1);
+          }
+          *reinterpret_cast<Word*>(dst + (int64_t)(h0 + u) * hd) = raw[u];
+        }
       }
-      *reinterpret_cast<Word*>(dst + (int64_t)h * hd) = raw;
     }
   }
 }
