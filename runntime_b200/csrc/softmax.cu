@@ -83,16 +83,33 @@ softmax_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __rest
   const T* xr = x + row * cols;
   T* orow = out + row * cols;
   float m = kNegMax, s = 0.f;
+  // Quads of columns [q0, q1) touch the kept range; only the first and the last of them
+  // can hold masked columns (32-bit column arithmetic: the launcher takes this path only for
+  // rows shorter than 2^31).
+  const int lo32 = (int)lo, hi32 = (int)hi;
+  const int q0 = lo32 >> 2, q1 = hi32 > lo32 ? (hi32 + 3) >> 2 : q0;
   if (VEC4) {
     const QV* xq = reinterpret_cast<const QV*>(xr);
-    for (int64_t i = (lo >> 2) + t; i < (hi + 3) >> 2; i += span) {
+    for (int i = q0 + t; i < q1; i += span) {
       float f[4];
       Q::unpack(xq[i], f);
+      const int j = i * 4;
+      const bool inner = j >= lo32 && j + 4 <= hi32;
+      if (!inner) {
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+          if (j + e < lo32 || j + e >= hi32) f[e] = kNegMax;
+      }
+      // one running-sum rescale per quad instead of per element: five exponentials for four columns
+      const float mNew = fmaxf(m, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
+      float add = 0.f;
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const int64_t j = i * 4 + e;
-        if (j >= lo && j < hi) fold(m, s, f[e]);
+        const float pe = __expf(f[e] - mNew);
+        add += (inner || (j + e >= lo32 && j + e < hi32)) ? pe : 0.f;
       }
+      s = s * __expf(m - mNew) + add;
+      m = mNew;
     }
   } else {
     for (int64_t j = lo + t; j < hi; j += span) fold(m, s, to_f32<T>(xr[j]));
@@ -113,14 +130,19 @@ softmax_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __rest
   if (VEC4) {
     const QV* xq = reinterpret_cast<const QV*>(xr);
     QV* oq = reinterpret_cast<QV*>(orow);
-    for (int64_t i = t; i < cols >> 2; i += span) {
+    const int nq = (int)(cols >> 2);
+    for (int i = t; i < nq; i += span) {
       float f[4] = {0.f, 0.f, 0.f, 0.f};
-      if (i >= (lo >> 2) && i < (hi + 3) >> 2) {
+      if (i >= q0 && i < q1) {
         Q::unpack(xq[i], f);
+        const int j = i * 4;
+        if (j >= lo32 && j + 4 <= hi32) {
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int64_t j = i * 4 + e;
-          f[e] = (j >= lo && j < hi) ? __expf(f[e] - m) * inv : 0.f;
+          for (int e = 0; e < 4; e++) f[e] = __expf(f[e] - m) * inv;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; e++)
+            f[e] = (j + e >= lo32 && j + e < hi32) ? __expf(f[e] - m) * inv : 0.f;
         }
       }
       oq[i] = Q::pack(f);
@@ -140,7 +162,7 @@ cudaError_t softmax_typed(const void* x, void* out, const float* segs, int64_t r
   auto* xi = static_cast<const T*>(x);
   auto* oi = static_cast<T*>(out);
   const uintptr_t quad = 4 * sizeof(T);
-  const bool vec4 = cols % 4 == 0 && reinterpret_cast<uintptr_t>(x) % quad == 0 &&
+  const bool vec4 = cols % 4 == 0 && cols < (1ll << 31) - 8 && reinterpret_cast<uintptr_t>(x) % quad == 0 &&
                     reinterpret_cast<uintptr_t>(out) % quad == 0;
   const bool warpRows = cols <= kWarpRowCols;
   const int64_t blocks = warpRows ? (rows + kThreads / 32 - 1) / (kThreads / 32) : rows;
