@@ -131,19 +131,24 @@ softmax_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __rest
     const QV* xq = reinterpret_cast<const QV*>(xr);
     QV* oq = reinterpret_cast<QV*>(orow);
     const int nq = (int)(cols >> 2);
-    for (int i = t; i < nq; i += span) {
-      float f[4] = {0.f, 0.f, 0.f, 0.f};
-      if (i >= q0 && i < q1) {
-        Q::unpack(xq[i], f);
-        const int j = i * 4;
-        if (j >= lo32 && j + 4 <= hi32) {
+    // zeros either side of the kept range: stores only
+    const float z4[4] = {0.f, 0.f, 0.f, 0.f};
+    const QV zero = Q::pack(z4);
+#pragma unroll 4
+    for (int i = t; i < q0; i += span) oq[i] = zero;
+#pragma unroll 4
+    for (int i = q1 + t; i < nq; i += span) oq[i] = zero;
+    for (int i = q0 + t; i < q1; i += span) {
+      float f[4];
+      Q::unpack(xq[i], f);
+      const int j = i * 4;
+      if (j >= lo32 && j + 4 <= hi32) {
 #pragma unroll
-          for (int e = 0; e < 4; e++) f[e] = __expf(f[e] - m) * inv;
-        } else {
+        for (int e = 0; e < 4; e++) f[e] = __expf(f[e] - m) * inv;
+      } else {
 #pragma unroll
-          for (int e = 0; e < 4; e++)
-            f[e] = (j + e >= lo32 && j + e < hi32) ? __expf(f[e] - m) * inv : 0.f;
-        }
+        for (int e = 0; e < 4; e++)
+          f[e] = (j + e >= lo32 && j + e < hi32) ? __expf(f[e] - m) * inv : 0.f;
       }
       oq[i] = Q::pack(f);
     }
