@@ -123,6 +123,10 @@ def _decoder_step(ex, dtype, heads, kvHeads, hd, rows, t, *, fused, seed=21):
     ("f16", 14, 2, 64, 600, 511),   # GQA
     ("f32", 4, 4, 38, 64, 9),       # head width off the vector paths
     ("f16", 8, 8, 128, 300, 299),
+    ("f32", 8, 8, 128, 200, 150),    # four threads per (key, head) pair, f32 rows
+    ("f32", 4, 4, 64, 333, 332),     # two threads per pair
+    ("f16", 32, 32, 128, 700, 650),  # a wide model: two keys of all heads per tile
+    ("f16", 32, 8, 128, 300, 0),     # first token, grouped heads
 ])
 def test_decoder_layer_step_in_one_launch(ex, dtype, heads, kvHeads, hd, rows, t):
     qw, kvw = heads * hd, kvHeads * hd
