@@ -133,6 +133,7 @@ class Prefill:
         c = self.cfg
         if self.nb == 0:
             return
+        self.ex.setStream(self.torch.cuda.current_stream().cuda_stream)
         wl, wr = self.windows(layer)
         prefill_batched(self.ex, self.q, self.k, self.v, self.out, dtype=c["dtype"], batch=self.nb,
                         seqStride=c["seq"], seqLens=self.lens, qHeads=c["qHeads"],
@@ -141,6 +142,44 @@ class Prefill:
     def io_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.q, self.k, self.v)), \
             self.out.numel() * self.out.element_size()
+
+    def verify(self):
+        """Runs every distinct layer once and checks a sample of output rows of this rank's
+        first and last sequences against the f64 oracle (a row's output depends only on that
+        row's q, so the sample is exact for the rows it covers).  Returns (worst absolute
+        error, rows checked, all within tolerance)."""
+        import numpy as np
+        import oracle
+        c, S, t = self.cfg, self.cfg["seq"], self.torch
+        if self.nb == 0:
+            return 0.0, 0, True
+        worst, nrows, ok = 0.0, 0, True
+        tol = oracle.TOLERANCE[c["dtype"]]
+        layers = sorted({0, self.layers - 1})
+        for layer in layers:
+            self.out.fill_(7.0)
+            self.step(layer)
+            t.cuda.synchronize()
+            wl, wr = self.windows(layer)
+            for b in sorted({0, self.nb - 1}):
+                L = int(self.lens_all[self.b0 + b])
+                q, k, v = (x[b * S:b * S + L].float().cpu().numpy() for x in (self.q, self.k, self.v))
+                got = self.out[b * S:(b + 1) * S].float().cpu().numpy()
+                rows = sorted({0, 1, L // 3, L // 2, L - 129 if L > 129 else 0, L - 2 if L > 1 else 0, L - 1}
+                              | {r for r in (127, 128, 255, 256, 511, 512, 513) if r < L})
+                for r in rows:
+                    hi = L if wr is None else min(L, r + wr + 1)   # keys past the band are never read
+                    want = oracle.sdpa_ref(q[r:r + 1], k[:hi], v[:hi], qHeads=c["qHeads"],
+                                           kvHeads=c["kvHeads"], headDim=c["hd"],
+                                           windowLeft=math.inf if wl is None else wl,
+                                           windowRight=math.inf if wr is None else wr,
+                                           qPosOffset=r).reshape(-1)
+                    err = np.abs(got[r] - want)
+                    worst = max(worst, float(err.max()))
+                    ok &= bool(np.all(err <= tol["atol"] + tol["rtol"] * np.abs(want)))
+                    nrows += 1
+                ok &= bool((got[L:] == 0).all())     # rows past the length are zeros
+        return worst, nrows, ok
 
     def make_host(self):
         t = self.torch
@@ -189,57 +228,75 @@ class Prefill:
 class Decode:
     def __init__(self, cfg, rank, world, ex):
         import torch
-        from runntime_b200.engine import ShardedDecode, shard_rows
+        from runntime_b200.engine import ShardedDecode
         self.cfg, self.ex, self.torch, self.world, self.rank = cfg, ex, torch, world, rank
         dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
         b, hd, H = cfg["batch"], cfg["hd"], cfg["kvHeads"]
         w = H * hd
         self.shard_kv = cfg["lens"] is None  # long-context: split KV rows across ranks
         gl = torch.Generator(device="cpu").manual_seed(77)
+        self.b0 = 0
         if self.shard_kv:
-            s, e = shard_rows(cfg["cacheRows"], world, rank)
-            self.rows = e - s
+            # every rank holds positions [rank*rows, (rank+1)*rows) of every sequence
+            self.rows = -(-cfg["cacheRows"] // world)
+            self.shardStart = rank * self.rows
             self.b = b
             self.lens_all = [cfg["cacheRows"]] * b
-            self.lens = None
+            self.lens = torch.full((b,), cfg["cacheRows"], dtype=torch.int32, device=dev)
         else:
             per = -(-b // world)
             b0, b1 = min(rank * per, b), min((rank + 1) * per, b)
-            self.b = b1 - b0
+            self.b0, self.b = b0, b1 - b0
             lens = torch.randint(cfg["lens"][0], cfg["lens"][1] + 1, (b,), generator=gl)
             self.lens_all = lens.tolist()
             self.lens_mine = self.lens_all[b0:b1]
             self.lens = lens[b0:b1].to(torch.int32).to(dev)
             self.rows = cfg["cacheRows"]
+            self.shardStart = 0
         gd = torch.Generator(device=dev).manual_seed(2000 + rank)
         nb = max(self.b, 1)
         self.k = torch.randn(nb, self.rows, w, generator=gd, device=dev, dtype=torch.float16)
         self.v = torch.randn(nb, self.rows, w, generator=gd, device=dev, dtype=torch.float16)
-        gq = torch.Generator(device=dev).manual_seed(3000)  # q is the same on every rank
-        self.q = (torch.randn(nb, cfg["qHeads"] * hd, generator=gq, device=dev)
-                  * hd ** -0.5).to(torch.float16)
-        self.out = torch.empty_like(self.q)
-        self.kNew = self.vNew = None
-        if not self.shard_kv:
-            self.kNew = torch.randn(nb, w, generator=gd, device=dev, dtype=torch.float16)
-            self.vNew = torch.randn(nb, w, generator=gd, device=dev, dtype=torch.float16)
+        gq = torch.Generator(device=dev).manual_seed(3000)  # q and the new row: the same on every rank
+        self.q = (torch.randn(cfg["batch"], cfg["qHeads"] * hd, generator=gq, device=dev)
+                  * hd ** -0.5).to(torch.float16)[self.b0:self.b0 + nb].contiguous()
+        self.kNew = torch.randn(cfg["batch"], w, generator=gq, device=dev,
+                                dtype=torch.float16)[self.b0:self.b0 + nb].contiguous()
+        self.vNew = torch.randn(cfg["batch"], w, generator=gq, device=dev,
+                                dtype=torch.float16)[self.b0:self.b0 + nb].contiguous()
+        self.out = torch.zeros_like(self.q)
         if cfg["cross"]:
             self.ck = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
             self.cv = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
             self.out2 = torch.empty_like(self.q)
         # KV rows split over ranks: the partials are traded through peer memory by the decode
-        # kernel itself (--exchange peer, the default) or by one NCCL all-gather (--exchange nccl,
-        # also the fallback when symmetric memory cannot be set up).
+        # kernel itself (--exchange peer, the default; the peers' blocks mapped through the
+        # library's own CUDA-IPC set-up, or torch's symmetric memory if that fails) or by one
+        # NCCL all-gather (--exchange nccl, also the last fallback).
         self.sharded = self.peer = None
         self.exchange = "none"
         if self.shard_kv and world > 1:
             if cfg.get("exchange", "peer") == "peer":
-                try:
-                    from runntime_b200.engine import PeerExchangeDecode
-                    self.peer = PeerExchangeDecode(units=nb * cfg["qHeads"], headDim=hd, device=dev)
-                    self.exchange = "peer memory, in the decode kernel"
-                except Exception as e:  # noqa: BLE001 - any set-up failure means: use NCCL
-                    sys.stderr.write(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL\n")
+                from runntime_b200.engine import PeerExchangeDecode
+                import torch.distributed as dist
+                for transport in ("ipc", "symm"):
+                    try:
+                        peer = PeerExchangeDecode(batch=nb, qHeads=cfg["qHeads"], headDim=hd,
+                                                  device=dev, transport=transport)
+                    except Exception as e:  # noqa: BLE001 - any set-up failure: next transport
+                        sys.stderr.write(f"rank {rank}: peer exchange over {transport} unavailable "
+                                         f"({type(e).__name__}: {e})\n")
+                        peer = None
+                    agreed = torch.tensor([1 if peer is not None else 0], device=dev)
+                    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)     # all ranks or none
+                    if int(agreed.item()):
+                        self.peer = peer
+                        self.exchange = ("peer memory (CUDA IPC), rows sent by the decode kernel to "
+                                         "the rank that merges the sequence" if transport == "ipc" else
+                                         "peer memory (torch symmetric memory), rows sent by the decode "
+                                         "kernel to the rank that merges the sequence")
+                        break
             if self.peer is None:
                 self.sharded = ShardedDecode()
                 self.exchange = "one NCCL all-gather"
@@ -255,8 +312,7 @@ class Decode:
         total = 0
         for L in lens:
             total += 2 * L * w * es + qo
-            if not self.shard_kv:
-                total += 2 * w * es          # appended K/V row write
+            total += 2 * w * es          # appended K/V row write
             if c["cross"]:
                 total += 2 * c["cross"] * w * es + qo
         if self.shard_kv and not all_ranks:
@@ -272,22 +328,80 @@ class Decode:
         c = self.cfg
         if self.b == 0:
             return
+        self.ex.setStream(self.torch.cuda.current_stream().cuda_stream)   # also inside a graph capture
         common = dict(dtype="f16", batch=self.b, qHeads=c["qHeads"], kvHeads=c["kvHeads"],
                       headDim=c["hd"])
         if self.peer:
-            self.peer.step(self.ex, self.q, self.k, self.v, self.out, shardRows=self.rows, **common)
+            self.peer.step(self.ex, self.q, self.k, self.v, self.out, shardRows=self.rows,
+                           kvLens=self.lens, kvLen=c["cacheRows"], kNew=self.kNew, vNew=self.vNew,
+                           shardStart=self.shardStart, **common)
             return
         if self.sharded:
             self.sharded.step(self.ex, self.q, self.k, self.v, self.out, shardRows=self.rows,
-                              partials=self.partials, **common)
+                              partials=self.partials, kvLens=self.lens, kvLen=c["cacheRows"],
+                              kNew=self.kNew, vNew=self.vNew, shardStart=self.shardStart, **common)
             return
         decode_batched(self.ex, self.q, self.out, self.k, self.v, cacheRows=self.rows,
-                       kvLen=max(self.lens_all) if self.lens is not None else self.rows,
-                       kvLens=self.lens, kNew=self.kNew, vNew=self.vNew,
+                       kvLen=max(self.lens_all), kvLens=self.lens, kNew=self.kNew, vNew=self.vNew,
                        splits=int(os.environ.get("RT_BENCH_SPLITS", "0")), **common)
         if c["cross"]:
             decode_batched(self.ex, self.q, self.out2, self.ck, self.cv, cacheRows=c["cross"],
                            kvLen=c["cross"], **common)
+
+    def verify(self):
+        """One step, then a few sequences against the f64 oracle over their whole caches
+        (gathered from the ranks when the KV rows are sharded; the appended row included).
+        Each rank checks sequences whose output it holds.  Returns (worst absolute error,
+        sequences checked, all within tolerance) over this rank."""
+        import numpy as np
+        import oracle
+        t, c = self.torch, self.cfg
+        if self.b == 0:
+            return 0.0, 0, True
+        self.out.fill_(7.0)
+        self.step()
+        t.cuda.synchronize()
+        H, hd = c["qHeads"], c["hd"]
+        tol = oracle.TOLERANCE["f16"]
+        sample = sorted({0, self.b // 2, self.b - 1})
+        if self.shard_kv and self.world > 1:
+            import torch.distributed as dist
+            idx = t.tensor(sample, device=self.dev)
+            parts_k = [t.empty(len(sample), self.rows, self.k.shape[2], dtype=self.k.dtype, device=self.dev)
+                       for _ in range(self.world)]
+            parts_v = [t.empty_like(parts_k[0]) for _ in range(self.world)]
+            dist.all_gather(parts_k, self.k[idx].contiguous())
+            dist.all_gather(parts_v, self.v[idx].contiguous())
+            kk = t.cat(parts_k, dim=1)[:, :c["cacheRows"]]
+            vv = t.cat(parts_v, dim=1)[:, :c["cacheRows"]]
+        else:
+            kk, vv = self.k[sample], self.v[sample]
+        if self.peer:
+            mine = range(self.peer.first, self.peer.first + self.peer.owned)
+        else:
+            mine = range(self.b)
+        worst, n, ok = 0.0, 0, True
+        for i, b in enumerate(sample):
+            L = int(self.lens_all[self.b0 + b]) if not self.shard_kv else c["cacheRows"]
+            kb, vb = kk[i, :L].float().cpu().numpy(), vv[i, :L].float().cpu().numpy()
+            # the step appended this sequence's new row at position L-1
+            ok &= bool(np.array_equal(kb[L - 1], self.kNew[b].float().cpu().numpy()))
+            if b not in mine:
+                continue
+            want = oracle.sdpa_ref(self.q[b:b + 1].float().cpu().numpy(), kb, vb, qHeads=H,
+                                   kvHeads=c["kvHeads"], headDim=hd).reshape(-1)
+            err = np.abs(self.out[b].float().cpu().numpy() - want)
+            worst = max(worst, float(err.max()))
+            ok &= bool(np.all(err <= tol["atol"] + tol["rtol"] * np.abs(want)))
+            n += 1
+            if c["cross"]:
+                want = oracle.sdpa_ref(self.q[b:b + 1].float().cpu().numpy(),
+                                       self.ck[b].float().cpu().numpy(), self.cv[b].float().cpu().numpy(),
+                                       qHeads=H, kvHeads=c["kvHeads"], headDim=hd).reshape(-1)
+                err = np.abs(self.out2[b].float().cpu().numpy() - want)
+                worst = max(worst, float(err.max()))
+                ok &= bool(np.all(err <= tol["atol"] + tol["rtol"] * np.abs(want)))
+        return worst, n, ok
 
     def io_bytes(self):
         n = self.q.numel() * 2
@@ -296,18 +410,16 @@ class Decode:
         return n, self.out.numel() * 2
 
     def make_host(self):
-        # A decode step's inputs are the new token's q (and K/V row); the cache is
+        # A decode step's inputs are the new token's q and K/V row; the cache is
         # device-resident state, as it is in the reference's decoder loop.
         self.hq = self.q.cpu().pin_memory()
         self.hout = self.torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
-        if self.kNew is not None:
-            self.hkn, self.hvn = self.kNew.cpu().pin_memory(), self.vNew.cpu().pin_memory()
+        self.hkn, self.hvn = self.kNew.cpu().pin_memory(), self.vNew.cpu().pin_memory()
 
     def e2e_step(self, layer=0):
         self.q.copy_(self.hq, non_blocking=True)
-        if self.kNew is not None:
-            self.kNew.copy_(self.hkn, non_blocking=True)
-            self.vNew.copy_(self.hvn, non_blocking=True)
+        self.kNew.copy_(self.hkn, non_blocking=True)
+        self.vNew.copy_(self.hvn, non_blocking=True)
         self.step(layer)
         self.hout.copy_(self.out, non_blocking=True)
 
@@ -436,6 +548,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun starts its workers with OMP_NUM_THREADS=1: the CPU arm uses every host core
+    # at every N, so that its number is the same beside each of the GPU arm's.
+    import oracle
+    oracle.set_num_threads(os.cpu_count() or 1)
     key = args.workload
     cfg = CONFIGS[key]
     vals, mss = [], []
@@ -470,26 +586,56 @@ def metric_name(cfg):
 # GPU arm
 # ----------------------------------------------------------------------------
 
-def timed(torch, dist, world, fn, steps, warmup, flush=None):
-    """W warm-ups, then K timed steps bracketed by barrier + sync; returns the
-    max over ranks of the device time in ms (CUDA events on the launch stream)."""
-    for i in range(warmup):
-        fn(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    total = 0.0
-    if flush is None:
+def timed(torch, dist, world, fn, steps, warmup, flush=None, min_warm_s=0.0, min_timed_s=0.0):
+    """Warm-up, then the timed steps bracketed by barrier + sync; returns (max over ranks of
+    the device time in ms, timed steps, warm-up steps), timed with CUDA events on the launch
+    stream.  At least `warmup` warm-up steps and `steps` timed steps; with min_warm_s /
+    min_timed_s both are extended — by the same counts on every rank, from the slowest
+    rank's estimate of a step — so that the timed region is long enough to be measured at
+    the clocks a sustained load settles at (a region of a few milliseconds sees boost
+    clocks that a one-second region does not: the two cannot be compared).  With `flush`
+    every step is timed on its own, with the L2 flushed before it."""
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(n, first=0):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(steps):
-            fn(i)
+        for i in range(n):
+            fn(first + i)
         e1.record()
         torch.cuda.synchronize()
-        total = e0.elapsed_time(e1)
+        return e0.elapsed_time(e1)
+
+    fn(0)                       # first call: lazy set-up (function attributes, tensor maps)
+    barrier()
+    est = run(max(warmup, 1), 1) / max(warmup, 1)      # ms per step, this rank
+    if world > 1:
+        t = torch.tensor([est], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        est = float(t.item())
+    est = max(est, 1e-3)
+    warm = max(warmup, 1)
+    extra = int(math.ceil(min_warm_s * 1e3 / est)) - warm
+    if extra > 0:
+        done = 0
+        while done < extra:                 # in slices, so the launch queue stays short
+            n = min(extra - done, 256)
+            run(n, warm + done)
+            done += n
+        warm += extra
+    total_steps = steps
+    if flush is None and min_timed_s > 0:
+        total_steps = max(steps, int(math.ceil(min_timed_s * 1e3 / est / steps)) * steps)
+    barrier()
+    total = 0.0
+    if flush is None:
+        total = run(total_steps)
     else:
-        for i in range(steps):
+        for i in range(total_steps):
             flush()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -502,7 +648,7 @@ def timed(torch, dist, world, fn, steps, warmup, flush=None):
         t = torch.tensor([total], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total = float(t.item())
-    return total
+    return total, total_steps, warm
 
 
 def run_gpu(args):
@@ -529,7 +675,20 @@ def run_gpu(args):
     peaks = load_peaks()
     traffic = load_traffic()
 
-    def measure(key, steps, warmup, with_e2e):
+    def verify(wl):
+        """Output check before anything is timed: a sample against the f64 oracle on every
+        rank; a miss anywhere ends the run with a non-zero exit code."""
+        worst, n, ok = wl.verify()
+        if world > 1:
+            t = torch.tensor([worst, -float(ok), float(n)], device="cuda", dtype=torch.float64)
+            mx = t.clone()
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            sm = t.clone()
+            dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+            worst, ok, n = float(mx[0].item()), mx[1].item() == -1.0, int(sm[2].item())
+        return {"max_abs_err": worst, "rows": n, "against": "f64 oracle, same inputs", "ok": bool(ok)}
+
+    def measure(key, steps, warmup, with_e2e, sized=True):
         cfg = dict(CONFIGS[key])
         cfg["exchange"] = args.exchange
         if args.batch and key == args.workload:
@@ -540,6 +699,14 @@ def run_gpu(args):
             cfg["name"] += f"_rows{args.rows}"
         wl = (Prefill if cfg["kind"] == "prefill" else Decode)(cfg, rank, world, ex)
         layers = cfg.get("layers", 1)
+        verified = None
+        if not args.no_verify:
+            verified = verify(wl)
+            if not verified["ok"]:
+                if rank == 0:
+                    sys.stderr.write(f"bench.py: {cfg['name']}: output differs from the oracle "
+                                     f"({json.dumps(verified)}); nothing was timed\n")
+                raise SystemExit(3)
         small = key in ("c1", "c2")
         # Flush by READING 256 MB: a written buffer leaves the L2 full of dirty lines and the
         # timed kernel then pays for their write-back (measured: +18 us on a 100 MB stream).
@@ -548,66 +715,84 @@ def run_gpu(args):
         sampler = ClockSampler(local) if (rank == 0 and not args.no_clocks) else None
         step_fn = lambda i: wl.step(i % layers)
         graphed = False
+        n1 = ex.launchCount()
+        for i in range(3):
+            wl.step(i % layers)
+        per_step = (ex.launchCount() - n1) / 3.0          # kernels of this library per step
+        torch.cuda.synchronize()
         if cfg["kind"] == "decode" and not args.no_graph:
-            # A decode step is a few short launches (kernel, all-gather, merge): capture
-            # it once in a CUDA graph so that the device is not left waiting for the host.
-            n1 = ex.launchCount()
-            for i in range(3):
-                wl.step(0)
-            per_step = (ex.launchCount() - n1) // 3
-            torch.cuda.synchronize()
+            # A decode step is a few short launches (kernel, merge): capture it once in a
+            # CUDA graph so that the device is not left waiting for the host.
             graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
             with torch.cuda.graph(graph, stream=side):
-                ex.setStream(torch.cuda.current_stream().cuda_stream)
                 wl.step(0)
             ex.setStream(torch.cuda.current_stream().cuda_stream)
             step_fn = lambda i: graph.replay()
             graphed = True
-        n0 = ex.launchCount()
         if sampler:
             sampler.start()
-        ms = timed(torch, dist, world, step_fn, steps, warmup, flush)
+        # Time-sized: at least 1.5 s of warm-up and a timed region of at least 1 s (whole
+        # multiples of --steps), so that every N is measured at sustained clocks.
+        ms, timed_steps, warm_steps = timed(torch, dist, world, step_fn, steps, warmup, flush,
+                                            min_warm_s=1.5 if (sized and not args.short) else 0.0,
+                                            min_timed_s=1.0 if (sized and not args.short) else 0.0)
         clocks = sampler.stop() if sampler else None
         ex.sync()
-        launches = (per_step * steps) if graphed else \
-            (ex.launchCount() - n0) * steps // (steps + warmup)
-        if world == 1 and clocks is not None and (clocks.get("samples") or 0) < 3:
+        launches = int(round(per_step * timed_steps))
+        resample = clocks is not None and (clocks.get("samples") or 0) < 3
+        if world > 1:      # rank 0 holds the sampler; every rank must take the same path
+            flag = torch.tensor([1 if resample else 0], device="cuda")
+            dist.broadcast(flag, 0)
+            resample = bool(flag.item())
+        if resample:
             # The timed region was shorter than the sampler's period: repeat the same
-            # steps untimed for about 1.5 s with the sampler on and report that.
-            sampler = ClockSampler(local)
-            sampler.start()
-            t_end = time.perf_counter() + 1.5
-            i = 0
-            while time.perf_counter() < t_end:
+            # steps untimed for about 1.5 s with the sampler on and report that.  Every
+            # rank runs the same number of steps (the ranks of a sharded decode wait for
+            # one another), counted from the measured step time.
+            sampler = ClockSampler(local) if rank == 0 else None
+            if sampler:
+                sampler.start()
+            n_rep = max(8, int(1500.0 / max(ms / timed_steps, 1e-3)))
+            n_rep = min(n_rep, 200000)
+            for i in range(n_rep):
                 step_fn(i)
-                i += 1
-                if i % 8 == 0:
+                if i % 64 == 63:
                     torch.cuda.synchronize()
             torch.cuda.synchronize()
-            clocks = sampler.stop()
-            clocks["sampled"] = "1.5 s untimed repeat of the timed loop (timed region < sampler period)"
+            if sampler:
+                clocks = sampler.stop()
+                clocks["sampled"] = "1.5 s untimed repeat of the timed loop (timed region < sampler period)"
         ex.sync()
+        long_region = ms >= 900.0 and flush is None
         if cfg["kind"] == "prefill":
-            work = sum(wl.flops(i % layers) for i in range(steps))
+            work = sum(wl.flops(i % layers) for i in range(timed_steps))
             value, unit = work / (ms * 1e-3) / 1e12, "TFLOP/s"
-            peak, bound = peaks["tflops"], "tensor"
-            per_launch_local = sum(wl.flops(i % layers, all_ranks=False) for i in range(steps)) / steps
+            # burst figure for a kernel timed alone, sustained one for a second-long region
+            peak = peaks["tflops_sustained"] if (long_region and peaks.get("tflops_sustained")) else peaks["tflops"]
+            bound = "tensor"
+            per_launch_local = sum(wl.flops(i % layers, all_ranks=False) for i in range(timed_steps)) / timed_steps
         else:
-            work = wl.bytes() * steps
+            work = wl.bytes() * timed_steps
             value, unit = work / (ms * 1e-3) / 1e9, "GB/s"
             peak, bound = peaks["hbm_gbs"], "hbm"
             per_launch_local = wl.bytes(all_ranks=False)
         # roofline of the dominant kernel on this rank: its algorithmic work / its launch time
-        achieved = per_launch_local / (ms / steps * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+        achieved = per_launch_local / (ms / timed_steps * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+        roof = {"bound": bound, "achieved": achieved, "peak": peak,
+                "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
+                "frac": achieved / peak, "traffic": traffic.get(key),
+                "peak_source": peaks["source"] + (
+                    "" if bound != "tensor" else
+                    " (sustained: the timed region is a second of back-to-back launches)"
+                    if peak != peaks["tflops"] else " (burst)")}
+        if bound == "tensor":
+            roof["frac_of_burst"] = achieved / peaks["tflops"]
         res = {
             "exchange": getattr(wl, "exchange", None),
-            "metric": metric_name(cfg), "value": value, "unit": unit, "ms_per_step": ms / steps,
-            "dtype": cfg["dtype"], "workload": cfg["name"],
-            "roofline": {"bound": bound, "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
-                         "frac": achieved / peak, "traffic": traffic.get(key),
-                         "peak_source": peaks["source"] + (" (burst)" if bound == "tensor" else "")},
-            "clocks": clocks, "gpu_launches": launches,
+            "metric": metric_name(cfg), "value": value, "unit": unit, "ms_per_step": ms / timed_steps,
+            "dtype": cfg["dtype"], "workload": cfg["name"], "timed_steps": timed_steps,
+            "warmup_steps": warm_steps, "roofline": roof,
+            "clocks": clocks, "gpu_launches": launches, "verified": verified,
             "l2": "256 MB read between timed steps" if small else "inputs larger than L2",
             "launch": "CUDA graph replay of one step" if graphed else "direct launches",
         }
@@ -615,7 +800,7 @@ def run_gpu(args):
             wl.make_host()
             h2d, d2h = wl.io_bytes()
             e_steps = max(2, min(steps, 3)) if not small else steps
-            ems = timed(torch, dist, world, lambda i: wl.e2e_step(i % layers), e_steps, 1)
+            ems, e_steps, _ = timed(torch, dist, world, lambda i: wl.e2e_step(i % layers), e_steps, 1)
             if cfg["kind"] == "prefill":
                 ework = sum(wl.flops(i % layers) for i in range(e_steps))
                 evalue = ework / (ems * 1e-3) / 1e12
@@ -631,9 +816,14 @@ def run_gpu(args):
     cfg = CONFIGS[key]
     main = measure(key, args.steps, args.warmup, True)
     cfg = dict(cfg, name=main["workload"])
-    extra = None
+    riders = {}
     if key == "c5" and not args.no_decode:
-        extra = measure("c4", max(args.steps, 5), max(args.warmup, 3), True)
+        riders["decode"] = measure("c4", max(args.steps, 5), max(args.warmup, 3), True)
+    if key == "c5" and not args.no_riders:
+        # the other three configurations: milliseconds each, so every configuration the
+        # headline table names is in the one line the driver records
+        for rk in ("c3", "c1", "c2"):
+            riders[rk] = measure(rk, max(args.steps, 5), max(args.warmup, 3), rk == "c3", sized=(rk == "c3"))
 
     if rank == 0:
         line = {
@@ -641,7 +831,10 @@ def run_gpu(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": main["dtype"], "data": "synthetic",
+            "timed_steps": main["timed_steps"], "warmup_steps": main["warmup_steps"],
             "config": {"workload": cfg["name"], "l2": main["l2"], "launch": main["launch"],
+                       "timing": "the timed region is --steps repeated to at least 1 s after at "
+                                 "least 1.5 s of warm-up (timed_steps, warmup_steps)",
                        "parallelism": ("sequences sharded over ranks, no collective"
                                        if cfg["kind"] == "prefill" else
                                        "KV rows sharded over ranks, partials exchanged by "
@@ -649,17 +842,18 @@ def run_gpu(args):
                                        if cfg.get("lens") is None else "sequences sharded over ranks")},
             "roofline": main["roofline"], "clocks": main["clocks"],
             "e2e": main.get("e2e"), "gpu_launches": main["gpu_launches"],
+            "verified": main["verified"],
         }
         if world == 1 and not args.no_cpu:
             v, cores, desc, _ = cpu_sample(key)
             line["cpu_baseline"] = {"value": v, "unit": main["unit"], "cores": cores,
                                     "kind": "port", "sample": desc}
-        if extra:
-            line["decode"] = {k: extra.get(k) for k in ("metric", "value", "unit", "ms_per_step",
-                                                        "workload", "roofline", "e2e",
-                                                        "gpu_launches", "clocks", "launch",
-                                                        "exchange")}
-            if world == 1 and not args.no_cpu:
+        for name, extra in riders.items():
+            line[name] = {k: extra.get(k) for k in ("metric", "value", "unit", "ms_per_step",
+                                                    "workload", "roofline", "e2e", "timed_steps",
+                                                    "gpu_launches", "clocks", "launch", "l2",
+                                                    "exchange", "verified")}
+            if name == "decode" and world == 1 and not args.no_cpu:
                 v, cores, desc, _ = cpu_sample("c4", budget_s=6.0)
                 line["decode"]["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores,
                                                   "kind": "port", "sample": desc}
@@ -876,9 +1070,9 @@ def run_aux(args):
     sampler = ClockSampler(0) if not args.no_clocks else None
     if sampler:
         sampler.start()
-    ms = timed(torch, None, 1, step, args.steps, args.warmup, (lambda: flushbuf.sum()) if small else None)
+    ms, _, _ = timed(torch, None, 1, step, args.steps, args.warmup, (lambda: flushbuf.sum()) if small else None)
     clocks = sampler.stop() if sampler else None
-    launches = (ex.launchCount() - n0) * args.steps // (args.steps + args.warmup)
+    launches = (ex.launchCount() - n0) * args.steps // (args.steps + max(args.warmup, 1) + 1)
     tensor = unit == "TFLOP/s"
     scale = 1e12 if tensor else 1e9
     value = work * args.steps / (ms * 1e-3) / scale
@@ -904,8 +1098,7 @@ def run_aux(args):
                 d.copy_(h, non_blocking=True)
             step(i)
             hout.copy_(host_out, non_blocking=True)
-        ems = timed(torch, None, 1, e2e, max(2, min(args.steps, 3)), 1)
-        esteps = max(2, min(args.steps, 3))
+        ems, esteps, _ = timed(torch, None, 1, e2e, max(2, min(args.steps, 3)), 1)
         line["e2e"] = {"value": work * esteps / (ems * 1e-3) / scale, "unit": unit,
                        "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
                        "d2h_bytes_per_step": host_out.numel() * host_out.element_size(),
@@ -931,6 +1124,10 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(CONFIGS) + sorted(AUX))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode rider of c5")
+    ap.add_argument("--no-riders", action="store_true", help="skip the c1/c2/c3 riders of c5")
+    ap.add_argument("--no-verify", action="store_true", help="skip the oracle check before timing")
+    ap.add_argument("--short", action="store_true",
+                    help="time exactly --steps after --warmup (small cases for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi clocks")

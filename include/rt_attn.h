@@ -66,11 +66,16 @@ RT_API int rt_ctx_destroy(rt_ctx* ctx);
  * restores the context's stream. */
 RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
 /* Context options.  RT_OPT_PREFILL_TC (default 1): route eligible f16 prefill
- * shapes to a tensor-core kernel, the library choosing between its two (one or
- * two 128-row query tiles per thread block); 0 sends every prefill to the
- * FP32-pipe kernel, 2 forces one tile, 3 forces two tiles where that kernel
- * applies (all compute the same op; the switch exists for testing). */
+ * shapes to a tensor-core kernel, the library choosing among its three (one or
+ * two 128-row query tiles per thread block, or one tile whose key tiles alternate
+ * between two softmax warpgroups); 0 sends every prefill to the FP32-pipe kernel,
+ * 2 forces one tile, 3 forces two tiles, 4 forces the alternating form, each where
+ * that kernel applies (all compute the same op; the switch exists for testing). */
 #define RT_OPT_PREFILL_TC 1
+/* RT_OPT_WAIT_POLLS (default 1 << 20, about a second): how often the merge of a
+ * cross-GPU decode step polls for the other ranks' rows before it gives up, writes
+ * zeros and makes rt_sync return RT_EXECUTION_FAILED. */
+#define RT_OPT_WAIT_POLLS 2
 RT_API int rt_ctx_set_option(rt_ctx* ctx, int option, int value);
 /* Message of the last failure on this context (or, with ctx == NULL, of the
  * last failed call on this thread that had no context to record it in). */
@@ -183,24 +188,40 @@ RT_API int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** rou
  * rt_attn_merge_partials (KV-sequence sharding across GPUs); keyOffset is
  * not needed because the softmax algebra is position-free. */
 /* Exchange of the partials between the GPUs that hold the KV rows of the same
- * sequences (one process per GPU; every pointer below is an address in THIS
- * process: a peer's buffer mapped here, for example through CUDA IPC or
- * torch's symmetric memory).  With it rt_attn_decode writes this rank's
- * (m, l, acc) rows straight into every peer's buffer from the decode kernel,
- * signals them (a one-thread kernel), and runs a merge kernel that waits
- * (bounded, about a second) for all peers' rows of the same step before it merges: the decode step, the
- * all-gather and the merge of packages/runntime/src/core/kernels/attention/
- * attnDecode.ts:388-424 lifted across devices, without a library collective.
- * Every rank must make the same sequence of calls.  Buffers alternate between
- * two halves by step parity, so a rank one step ahead never overwrites rows a
- * slower peer is still merging.  All words start at zero. */
+ * sequences (KV-sequence sharding: rank r's caches hold rows [r*cacheRows,
+ * (r+1)*cacheRows) of every sequence).  Every pointer below is an address in
+ * THIS process: a peer's block mapped here (rt_xmem_* below does that; any other
+ * peer mapping works too).  With it rt_attn_decode
+ *   1. attends to this rank's rows and sends the (m, l, acc) rows of each
+ *      sequence, from the decode kernel, with plain stores, to the ONE rank that
+ *      merges that sequence: the ranks own contiguous blocks of sequences,
+ *      balanced to within one (the first batch % world ranks own one more; batch
+ *      must be at least world).  The last thread block to finish an owner's
+ *      sequences publishes this rank's step in that owner's arrival word;
+ *   2. runs a merge kernel over this rank's own sequences that first waits
+ *      (bounded, about a second; RT_OPT_WAIT_POLLS) until every rank's arrival word
+ *      has reached the step: the decode step, the all-gather and the merge of
+ *      packages/runntime/src/core/kernels/attention/attnDecode.ts:388-424 lifted
+ *      across devices, without a library collective and without a second signal
+ *      launch.
+ * `out` therefore receives the rows of this rank's own sequences only; the rest
+ * of `out` is left alone: the
+ * output stays sharded by sequence, which is how the layers after attention want
+ * it.  Every rank must make the same sequence of calls.  Buffers alternate
+ * between two halves by step parity, so a rank one step ahead never overwrites
+ * rows a slower peer is still merging.  All words start at zero.  After a wait
+ * has run out (rt_sync: RT_EXECUTION_FAILED) the counters are no longer
+ * consistent: make a new exchange. */
 #define RT_MAX_PEERS 8
 typedef struct {
   int32_t world;                   /* ranks sharing the sequences, 1..RT_MAX_PEERS */
   int32_t rank;                    /* this rank */
-  float* partials[RT_MAX_PEERS];   /* rank r's buffer: f32 [2][world][batch*qHeads][2+headDim] */
+  float* partials[RT_MAX_PEERS];   /* rank r's buffer: f32 [2][world][per*qHeads][2+headDim],
+                                      per = ceil(batch / world) */
   uint32_t* flags[RT_MAX_PEERS];   /* rank r's arrival words: [world] */
-  uint32_t* step;                  /* this rank's step counter (one word) */
+  uint32_t* step;                  /* this rank's counters: [world + 3] words (step, spare,
+                                      thread blocks arrived per owner, owners done) */
+  float* stage;                    /* this rank's staging rows: f32 [batch*qHeads][2+headDim] */
   int32_t phases;                  /* 0 or 3: the whole step; 1: attend and send only; 2: wait and
                                       merge only (for callers that put other work in between) */
 } rt_exchange;
@@ -232,6 +253,14 @@ typedef struct {
   int64_t kNewRowStride;  /* elements between kNew rows; 0 = kvHeads*headDim */
   int64_t vNewRowStride;  /* elements between vNew rows; 0 = kvHeads*headDim */
   const rt_exchange* exchange; /* host pointer or NULL: merge with the other ranks' rows into out */
+  /* KV-sequence sharding with append (0 / 0 for a cache that holds whole sequences):
+   * with kvSharded = 1 each cache holds rows [shardStart, shardStart + cacheRows) of its
+   * sequence, and kvLen / kvLens are the sequences' GLOBAL lengths.  The kernel attends
+   * to the rows of [0, L_b) that fall inside the shard and appends kNew/vNew (global
+   * row L_b-1) only on the rank whose shard contains that row; every rank passes the
+   * same q, kNew, vNew and lengths.  ropeByPosition uses the global position. */
+  int32_t kvSharded;
+  int32_t shardStart;
 } rt_decode_args;
 
 RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);
@@ -259,9 +288,38 @@ RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);
  * contents (the counters are cleared on the stream before each launch): two
  * calls whose kernels may overlap on the GPU — different streams, or the same
  * call from two threads — race on it, so serialise them.  Errors are reported
- * through the return code and rt_last_error(NULL); a device-side wait that
- * runs out is recorded in the array's status word only. */
+ * through the return code and rt_last_error(NULL); what a kernel finds wrong
+ * while it runs (a bounded wait that ran out, a kvLens entry past cacheRows) is
+ * recorded in the array's status word, which rt_attn_decode_noalloc_status
+ * reads. */
 RT_API int rt_attn_decode_noalloc(const rt_decode_args* args, void* cuda_stream);
+
+/* What rt_sync is to rt_attn_decode, for the entry point above (it has no
+ * counterpart in the reference either): waits for `cuda_stream`, reads the
+ * status word of the current device's fixed array and, if a kernel recorded a
+ * failure there, clears the word and returns RT_EXECUTION_FAILED with the
+ * reason in rt_last_error(NULL).  Allocates nothing. */
+RT_API int rt_attn_decode_noalloc_status(void* cuda_stream);
+
+/* ---- set-up of the exchange without a launcher or a collective library --------
+ * Allocates this rank's block (exchange buffer, control words, staging rows; all
+ * zero) on `device` and maps the other ranks' blocks, so that a host with no
+ * torch.distributed / NCCL — the TypeScript host of this library — can run the
+ * KV-sequence-sharded decode.  One process per GPU: rt_xmem_export gives a
+ * RT_XMEM_HANDLE_BYTES handle (a CUDA IPC handle) to send to the other processes
+ * by any channel, rt_xmem_import maps a received one.  One process owning several
+ * devices: rt_xmem_attach takes the peer's rt_xmem directly (peer access between
+ * the two devices is enabled).  rt_xmem_exchange fills the rt_exchange once every
+ * rank is mapped.  No counterpart in the reference, which has no multi-device code. */
+typedef struct rt_xmem rt_xmem;
+#define RT_XMEM_HANDLE_BYTES 64
+RT_API int rt_xmem_create(int device, int32_t world, int32_t rank, int32_t batch, int32_t qHeads,
+                          int32_t headDim, rt_xmem** out);
+RT_API int rt_xmem_export(rt_xmem* m, void* handle);
+RT_API int rt_xmem_import(rt_xmem* m, int32_t peer, const void* handle);
+RT_API int rt_xmem_attach(rt_xmem* m, int32_t peer, rt_xmem* other);
+RT_API int rt_xmem_exchange(rt_xmem* m, rt_exchange* out);
+RT_API int rt_xmem_destroy(rt_xmem* m);
 
 /* Merges `parts` sets of partials (m, l, acc) — the algebra of attnDecodeMerge
  * (packages/runntime/src/core/kernels/attention/attnDecode.ts:405-422) lifted

@@ -271,6 +271,12 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Host threads for the parallel loops (a launcher such as torchrun sets
+    OMP_NUM_THREADS=1 for its workers; the CPU baseline wants all cores)."""
+    lib().oracle_set_num_threads(C.c_int(int(n)))
+
+
 # Tolerances of the reference's own comparison (checkSdpa.ts:127):
 # |got - want| <= atol + rtol * |want|.
 TOLERANCE = {"f32": dict(atol=2e-5, rtol=1e-4), "f16": dict(atol=2e-3, rtol=4e-3)}

@@ -345,3 +345,13 @@ int oracle_num_threads(void) {
 #endif
   return n;
 }
+
+/* Number of host threads the parallel loops use from now on (a launcher may have set
+ * OMP_NUM_THREADS=1 for its worker processes before this library was loaded). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}

@@ -16,6 +16,8 @@ LIB_PATH = os.path.join(_HERE, "librt_attn.so")
 RT_F32, RT_F16 = 0, 1
 WINDOW_INF = 0x3FFFFFFF
 OPT_PREFILL_TC = 1
+OPT_WAIT_POLLS = 2
+XMEM_HANDLE_BYTES = 64
 DTYPE_CODE = {"f32": RT_F32, "f16": RT_F16}
 
 
@@ -42,7 +44,7 @@ class Exchange(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32),
         ("partials", C.c_void_p * MAX_PEERS), ("flags", C.c_void_p * MAX_PEERS),
-        ("step", C.c_void_p), ("phases", C.c_int32),
+        ("step", C.c_void_p), ("stage", C.c_void_p), ("phases", C.c_int32),
     ]
 
 
@@ -58,6 +60,7 @@ class DecodeArgs(C.Structure):
         ("ropeByPosition", C.c_int32), ("ropeCos", C.c_void_p), ("ropeSin", C.c_void_p),
         ("qRowStride", C.c_int64), ("kNewRowStride", C.c_int64), ("vNewRowStride", C.c_int64),
         ("exchange", C.POINTER(Exchange)),
+        ("kvSharded", C.c_int32), ("shardStart", C.c_int32),
     ]
 
 
@@ -78,6 +81,14 @@ SYMBOLS = {
     "rt_attn_route": (C.c_int, [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(C.c_char_p)]),
     "rt_attn_decode": (C.c_int, [C.c_void_p, C.POINTER(DecodeArgs)]),
     "rt_attn_decode_noalloc": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "rt_attn_decode_noalloc_status": (C.c_int, [C.c_void_p]),
+    "rt_xmem_create": (C.c_int, [C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                 C.POINTER(C.c_void_p)]),
+    "rt_xmem_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "rt_xmem_import": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "rt_xmem_attach": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "rt_xmem_exchange": (C.c_int, [C.c_void_p, C.POINTER(Exchange)]),
+    "rt_xmem_destroy": (C.c_int, [C.c_void_p]),
     "rt_attn_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                          C.c_void_p, C.c_int32]),
     "rt_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,

@@ -22,6 +22,7 @@ struct rt_ctx {
   int* statusDev;
   int64_t launches;
   int useTc;
+  int waitPolls;   // polls of the cross-GPU merge's wait before it gives up
   std::string err;
 };
 
@@ -272,6 +273,7 @@ int rt_ctx_create(int device, rt_ctx** out) {
   ctx->counterCount = 0;
   ctx->launches = 0;
   ctx->useTc = 1;
+  ctx->waitPolls = 1 << 20;   // about a second with the kernel's sleeps
   if ((e = cudaSetDevice(device)) != cudaSuccess ||
       (e = cudaStreamCreateWithFlags(&ctx->own, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaMalloc(&ctx->statusDev, sizeof(int))) != cudaSuccess ||
@@ -309,10 +311,17 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
 int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
   RT_ENTER(ctx);
   if (option == RT_OPT_PREFILL_TC) {
-    if (value < 0 || value > 3)
-      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..3, got %d",
+    if (value < 0 || value > 4)
+      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..4, got %d",
                   value);
     ctx->useTc = value;
+    return RT_OK;
+  }
+  if (option == RT_OPT_WAIT_POLLS) {
+    if (value < 1)
+      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_WAIT_POLLS takes a positive count, got %d",
+                  value);
+    ctx->waitPolls = value;
     return RT_OK;
   }
   return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: unknown option %d", option);
@@ -330,10 +339,14 @@ int rt_sync(rt_ctx* ctx) {
   RT_CUDA(ctx, cudaMemcpy(&status, ctx->statusDev, sizeof(int), cudaMemcpyDeviceToHost));
   if (status != 0) {
     cudaMemset(ctx->statusDev, 0, sizeof(int));
+    // A block that gave up never counted itself in: the arrival counters of the split
+    // merge are no longer zero, and the next split launch would pick the wrong last block.
+    if (ctx->counters) cudaMemset(ctx->counters, 0, ctx->counterCount * sizeof(unsigned));
     return fail(ctx, RT_EXECUTION_FAILED,
                 "a kernel reported status 0x%x (%s)", status,
-                (status & rt::kStatusWaitTimeout) ? "a bounded device-side wait ran out"
-                                                  : "inconsistent kernel state");
+                (status & rt::kStatusWaitTimeout)
+                    ? "a bounded device-side wait ran out"
+                    : "a device-side length exceeds its buffer (kvLens entry past cacheRows)");
   }
   return RT_OK;
 }
@@ -375,9 +388,13 @@ int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* ho
   return rt_sync(ctx);
 }
 
-// 0 = FP32-pipe kernel, 1 = tensor cores, one query tile per CTA, 2 = two tiles per CTA.
+// 0 = FP32-pipe kernel, 1 = tensor cores, one query tile per CTA, 2 = two tiles per CTA,
+// 3 = one tile with two softmax warpgroups on alternate key tiles.
 static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dtype) {
-  if (!ctx->useTc || !rt::prefill_tc_supported(p, dtype)) return 0;
+  if (!ctx->useTc) return 0;
+  const bool tc3 = rt::prefill_tc3_supported(p, dtype);
+  if (ctx->useTc == 4 && tc3) return 3;
+  if (!rt::prefill_tc_supported(p, dtype)) return tc3 ? 3 : 0;   // heads narrower than 64
   if (ctx->useTc != 2 && rt::prefill_tc2_supported(p, dtype)) {
     const int64_t blocks = (p.qLen + 255) / 256 * p.qHeads;
     if (ctx->useTc == 3 || blocks >= kTwoTileBlocksPerSm * ctx->smCount) return 2;
@@ -388,7 +405,7 @@ static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dty
 static const char* route_of(const rt_ctx* ctx, const rt_attn_args* a) {
   if (a->qLen == 1) return "decode";
   const int k = prefill_kernel_of(ctx, to_params(a), a->dtype);
-  return k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
+  return k == 3 ? "prefill_tc3" : k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
 }
 
 int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
@@ -429,9 +446,9 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
   const int kernel = prefill_kernel_of(ctx, p, a->dtype);
   if (kernel != 0) {
     std::string err;
-    cudaError_t e = kernel == 2
-                        ? rt::launch_prefill_tc2(p, ctx->statusDev, ctx->stream, &err)
-                        : rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
+    cudaError_t e = kernel == 3   ? rt::launch_prefill_tc3(p, ctx->statusDev, ctx->stream, &err)
+                    : kernel == 2 ? rt::launch_prefill_tc2(p, ctx->statusDev, ctx->stream, &err)
+                                  : rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
     if (e != cudaSuccess)
       return fail(ctx, RT_EXECUTION_FAILED, "prefill_tc launch: %s %s", cudaGetErrorString(e),
                   err.c_str());
@@ -464,7 +481,7 @@ int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
   if (a->headDim > 128)
     return fail(ctx, RT_INVALID_ARGUMENT, "sdpa: headDim %d exceeds the kernel's max (128)",
                 a->headDim);
-  if (a->kvLen < 0 || a->kvLen > a->cacheRows)
+  if (a->kvLen < 0 || (!a->kvSharded && a->kvLen > a->cacheRows))
     return fail(ctx, RT_INVALID_ARGUMENT,
                 "writeRows: rows [%d, %d) exceed dst capacity %d", a->kvLen - 1, a->kvLen,
                 a->cacheRows);
@@ -491,18 +508,16 @@ int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
   if (phases & 1) {
     const int s = run_decode(ctx, p, a->dtype);
     if (s != RT_OK) return s;
-    if (a->exchange) {
-      RT_CUDA(ctx, rt::launch_exchange_signal(a->exchange->step, a->exchange->flags,
-                                              a->exchange->world, a->exchange->rank, ctx->stream));
-      ctx->launches++;
-    }
   }
   if (!a->exchange || !(phases & 2)) return RT_OK;
   const rt_exchange& x = *a->exchange;
-  RT_CUDA(ctx, rt::launch_merge_exchanged(x.partials[x.rank], x.flags[x.rank], x.step, x.world,
-                                          (int64_t)a->batch * a->qHeads, a->headDim, a->out,
-                                          a->dtype, ctx->statusDev, ctx->stream));
-  ctx->launches++;
+  const int per = rt::exchange_per(a->batch, x.world);
+  const int first = rt::owner_first(x.rank, a->batch, x.world);
+  const int owned = rt::owner_count(x.rank, a->batch, x.world);
+  RT_CUDA(ctx, rt::launch_merge_exchanged(x.partials[x.rank], x.flags[x.rank], x.step, x.world, per,
+                                          owned, first, a->qHeads, a->headDim, a->out, a->dtype,
+                                          ctx->statusDev, ctx->waitPolls, ctx->stream));
+  if (owned > 0) ctx->launches++;
   return RT_OK;
 }
 

@@ -88,6 +88,7 @@ struct DecodeParams {
   int64_t lo, end;      // explicit key range (useRange), for the single-sequence op
   int32_t useRange;
   int32_t batch, kvLen, qHeads, kvHeads, hd, wl, splits;
+  int32_t cacheRows;    // capacity of each cache in rows: a device-side length past it is refused
   int32_t kvPerCta;     // kv heads handled by one CTA
   int32_t keySlots;     // keys processed concurrently by one CTA
   int32_t stages;       // smem ring depth (bulk path)
@@ -100,9 +101,37 @@ struct DecodeParams {
   // cross-GPU exchange of the final partials (xWorld = 0: off); see rt_exchange
   float* xPartials[RT_MAX_PEERS];
   uint32_t* xFlags[RT_MAX_PEERS];
-  uint32_t* xStep;
+  uint32_t* xStep;      // this rank's counter block: step, (unused), [world] arrivals per owner, owners done
+  float* xStage;        // this rank's final rows before they go to their owners: [batch, qHeads, 2+hd]
   int32_t xWorld, xRank;
+  int32_t xPer;         // sequences per owner: rank o merges sequences [o*xPer, (o+1)*xPer)
+  int32_t xRot;         // added to blockIdx.y: a rank's own sequences are attended last
+  // KV-sequence sharding with append: this cache holds global rows [shardStart,
+  // shardStart + cacheRows) of every sequence and kvLens are global lengths
+  int32_t kvSharded, shardStart;
 };
+
+// Who merges which sequences in the cross-GPU exchange: contiguous blocks balanced to within
+// one sequence (the first batch % world ranks own one more); every rank owns at least one,
+// which the API ensures by refusing batch < world (a rank with nothing to merge would have
+// nothing to wait for and could run steps ahead of the others).
+#ifdef __CUDACC__
+#define RT_HD __host__ __device__
+#else
+#define RT_HD
+#endif
+RT_HD inline int exchange_per(int batch, int world) { return (batch + world - 1) / world; }
+RT_HD inline int owner_first(int o, int batch, int world) {
+  const int base = batch / world, extra = batch % world;
+  return o * base + (o < extra ? o : extra);
+}
+RT_HD inline int owner_count(int o, int batch, int world) {
+  return batch / world + (o < batch % world ? 1 : 0);
+}
+RT_HD inline int owner_of(int b, int batch, int world) {
+  const int base = batch / world, extra = batch % world, cut = extra * (base + 1);
+  return b < cut ? b / (base + 1) : extra + (b - cut) / base;
+}
 
 // Copies the caller's decode arguments (already validated) into kernel parameters.
 inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
@@ -117,6 +146,7 @@ inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
   p.partialsOut = a.partialsOut;
   p.cacheSeqStride = a.cacheSeqStride;
   p.batch = a.batch;
+  p.cacheRows = a.cacheRows;
   p.kvLen = a.kvLens ? (a.kvLen > 0 ? a.kvLen : a.cacheRows) : a.kvLen;
   p.qHeads = a.qHeads;
   p.kvHeads = a.kvHeads;
@@ -138,8 +168,13 @@ inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
       p.xFlags[r] = r < a.exchange->world ? a.exchange->flags[r] : nullptr;
     }
     p.xStep = a.exchange->step;
+    p.xStage = a.exchange->stage;
+    p.xPer = exchange_per(a.batch, a.exchange->world);
+    p.xRot = owner_first((a.exchange->rank + 1) % a.exchange->world, a.batch, a.exchange->world);
     p.partialsOut = nullptr;
   }
+  p.kvSharded = a.kvSharded;
+  p.shardStart = a.shardStart;
 }
 
 // What is wrong with the rope / stride fields of decode arguments, or NULL.
@@ -156,11 +191,15 @@ inline const char* decode_rope_args_error(const rt_decode_args& a) {
     const rt_exchange& x = *a.exchange;
     if (x.world < 1 || x.world > RT_MAX_PEERS || x.rank < 0 || x.rank >= x.world)
       return "exchange: world must be 1..8 and rank inside it";
-    if (!x.step || !a.out) return "exchange: step and out must be given";
+    if (!x.step || !x.stage || !a.out) return "exchange: step, stage and out must be given";
+    if (a.batch < x.world) return "exchange: batch must be at least world (every rank merges a sequence)";
     if (x.phases < 0 || x.phases > 3) return "exchange: phases must be 0..3";
     for (int r = 0; r < x.world; r++)
       if (!x.partials[r] || !x.flags[r]) return "exchange: a peer buffer is NULL";
   }
+  if (a.kvSharded != 0 && a.kvSharded != 1) return "kvSharded must be 0 or 1";
+  if (a.shardStart < 0 || (!a.kvSharded && a.shardStart != 0))
+    return "shardStart must be non-negative, and zero unless kvSharded is set";
   return nullptr;
 }
 
@@ -224,19 +263,20 @@ cudaError_t launch_prefill_tc(const AttnParams& p, int dtype, int* status, cudaS
 // Two query tiles per CTA (head sizes 64 and 128, more than 128 query rows).
 bool prefill_tc2_supported(const AttnParams& p, int dtype);
 cudaError_t launch_prefill_tc2(const AttnParams& p, int* status, cudaStream_t s, std::string* err);
+// One query tile per CTA, two softmax warpgroups on alternate key tiles (head sizes 64, 128,
+// 256, and heads narrower than 64 padded inside the tile).
+bool prefill_tc3_supported(const AttnParams& p, int dtype);
+cudaError_t launch_prefill_tc3(const AttnParams& p, int* status, cudaStream_t s, std::string* err);
 // Fills kvPerCta/keySlots/stages/splits; returns false with a message when the shape cannot run.
 bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_merge_partials(const float* partials, int parts, int64_t units, int hd,
                                   void* out, int dtype, cudaStream_t s);
-// After a decode launch with the exchange: advances *step and publishes it in every rank's
-// arrival word for this rank.
-cudaError_t launch_exchange_signal(uint32_t* step, uint32_t* const* flags, int world, int rank,
-                                   cudaStream_t s);
-// Merge of the exchanged partials: waits for every rank's arrival word to reach *step.
+// Merge of the exchanged partials on the rank that owns sequences [firstSeq, firstSeq+owned):
+// waits (at most `limit` polls) for every rank's arrival word to reach *step.
 cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, const uint32_t* step,
-                                   int world, int64_t units, int hd, void* out, int dtype,
-                                   int* status, cudaStream_t s);
+                                   int world, int per, int owned, int firstSeq, int heads, int hd,
+                                   void* out, int dtype, int* status, int limit, cudaStream_t s);
 cudaError_t launch_rope(const void* x, const float* cosT, const float* sinT, void* out,
                         int64_t rows, int64_t srcCols, int hd, int64_t srcStart, int64_t width,
                         int dtype, cudaStream_t s);

@@ -250,25 +250,39 @@ __device__ __forceinline__ void process_key_pair(const T* ka, const T* va, const
 }
 
 // Cross-GPU hand-over, called by the consumer threads of the block that wrote the final
-// rows of (sequence b, head block zb) into this rank's slot: copies those rows into the
-// same slot of every peer's buffer (plain stores to peer memory).  The ranks are told by
-// the small kernel that follows this one in the stream: a kernel's stores, peer stores
-// included, are complete when it ends, so that kernel only has to publish the step —
-// fencing at system scope in every block here costs microseconds per wave of blocks.
-__device__ __forceinline__ void exchange_rows(const DecodeParams& p, float* mySlot, int b, int hq,
-                                              int h0, int tid) {
-  if (p.xWorld <= 1) return;
+// rows of (sequence b, head block) into this rank's staging buffer.  The rows go to the one
+// rank that merges sequence b (its owner): plain, coalesced stores into that rank's
+// exchange buffer — peer memory unless the owner is this rank.  The block then counts
+// itself in for that owner; the last block to do so fences at system scope and publishes
+// this rank's step in the owner's arrival word (one release store), so an owner is told as
+// soon as its rows are complete, while the other owners' sequences are still being
+// attended.  The last owner group to finish moves this rank's step counter for the merge
+// kernel and the next launch.
+__device__ __forceinline__ void exchange_rows(const DecodeParams& p, int b, int hq, int h0, int tid,
+                                              uint32_t epoch, int headBlocks) {
   const int stride = 2 + p.hd;
-  const int64_t first = ((int64_t)b * p.qHeads + h0) * stride;  // this block's rows: contiguous
+  const int owner = owner_of(b, p.batch, p.xWorld), bl = b - owner_first(owner, p.batch, p.xWorld);
+  const float* src = p.xStage + ((int64_t)b * p.qHeads + h0) * stride;  // this block's rows: contiguous
+  float* dst = p.xPartials[owner] +
+               ((((int64_t)(epoch & 1u) * p.xWorld + p.xRank) * p.xPer + bl) * p.qHeads + h0) * stride;
   const int n = hq * stride;
   __threadfence();                     // the rows written by this block's threads ...
   named_barrier_sync(1, kConsumers);   // ... are visible to all of them
-  const int64_t slotOffset = mySlot - p.xPartials[p.xRank];
-  for (int r = 0; r < p.xWorld; r++) {
-    if (r == p.xRank) continue;
-    float* dst = p.xPartials[r] + slotOffset + first;
-    for (int i = tid; i < n; i += kConsumers) dst[i] = __ldcg(mySlot + first + i);
-  }
+  for (int i = tid; i < n; i += kConsumers) dst[i] = __ldcg(src + i);
+  __threadfence();                     // each thread's stores, before the block is counted in
+  named_barrier_sync(1, kConsumers);
+  if (tid != 0) return;
+  unsigned* counts = p.xStep + 2;      // [world] blocks arrived per owner, then owners done
+  const int owned = owner_count(owner, p.batch, p.xWorld);
+  if (atomicAdd(counts + owner, 1u) != (unsigned)(owned * headBlocks) - 1u) return;
+  counts[owner] = 0;                   // ready for the next launch
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.xFlags[owner] + p.xRank), "r"(epoch)
+               : "memory");
+  if (atomicAdd(counts + p.xWorld, 1u) != (unsigned)p.xWorld - 1u) return;   // every rank owns some
+  counts[p.xWorld] = 0;
+  __threadfence();
+  *reinterpret_cast<volatile uint32_t*>(p.xStep) = epoch;
 }
 
 template <typename T, int HDP, bool EXACT, int VEC, bool BULK, int R = 1>
@@ -280,11 +294,17 @@ decode_kernel(const DecodeParams p) {
   constexpr int QS = q_stride(HDP);
   extern __shared__ __align__(128) unsigned char smemRaw[];
   __shared__ int sAbort;
+  __shared__ int sAbortSeen;
   __shared__ int sIsLast;
   __shared__ __align__(8) uint64_t sFull[kMaxStages], sEmpty[kMaxStages];
 
   const int tid = threadIdx.x;
-  const int split = blockIdx.x, b = blockIdx.y, zb = blockIdx.z;
+  const int split = blockIdx.x, zb = blockIdx.z;
+  int b = blockIdx.y;
+  if (p.xWorld > 1) {   // the sequences this rank merges itself come last
+    b += p.xRot;
+    if (b >= p.batch) b -= p.batch;
+  }
   const int hd = p.hd;
   const int group = p.qHeads / p.kvHeads;
   const int kvh0 = zb * p.kvPerCta;
@@ -295,27 +315,45 @@ decode_kernel(const DecodeParams p) {
   const int KS = p.keySlots;
   const int sliceElems = nkv * hd;
   const int rowElems = p.kvHeads * hd;
-  const bool hasNew = p.kNew != nullptr;
   // Where the final (m, l, acc) rows go, if not into `out`: the caller's buffer, or —
-  // with the cross-GPU exchange — this rank's slot of its own exchange buffer, in the
-  // half that belongs to the step now starting (the step counter is moved by the kernel
-  // that follows this one, so all blocks read the same value).
+  // with the cross-GPU exchange — this rank's staging buffer, from where exchange_rows
+  // sends them to the rank that merges the sequence.  The step now starting is one past
+  // the rank's step counter, which only the last block of this launch moves, so all
+  // blocks read the same value.
   float* partialsOut = p.partialsOut;
+  uint32_t epoch = 0;
   if (p.xWorld > 0) {
-    const uint32_t parity = (*reinterpret_cast<volatile uint32_t*>(p.xStep) + 1u) & 1u;
-    const int64_t slotFloats = (int64_t)p.batch * p.qHeads * (2 + p.hd);
-    partialsOut = p.xPartials[p.xRank] + ((int64_t)parity * p.xWorld + p.xRank) * slotFloats;
+    epoch = *reinterpret_cast<volatile uint32_t*>(p.xStep) + 1u;
+    partialsOut = p.xStage;
   }
 
   // Key range of this sequence that lives in the cache.
-  int64_t lo, end, L = 0;
+  // L: visible rows of this cache; Lg: the sequence's length (the two differ only when the
+  // cache is one rank's shard of the sequence).
+  int64_t lo, end, L = 0, Lg = 0;
+  bool hasNew = p.kNew != nullptr;
   if (p.useRange) {
     lo = p.lo;
     end = p.end;
   } else {
-    L = p.kvLens ? p.kvLens[b] : p.kvLen;
+    Lg = L = p.kvLens ? p.kvLens[b] : p.kvLen;
+    if (p.kvSharded) {
+      // This cache holds rows [shardStart, shardStart + cacheRows) of the sequence: it sees
+      // what falls inside, and takes the appended row (global row Lg-1) only if that is one
+      // of its own.
+      const int64_t local = Lg - p.shardStart;
+      hasNew = hasNew && local >= 1 && local <= p.cacheRows;
+      L = local < 0 ? 0 : local > p.cacheRows ? p.cacheRows : local;
+    } else if (L > p.cacheRows) {
+      // A length past the cache's capacity (the host checks only the scalar kvLen; this one
+      // lives on the device): writeRows would refuse it ('rows exceed dst capacity').  The
+      // sequence is treated as empty — nothing appended, nothing read, zeros out — and the
+      // status word reports it.
+      if (tid == 0) atomicOr(p.status, kStatusBadState);
+      Lg = L = 0;
+    }
     end = L - 1;
-    lo = L - 1 - p.wl;
+    lo = Lg - 1 - p.wl - p.shardStart;
     if (lo < 0) lo = 0;
     if (hasNew) end -= 1;  // row L-1 is the appended one, taken from kNew/vNew
     if (L <= 0) { lo = 1; end = -1; }
@@ -336,7 +374,7 @@ decode_kernel(const DecodeParams p) {
   // (threads that own a slice of a head keep q in registers and read the appended row back
   // from the cache: no staging areas)
   const int qBytes = R == 1 ? ((hqMax * QS * 4 + 127) / 128) * 128 : 0;
-  const int newBytes = (R == 1 && hasNew) ? ((p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128 : 0;
+  const int newBytes = (R == 1 && p.kNew != nullptr) ? ((p.kvPerCta * hd * (int)sizeof(T) + 127) / 128) * 128 : 0;
   T* sKn = reinterpret_cast<T*>(smemRaw + qBytes);           // appended K slice
   T* sVn = reinterpret_cast<T*>(smemRaw + qBytes + newBytes);  // appended V slice
   unsigned char* ring = smemRaw + qBytes + 2 * newBytes;
@@ -406,7 +444,7 @@ decode_kernel(const DecodeParams p) {
   const float* qv = sQ + hl * QS;
   const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qRowStride;
   const bool roped = p.ropeCos != nullptr && !p.useRange;
-  const int64_t ropeRow = p.ropeByPos ? (L >= 1 ? L - 1 : 0) : b;
+  const int64_t ropeRow = p.ropeByPos ? (Lg >= 1 ? Lg - 1 : 0) : b;
   const float* rc = roped ? p.ropeCos + ropeRow * hd : nullptr;
   const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
   {
@@ -570,7 +608,13 @@ decode_kernel(const DecodeParams p) {
     else process_key<T, HDP, EXACT, VEC, QSMEM>(sKn + off, sVn + off, qv, hd, m, l, acc, rot);
   }
 
-  if (!ok || sAbort) {
+  // Every consumer is through its tiles (or has given up): the ring is free.  Whether a wait
+  // ran out is decided once for the whole block — a thread that finished its tiles before
+  // another one's wait ran out must not go on to barriers the other will never reach.
+  named_barrier_sync(1, kConsumers);
+  if (tid == 0) sAbortSeen = sAbort;
+  named_barrier_sync(1, kConsumers);
+  if (sAbortSeen) {
     // A wait ran out: record it, let copies in flight land, leave.
     if (tid == 0) atomicOr(p.status, kStatusWaitTimeout);
     for (int i = 0; i < 64; i++) __nanosleep(4000);
@@ -578,7 +622,6 @@ decode_kernel(const DecodeParams p) {
   }
 
   // ---- merge the key slots of each head (log-sum-exp) ----
-  named_barrier_sync(1, kConsumers);  // every tile consumed: the ring is free
   float* sM = reinterpret_cast<float*>(ring);  // [KS][hqMax][2 + W]
   constexpr int MS = 2 + W;
   if (active) {
@@ -641,7 +684,7 @@ decode_kernel(const DecodeParams p) {
     }
   }
   if (p.splits == 1) {
-    if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hqReal, kvh0 * group, tid);
+    if (p.xWorld > 0) exchange_rows(p, b, hqReal, kvh0 * group, tid, epoch, gridDim.z);
     return;
   }
 
@@ -682,7 +725,7 @@ decode_kernel(const DecodeParams p) {
     }
   }
   if (tid == 0) p.counters[b * gridDim.z + zb] = 0;  // ready for the next launch
-  if (p.xWorld > 0) exchange_rows(p, partialsOut, b, hqReal, kvh0 * group, tid);
+  if (p.xWorld > 0) exchange_rows(p, b, hqReal, kvh0 * group, tid, epoch, gridDim.z);
 }
 
 size_t smem_bytes(const DecodeParams& p, int esize, int hdp, bool bulk) {
@@ -846,6 +889,10 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     const int zBlocks = (p.kvHeads + kvPerCta - 1) / kvPerCta;
     const int64_t ctas = (int64_t)p.batch * zBlocks;
     int64_t nmax = p.useRange ? (p.end >= p.lo ? p.end - p.lo + 1 : 0) : p.kvLen;
+    if (p.kvSharded) {   // the longest stretch of a sequence this shard can hold
+      nmax -= p.shardStart;
+      nmax = nmax < 1 ? 1 : nmax > p.cacheRows ? p.cacheRows : nmax;
+    }
     if (!p.useRange && p.wl < nmax) nmax = (int64_t)p.wl + 1;
     int64_t maxS = nmax / (4ll * keySlots);  // at least four tiles per split
     if (maxS > 32) maxS = 32;
@@ -913,10 +960,63 @@ int static_fail(int code, const std::string& msg) {
   return code;
 }
 
+// The current device's copy of the area.  Set-up, once per device, with that device
+// current: in host code the array's name is only a handle, the kernel needs its device
+// address.
+int static_area(StaticDecodeArea** area, int* smCount) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess)
+    return static_fail(RT_EXECUTION_FAILED, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  if (device < 0 || device >= kMaxDevices)
+    return static_fail(RT_UNSUPPORTED_DEVICE, "rt_attn_decode_noalloc: device ordinal " +
+                                                  std::to_string(device) + " is past the " +
+                                                  std::to_string(kMaxDevices) +
+                                                  " devices this entry point keeps an address for");
+  std::lock_guard<std::mutex> lock(gStaticMutex);
+  if (!gStaticAddr[device]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, gStaticDecodeArea);
+    if (e != cudaSuccess || !ptr)
+      return static_fail(RT_EXECUTION_FAILED,
+                         std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess || sms < 1)
+      return static_fail(RT_EXECUTION_FAILED,
+                         std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+    gStaticSmCount[device] = sms;
+    gStaticAddr[device] = static_cast<StaticDecodeArea*>(ptr);
+  }
+  *area = gStaticAddr[device];
+  *smCount = gStaticSmCount[device];
+  return RT_OK;
+}
+
 }  // namespace
 }  // namespace rt
 
 extern "C" {
+
+int rt_attn_decode_noalloc_status(void* cuda_stream) {
+  using namespace rt;
+  StaticDecodeArea* area;
+  int smCount;
+  if (int s = static_area(&area, &smCount)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaStreamSynchronize(stream);
+  int status = 0;
+  if (e == cudaSuccess) e = cudaMemcpy(&status, &area->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess)
+    return static_fail(RT_EXECUTION_FAILED,
+                       std::string("rt_attn_decode_noalloc_status: ") + cudaGetErrorString(e));
+  if (status == 0) return RT_OK;
+  cudaMemset(&area->status, 0, sizeof(int));
+  return static_fail(RT_EXECUTION_FAILED,
+                     (status & kStatusWaitTimeout)
+                         ? "rt_attn_decode_noalloc: a bounded device-side wait ran out"
+                         : "rt_attn_decode_noalloc: a kvLens entry exceeds cacheRows");
+}
 
 int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
   using namespace rt;
@@ -932,7 +1032,7 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
                        "rt_attn_decode_noalloc: the cross-GPU exchange needs rt_attn_decode");
   if (a->batch < 1 || a->batch > 65535 || a->cacheRows < 1 || a->qHeads < 1 || a->headDim < 1 ||
       a->headDim > 128 || a->kvHeads < 1 || a->qHeads % a->kvHeads != 0 || a->kvLen < 0 ||
-      a->kvLen > a->cacheRows || (!a->kvLens && a->kvLen < 1) || a->windowLeft < 0 ||
+      (!a->kvSharded && a->kvLen > a->cacheRows) || (!a->kvLens && a->kvLen < 1) || a->windowLeft < 0 ||
       a->splits < 0 || a->splits > 64 || (a->kNew == nullptr) != (a->vNew == nullptr) ||
       a->cacheSeqStride < 0 ||
       (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim) ||
@@ -941,33 +1041,10 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
                        "rt_attn_decode_noalloc: a size or option is out of range (same rules as "
                        "rt_attn_decode)");
 
-  int device = 0;
-  cudaError_t e = cudaGetDevice(&device);
-  if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
-    return static_fail(RT_EXECUTION_FAILED, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
   StaticDecodeArea* area;
   int smCount;
-  {
-    // Set-up, once per device, with that device current: in host code the
-    // array's name is only a handle, the kernel needs its device address.
-    std::lock_guard<std::mutex> lock(gStaticMutex);
-    if (!gStaticAddr[device]) {
-      void* ptr = nullptr;
-      e = cudaGetSymbolAddress(&ptr, gStaticDecodeArea);
-      if (e != cudaSuccess || !ptr)
-        return static_fail(RT_EXECUTION_FAILED,
-                           std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-      int sms = 0;
-      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-      if (e != cudaSuccess || sms < 1)
-        return static_fail(RT_EXECUTION_FAILED,
-                           std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
-      gStaticSmCount[device] = sms;
-      gStaticAddr[device] = static_cast<StaticDecodeArea*>(ptr);
-    }
-    area = gStaticAddr[device];
-    smCount = gStaticSmCount[device];
-  }
+  cudaError_t e;
+  if (int s = static_area(&area, &smCount)) return s;
 
   DecodeParams p{};
   decode_params_from_args(*a, p);

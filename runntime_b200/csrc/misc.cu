@@ -59,44 +59,30 @@ __global__ void merge_partials_kernel(const float* __restrict__ partials, int pa
   }
 }
 
-// Runs after a decode launch that stored this rank's rows into the peers' buffers.  That
-// kernel has ended, so its stores are complete; one thread fences at system scope,
-// advances this rank's step counter and stores the new value into every rank's arrival
-// word for this rank.
-struct FlagPointers {
-  uint32_t* rank[RT_MAX_PEERS];
-};
-__global__ void exchange_signal_kernel(uint32_t* step, FlagPointers flags, int world, int rank) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  __threadfence_system();
-  const uint32_t epoch = *step + 1u;
-  *step = epoch;
-  for (int r = 0; r < world; r++)
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.rank[r] + rank), "r"(epoch)
-                 : "memory");
-}
-
-// The same merge over the rows the ranks exchanged: buffer holds two halves of
-// [world][units][2+hd]; the half of the step just computed is *step & 1.  Each block
-// first waits until every rank's arrival word has reached *step (the decode kernels of
-// the peers publish it after their rows have landed here).  The wait is bounded: about
-// a second, then the block records the failure in *status and writes zeros.
+// Merge of the rows the ranks exchanged, on the rank that owns the sequences.  `buffer` is
+// this rank's exchange buffer: two halves (by step parity) of [world][per * heads][2+hd],
+// source rank p's rows for this rank's `per` sequences; the half of the step just computed
+// is *step & 1 (the decode kernel's last block has moved *step before this kernel starts).
+// Each block first waits until every rank's arrival word has reached *step: a rank
+// publishes it after all of its rows for this owner have landed here.  The wait is bounded
+// (`limit` polls, about a second by default), then the block records the failure in *status
+// and writes zeros.  Output rows: sequences [firstSeq, firstSeq + owned) of `out`.
 template <typename T>
 __global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
                                        const uint32_t* __restrict__ flags,
-                                       const uint32_t* __restrict__ step, int world,
-                                       int64_t units, int hd, T* __restrict__ out, int* status) {
+                                       const uint32_t* __restrict__ step, int world, int per,
+                                       int owned, int firstSeq, int heads, int hd,
+                                       T* __restrict__ out, int* status, int limit) {
   __shared__ int sOk;
   const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(step);
   if (threadIdx.x == 0) sOk = 1;
   __syncthreads();
   if ((int)threadIdx.x < world) {
-    // An acquire load at system scope pairs with the peer's fence + store: once the
-    // word is seen, the rows stored before it are visible too (no full fence needed,
-    // which costs microseconds in every block).
+    // An acquire load at system scope pairs with the peer's fence + release store: once the
+    // word is seen, the rows stored before it are visible too.
     const uint32_t* f = flags + threadIdx.x;
     bool arrived = false;
-    for (int i = 0; i < (1 << 20); i++) {   // about a second with the sleeps below
+    for (int i = 0; i < limit; i++) {
       uint32_t seen;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
       // signed distance: a peer may already be a step ahead
@@ -107,22 +93,25 @@ __global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
+  const int64_t units = (int64_t)owned * heads;
   const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  T* dst = out + ((int64_t)firstSeq * heads + u) * hd;
   if (!sOk) {
     if (threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
     if (u < units)
-      for (int x = lane; x < hd; x += 32) out[u * hd + x] = from_f32<T>(0.f);
+      for (int x = lane; x < hd; x += 32) dst[x] = from_f32<T>(0.f);
     return;
   }
   if (u >= units) return;
   const int64_t stride = 2 + hd;
-  const float* partials = buffer + (int64_t)(epoch & 1u) * world * units * stride;
+  const int64_t slot = (int64_t)per * heads * stride;   // one source rank's rows
+  const float* partials = buffer + (int64_t)(epoch & 1u) * world * slot + u * stride;
   float M = kNegSeed;
-  for (int p = lane; p < world; p += 32) M = fmaxf(M, __ldcg(partials + ((int64_t)p * units + u) * stride));
+  for (int p = lane; p < world; p += 32) M = fmaxf(M, __ldcg(partials + p * slot));
   M = warp_max(M);
   float L = 0.f;
   for (int p = lane; p < world; p += 32) {
-    const float* r = partials + ((int64_t)p * units + u) * stride;
+    const float* r = partials + p * slot;
     L += __ldcg(r + 1) * __expf(__ldcg(r) - M);
   }
   L = warp_sum(L);
@@ -130,10 +119,10 @@ __global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
   for (int x = lane; x < hd; x += 32) {
     float o = 0.f;
     for (int p = 0; p < world; p++) {
-      const float* r = partials + ((int64_t)p * units + u) * stride;
+      const float* r = partials + p * slot;
       o = fmaf(__ldcg(r + 2 + x), __expf(__ldcg(r) - M), o);
     }
-    out[u * hd + x] = from_f32<T>(o * invL);
+    dst[x] = from_f32<T>(o * invL);
   }
 }
 
@@ -328,25 +317,21 @@ cudaError_t launch_write_rows(void* dst, const void* src, int64_t dstOffsetBytes
   return cudaGetLastError();
 }
 
-cudaError_t launch_exchange_signal(uint32_t* step, uint32_t* const* flags, int world, int rank,
-                                   cudaStream_t s) {
-  FlagPointers f{};
-  for (int r = 0; r < world && r < RT_MAX_PEERS; r++) f.rank[r] = flags[r];
-  exchange_signal_kernel<<<1, 32, 0, s>>>(step, f, world, rank);
-  return cudaGetLastError();
-}
-
 cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, const uint32_t* step,
-                                   int world, int64_t units, int hd, void* out, int dtype,
-                                   int* status, cudaStream_t s) {
+                                   int world, int per, int owned, int firstSeq, int heads, int hd,
+                                   void* out, int dtype, int* status, int limit, cudaStream_t s) {
+  if (owned <= 0) return cudaSuccess;   // this rank owns none of the sequences: nothing to merge
   const int warps = 8;
+  const int64_t units = (int64_t)owned * heads;
   const unsigned grid = (unsigned)((units + warps - 1) / warps);
   if (dtype == RT_F16)
-    merge_exchanged_kernel<__half><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, units, hd,
-                                                                static_cast<__half*>(out), status);
+    merge_exchanged_kernel<__half><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, per, owned,
+                                                                firstSeq, heads, hd,
+                                                                static_cast<__half*>(out), status, limit);
   else
-    merge_exchanged_kernel<float><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, units, hd,
-                                                               static_cast<float*>(out), status);
+    merge_exchanged_kernel<float><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, per, owned,
+                                                               firstSeq, heads, hd,
+                                                               static_cast<float*>(out), status, limit);
   return cudaGetLastError();
 }
 

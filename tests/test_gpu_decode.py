@@ -139,6 +139,49 @@ def test_batched_decode_with_append_matches_per_sequence_oracle(ex, dtype, heads
         ex.setStream(None)
 
 
+@pytest.mark.parametrize("heads,hd", [(8, 52), (32, 128)])
+def test_device_side_length_past_the_cache_is_refused_not_written(ex, heads, hd):
+    """kvLens lives on the device, so the host cannot check it: an entry one past
+    cacheRows must not append (writeRows: 'rows exceed dst capacity') nor read past the
+    cache.  The sequence comes out as zeros, the rows after its cache keep their
+    contents, the other sequences are computed, and rt_sync reports it."""
+    import torch
+    import runntime_b200 as rt
+    from runntime_b200.engine import decode_batched
+    batch, cacheRows, alloc = 3, 100, 104      # four guard rows behind each cache
+    lens = [100, 101, 37]
+    q, kc, vc, kn, vn, lt = _batched_inputs(batch, alloc, heads, heads, hd, "f16", lens)
+    dev = torch.device("cuda", 0)
+    qd, kcd, vcd, knd, vnd, ld = (t.to(dev) for t in (q, kc, vc, kn, vn, lt))
+    out = torch.full((batch, heads * hd), 7.0, dtype=qd.dtype, device=dev)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        for splits in (1, 3):
+            kcd.copy_(kc)
+            vcd.copy_(vc)
+            decode_batched(ex, qd, out, kcd, vcd, dtype="f16", batch=batch, cacheRows=cacheRows,
+                           cacheSeqStride=alloc * heads * hd, qHeads=heads, kvHeads=heads,
+                           headDim=hd, kvLen=cacheRows, kvLens=ld, kNew=knd, vNew=vnd,
+                           splits=splits)
+            with pytest.raises(rt.RunntimeError, match="kvLens entry past cacheRows") as e:
+                ex.sync()
+            assert e.value.code == "EXECUTION_FAILED"
+            got = out.float().cpu().numpy()
+            assert (got[1] == 0).all()
+            kc2, vc2 = kc.clone(), vc.clone()
+            for b in (0, 2):
+                L = lens[b]
+                kc2[b, L - 1], vc2[b, L - 1] = kn[b], vn[b]
+                want = sdpa_ref(q[b:b + 1].float().numpy(), kc2[b, :L].float().numpy(),
+                                vc2[b, :L].float().numpy(), qHeads=heads, kvHeads=heads,
+                                headDim=hd, windowRight=0, qPosOffset=L - 1)
+                oracle.assert_close(got[b], want, "f16", f"seq {b} splits {splits}")
+            assert torch.equal(kcd.cpu(), kc2) and torch.equal(vcd.cpu(), vc2)   # guard rows too
+            ex.sync()     # the report cleared the status word
+    finally:
+        ex.setStream(None)
+
+
 def test_batched_cross_attention_and_window(ex):
     import torch
     from runntime_b200.engine import decode_batched

@@ -163,25 +163,36 @@ def test_no_buffer_leak_across_evals(ex):
     assert ex.liveBuffers() == base
 
 
+def _emulated_world(world, batch, heads, hd, dev):
+    """Exchange structures for `world` ranks that all live on this GPU (plain torch
+    allocations stand where the peers' mapped blocks would)."""
+    import torch
+    from runntime_b200.engine import exchange_sizes, make_exchange
+    nfloat, nword, nstage = exchange_sizes(world, batch, heads, hd)
+    partials = [torch.zeros(nfloat, dtype=torch.float32, device=dev) for _ in range(world)]
+    control = [torch.zeros(nword, dtype=torch.int32, device=dev) for _ in range(world)]
+    stage = [torch.zeros(nstage, dtype=torch.float32, device=dev) for _ in range(world)]
+    xs = [make_exchange(world, r, partials, control, stage[r]) for r in range(world)]
+    return xs, control, (partials, stage)
+
+
 @pytest.mark.parametrize("world,splits,dtype", [(1, 0, "f16"), (2, 0, "f16"), (4, 3, "f16"),
                                                 (8, 0, "f16"), (3, 2, "f32")])
 def test_peer_exchange_of_partials_emulated_on_one_gpu(ex, world, splits, dtype):
     """The cross-GPU exchange with every "rank" on this GPU: the ranks' decode
-    launches run one after the other (each writes its rows into all the buffers and
-    signals), then each rank's merge finds all arrival words already set.  Three
-    steps, so that both halves of the buffers and the step counters are exercised."""
+    launches run one after the other (each sends every sequence's rows to the rank
+    that owns the sequence and signals it), then each rank's merge finds all arrival
+    words already set and writes its own sequences.  Three steps, so that both halves
+    of the buffers and the step counters are exercised.  Nine sequences: the ranks
+    own unequal numbers of them."""
     import torch
-    from runntime_b200.engine import decode_batched, exchange_words, make_exchange, shard_rows
-    batch, heads, kvHeads, hd, rows = 5, 8, 4, 64, 700
+    from runntime_b200.engine import owned_sequences, shard_rows
+    batch, heads, kvHeads, hd, rows = 9, 8, 4, 64, 700
     dev = torch.device("cuda", 0)
     tdt = torch.float16 if dtype == "f16" else torch.float32
     g = torch.Generator().manual_seed(9)
-    units = batch * heads
-    nfloat, nword = exchange_words(world, units, hd)
-    partials = [torch.zeros(nfloat, dtype=torch.float32, device=dev) for _ in range(world)]
-    control = [torch.zeros(nword, dtype=torch.int32, device=dev) for _ in range(world)]
-    xs = [make_exchange(world, r, partials, control) for r in range(world)]
-    outs = [torch.empty(batch, heads * hd, dtype=tdt, device=dev) for _ in range(world)]
+    xs, control, keep = _emulated_world(world, batch, heads, hd, dev)
+    outs = [torch.full((batch, heads * hd), 7.0, dtype=tdt, device=dev) for _ in range(world)]
     ex.setStream(torch.cuda.current_stream().cuda_stream)
     try:
         for step in range(3):
@@ -195,7 +206,6 @@ def test_peer_exchange_of_partials_emulated_on_one_gpu(ex, world, splits, dtype)
                 shards.append((k[:, s:e].contiguous().to(dev), v[:, s:e].contiguous().to(dev), e - s))
             # decode kernels of all ranks first, their merges after: nothing waits on a later launch
             from runntime_b200._lib import DecodeArgs, DTYPE_CODE, check
-            import ctypes as C
             for r in range(world):
                 ks, vs, n = shards[r]
                 d = DecodeArgs()
@@ -213,14 +223,156 @@ def test_peer_exchange_of_partials_emulated_on_one_gpu(ex, world, splits, dtype)
                     xs[r].phases = phase
                     check(ex._lib.rt_attn_decode(ex.ctx, C.byref(shards[r][3])), ex.ctx)
             ex.sync()
-            for b in range(batch):
-                ref = oracle.sdpa_ref(q[b:b + 1].float().numpy(), k[b].float().numpy(),
-                                      v[b].float().numpy(), qHeads=heads, kvHeads=kvHeads,
-                                      headDim=hd)
-                for r in range(world):
-                    oracle.assert_close(outs[r][b].float().cpu().numpy(), ref.reshape(-1), dtype,
-                                        f"step {step} rank {r} seq {b}")
-            assert all(int(c[world].item()) == step + 1 for c in control)      # step counters
-            assert all((c[:world] == step + 1).all().item() for c in control)  # arrival words
+            for r in range(world):
+                first, n = owned_sequences(batch, world, r)
+                got = outs[r].float().cpu().numpy()
+                for b in range(batch):
+                    if first <= b < first + n:
+                        ref = oracle.sdpa_ref(q[b:b + 1].float().numpy(), k[b].float().numpy(),
+                                              v[b].float().numpy(), qHeads=heads, kvHeads=kvHeads,
+                                              headDim=hd)
+                        oracle.assert_close(got[b], ref.reshape(-1), dtype,
+                                            f"step {step} rank {r} seq {b}")
+                    else:
+                        assert (got[b] == 7.0).all()       # another rank's sequence: untouched
+            for r, c in enumerate(control):
+                c = c.cpu()
+                assert int(c[world]) == step + 1                       # the rank's step counter
+                assert (c[world + 2:] == 0).all()                      # arrival counters back at zero
+                assert (c[:world] == step + 1).all()                   # every rank's arrival word
     finally:
         ex.setStream(None)
+
+
+def test_merge_gives_up_when_a_rank_never_signals(ex):
+    """A bounded wait that runs out: two ranks emulated on this GPU, rank 0 runs its
+    whole step, rank 1 never launches — rank 0's merge polls rank 1's arrival word a
+    (shortened) bounded number of times, writes zeros and records the failure, which
+    rt_sync turns into EXECUTION_FAILED.  Nothing spins without a bound."""
+    import torch
+    import runntime_b200 as rt
+    from runntime_b200._lib import OPT_WAIT_POLLS
+    from runntime_b200.engine import decode_batched
+    batch, heads, hd, rows = 4, 8, 52, 300
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(2)
+    xs, control, keep = _emulated_world(2, batch, heads, hd, dev)
+    k = torch.randn(batch, rows, heads * hd, generator=g).half().to(dev)
+    v = torch.randn(batch, rows, heads * hd, generator=g).half().to(dev)
+    q = (torch.randn(batch, heads * hd, generator=g) / 7).half().to(dev)
+    out = torch.full((batch, heads * hd), 3.0, dtype=torch.float16, device=dev)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    ex.setOption(OPT_WAIT_POLLS, 2000)      # a couple of milliseconds
+    try:
+        decode_batched(ex, q, out, k, v, dtype="f16", batch=batch, cacheRows=rows, qHeads=heads,
+                       kvHeads=heads, headDim=hd, kvLen=rows, exchange=xs[0])
+        with pytest.raises(rt.RunntimeError, match="bounded device-side wait ran out") as e:
+            ex.sync()
+        assert e.value.code == "EXECUTION_FAILED"
+        got = out.float().cpu().numpy()
+        assert (got[:2] == 0).all() and (got[2:] == 3.0).all()   # rank 0 merges sequences 0 and 1
+        ex.sync()                                                # the status word was cleared
+    finally:
+        ex.setOption(OPT_WAIT_POLLS, 1 << 20)
+        ex.setStream(None)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_sharded_kv_cache_engine_appends_on_the_owning_rank(ex, world):
+    """Caches split by position over `world` ranks (all emulated on this GPU): each
+    step's new K/V row lands in the shard that owns the position and nowhere else,
+    the ranks' partials merge to the attention over the whole sequence, and stepping
+    walks across the shard boundaries."""
+    import torch
+    from runntime_b200.engine import ShardedKvCacheEngine, owned_sequences, shard_of_position
+    batch, heads, hd, maxPositions, steps = 3, 8, 36, 40, 31
+    dev = torch.device("cuda", 0)
+    xs, control, keep = _emulated_world(world, batch, heads, hd, dev)
+    engines = [ShardedKvCacheEngine(ex, xs[r], batch=batch, maxPositions=maxPositions, qHeads=heads,
+                                    kvHeads=heads, headDim=hd, dtype="f16", device=dev)
+               for r in range(world)]
+    g = torch.Generator().manual_seed(5)
+    w = heads * hd
+    ks = torch.randn(steps, batch, w, generator=g).half()
+    vs = torch.randn(steps, batch, w, generator=g).half()
+    qs = (torch.randn(steps, batch, w, generator=g) / 6).half()
+    outs = [torch.empty(batch, w, dtype=torch.float16, device=dev) for _ in range(world)]
+    try:
+        for t in range(steps):
+            qd, kd, vd = qs[t].to(dev), ks[t].to(dev), vs[t].to(dev)
+            for phase in (1, 2):
+                for r in range(world):
+                    engines[r].step(qd, kd, vd, outs[r], phases=phase)
+            ex.sync()
+            if t in (0, 1, 12, 13, 14, 20, 27, 30):
+                for r in range(world):
+                    first, n = owned_sequences(batch, world, r)
+                    for b in range(first, first + n):
+                        want = sdpa_ref(qs[t, b:b + 1].float().numpy(), ks[:t + 1, b].float().numpy(),
+                                        vs[:t + 1, b].float().numpy(), qHeads=heads, kvHeads=heads,
+                                        headDim=hd, windowRight=0, qPosOffset=t)
+                        oracle.assert_close(outs[r][b].float().cpu().numpy(), want, "f16",
+                                            f"t={t} rank {r} seq {b}")
+        shardRows = engines[0].shardRows
+        for r in range(world):
+            kc = engines[r].k.cpu()
+            for row in range(shardRows):
+                t = r * shardRows + row
+                if t < steps:
+                    owner, local = shard_of_position(t, shardRows)
+                    assert (owner, local) == (r, row)
+                    assert torch.equal(kc[:, row], ks[t])
+                else:
+                    assert (kc[:, row] == 0).all()
+    finally:
+        ex.setStream(None)
+
+
+def test_exchange_blocks_from_the_c_abi_on_one_gpu(ex):
+    """rt_xmem_*: two ranks that live in one process attach each other's blocks (the
+    one-process-several-devices form; here both on this GPU) and run a step."""
+    import torch
+    from runntime_b200.engine import ExchangeMemory, decode_batched, owned_sequences, shard_rows
+    import runntime_b200 as rt
+    batch, heads, hd, rows, world = 6, 8, 52, 500, 2
+    dev = torch.device("cuda", 0)
+    mems = [ExchangeMemory(0, world, r, batch, heads, hd) for r in range(world)]
+    with pytest.raises(rt.RunntimeError, match="rank 1 has not been imported or attached") as e:
+        mems[0].exchange()
+    assert e.value.code == "NOT_INITIALIZED"
+    handle = mems[0].export()
+    assert len(handle) == 64
+    mems[0].attach(1, mems[1])
+    mems[1].attach(0, mems[0])
+    with pytest.raises(rt.RunntimeError, match="already mapped"):
+        mems[1].attach(0, mems[0])
+    xs = [m.exchange() for m in mems]
+    g = torch.Generator().manual_seed(8)
+    k = torch.randn(batch, rows, heads * hd, generator=g).half()
+    v = torch.randn(batch, rows, heads * hd, generator=g).half()
+    q = (torch.randn(batch, heads * hd, generator=g) / 7).half()
+    outs = [torch.empty(batch, heads * hd, dtype=torch.float16, device=dev) for _ in range(world)]
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        shards = []
+        for r in range(world):
+            s, e_ = shard_rows(rows, world, r)
+            shards.append((k[:, s:e_].contiguous().to(dev), v[:, s:e_].contiguous().to(dev), e_ - s))
+        for phase in (1, 2):
+            for r in range(world):
+                xs[r].phases = phase
+                ks_, vs_, n = shards[r]
+                decode_batched(ex, q.to(dev), outs[r], ks_, vs_, dtype="f16", batch=batch,
+                               cacheRows=n, qHeads=heads, kvHeads=heads, headDim=hd, kvLen=n,
+                               exchange=xs[r])
+        ex.sync()
+        for r in range(world):
+            first, n = owned_sequences(batch, world, r)
+            for b in range(first, first + n):
+                ref = oracle.sdpa_ref(q[b:b + 1].float().numpy(), k[b].float().numpy(),
+                                      v[b].float().numpy(), qHeads=heads, kvHeads=heads, headDim=hd)
+                oracle.assert_close(outs[r][b].float().cpu().numpy(), ref.reshape(-1), "f16")
+    finally:
+        ex.setStream(None)
+        for m in mems:
+            m.destroy()

@@ -1,6 +1,8 @@
-"""KV-sequence-sharded decode on two real GPUs (skipped on a one-GPU box): the
-exchange of partials through peer memory against the NCCL all-gather form and
-against the oracle over the whole, unsharded cache.  One process per GPU."""
+"""KV-sequence-sharded decode on two real GPUs (skipped on a one-GPU box), one process
+per GPU: the exchange of partials through peer memory — buffers from torch's symmetric
+memory and from the library's own CUDA-IPC set-up (rt_xmem_*) — against the NCCL
+all-gather form and against the oracle over the whole, unsharded cache; then the
+position-sharded KV-cache engine stepping tokens across the shard boundary."""
 import os
 
 import numpy as np
@@ -28,38 +30,86 @@ def _worker(rank, world, port, result):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     import oracle
     import runntime_b200 as rt
-    from runntime_b200.engine import PeerExchangeDecode, ShardedDecode, shard_rows
+    from runntime_b200.engine import (PeerExchangeDecode, ShardedDecode, ShardedKvCacheEngine,
+                                      owned_sequences, shard_rows)
     ex = rt.CudaExecutor(rank)
-    ex.setStream(torch.cuda.current_stream().cuda_stream)
     batch, heads, kvHeads, hd, rows = 6, 8, 8, 52, 1500
-    peer = PeerExchangeDecode(units=batch * heads, headDim=hd, device=dev)
-    nccl = ShardedDecode()
-    g = torch.Generator().manual_seed(4)          # same numbers on every rank
-    worst_vs_nccl, worst_ok = 0.0, True
+    first, owned = owned_sequences(batch, world, rank)
+    mine = slice(first, first + owned)
+    report = {"transports": []}
     try:
+        peers = {}
+        for transport in ("symm", "ipc"):
+            try:
+                peers[transport] = PeerExchangeDecode(batch=batch, qHeads=heads, headDim=hd,
+                                                      device=dev, transport=transport)
+                report["transports"].append(transport)
+            except Exception as e:  # noqa: BLE001 - recorded; at least one transport must work
+                report[transport + "_error"] = f"{type(e).__name__}: {e}"
+            # every rank must agree on which transports exist
+            ok = torch.tensor([1 if transport in peers else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if not int(ok.item()):
+                peers.pop(transport, None)
+        nccl = ShardedDecode()
+        g = torch.Generator().manual_seed(4)          # same numbers on every rank
+        worst_vs_nccl, worst_ok = 0.0, True
         for step in range(4):
             k = torch.randn(batch, rows, kvHeads * hd, generator=g).half()
             v = torch.randn(batch, rows, kvHeads * hd, generator=g).half()
             q = (torch.randn(batch, heads * hd, generator=g) / 7).half()
             s, e = shard_rows(rows, world, rank)
             ks, vs, qd = k[:, s:e].contiguous().to(dev), v[:, s:e].contiguous().to(dev), q.to(dev)
-            out_p = torch.empty(batch, heads * hd, dtype=torch.float16, device=dev)
-            out_n = torch.empty_like(out_p)
+            out_n = torch.empty(batch, heads * hd, dtype=torch.float16, device=dev)
             part = torch.empty(batch * heads, 2 + hd, dtype=torch.float32, device=dev)
             common = dict(dtype="f16", batch=batch, shardRows=e - s, qHeads=heads, kvHeads=kvHeads,
                           headDim=hd)
-            peer.step(ex, qd, ks, vs, out_p, **common)
             nccl.step(ex, qd, ks, vs, out_n, partials=part, **common)
             ex.sync()
-            worst_vs_nccl = max(worst_vs_nccl, float((out_p.float() - out_n.float()).abs().max()))
-            if rank == 0:
-                for b in range(batch):
-                    ref = oracle.sdpa_ref(q[b:b + 1].float().numpy(), k[b].float().numpy(),
-                                          v[b].float().numpy(), qHeads=heads, kvHeads=kvHeads,
-                                          headDim=hd).reshape(-1)
-                    got = out_p[b].float().cpu().numpy()
+            refs = [oracle.sdpa_ref(q[b:b + 1].float().numpy(), k[b].float().numpy(),
+                                    v[b].float().numpy(), qHeads=heads, kvHeads=kvHeads,
+                                    headDim=hd).reshape(-1) for b in range(first, first + owned)]
+            for name, peer in peers.items():
+                out_p = torch.zeros(batch, heads * hd, dtype=torch.float16, device=dev)
+                peer.step(ex, qd, ks, vs, out_p, **common)
+                ex.sync()
+                worst_vs_nccl = max(worst_vs_nccl,
+                                    float((out_p[mine].float() - out_n[mine].float()).abs().max()))
+                for i, ref in enumerate(refs):
+                    got = out_p[first + i].float().cpu().numpy()
                     worst_ok &= bool(np.all(np.abs(got - ref) <= 2e-3 + 4e-3 * np.abs(ref)))
-        result[rank] = (worst_vs_nccl, worst_ok)
+        # the KV-cache engine sharded by position: tokens cross from rank 0's shard to rank 1's
+        append_ok = True
+        if peers:
+            peer = next(iter(peers.values()))
+            maxPositions, steps = 64, 50
+            eng = ShardedKvCacheEngine(ex, peer.exchange, batch=batch, maxPositions=maxPositions,
+                                       qHeads=heads, kvHeads=kvHeads, headDim=hd, dtype="f16",
+                                       device=dev)
+            w = kvHeads * hd
+            kt = torch.randn(steps, batch, w, generator=g).half()
+            vt = torch.randn(steps, batch, w, generator=g).half()
+            qt = (torch.randn(steps, batch, heads * hd, generator=g) / 7).half()
+            out = torch.zeros(batch, heads * hd, dtype=torch.float16, device=dev)
+            for t in range(steps):
+                eng.step(qt[t].to(dev), kt[t].to(dev), vt[t].to(dev), out)
+                if t in (0, 30, 31, 32, 33, 49):
+                    ex.sync()
+                    for b in range(first, first + owned):
+                        ref = oracle.sdpa_ref(qt[t, b:b + 1].float().numpy(),
+                                              kt[:t + 1, b].float().numpy(),
+                                              vt[:t + 1, b].float().numpy(), qHeads=heads,
+                                              kvHeads=kvHeads, headDim=hd, windowRight=0,
+                                              qPosOffset=t).reshape(-1)
+                        got = out[b].float().cpu().numpy()
+                        append_ok &= bool(np.all(np.abs(got - ref) <= 2e-3 + 4e-3 * np.abs(ref)))
+            ex.sync()
+            lo = rank * eng.shardRows
+            mine_rows = kt[lo:min(steps, lo + eng.shardRows)].transpose(0, 1)
+            append_ok &= bool(torch.equal(eng.k[:, :mine_rows.shape[1]].cpu(), mine_rows))
+            append_ok &= bool((eng.k[:, mine_rows.shape[1]:] == 0).all().item())
+        report.update(diff=worst_vs_nccl, ok=worst_ok, append_ok=append_ok)
+        result[rank] = report
     finally:
         ex.setStream(None)
         ex.dispose()
@@ -76,6 +126,10 @@ def test_peer_exchange_matches_nccl_and_oracle_on_two_gpus():
         mp.spawn(_worker, args=(world, 29533, result), nprocs=world, join=True)
         assert len(result) == world
         for rank in range(world):
-            diff, ok = result[rank]
-            assert diff <= 1e-3, (rank, diff)     # same partials, merged in another order
-            assert ok, rank
+            r = result[rank]
+            assert r["transports"], r              # at least one way to map the peers worked
+            assert r["diff"] <= 1e-3, (rank, r)    # same partials, merged in another order
+            assert r["ok"], (rank, r)
+            assert r["append_ok"], (rank, r)
+        # the library's own set-up is the one a host without torch has: say so if it failed
+        assert "ipc" in result[0]["transports"], result[0]

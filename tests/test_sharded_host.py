@@ -91,14 +91,79 @@ def test_sharded_decode_exchange_on_cpu_ranks(world, rows):
 
 def test_exchange_layout_of_buffers_and_control_words():
     """Sizes and addresses of the cross-GPU exchange (host arithmetic only)."""
-    from runntime_b200.engine import exchange_words, make_exchange
-    world, units, hd = 4, 512 * 8, 52
-    nfloat, nword = exchange_words(world, units, hd)
-    assert nfloat == 2 * world * units * 54 and nword == world + 1
+    from runntime_b200.engine import exchange_sizes, make_exchange, owned_sequences
+    world, batch, heads, hd = 4, 512, 8, 52
+    nfloat, nword, nstage = exchange_sizes(world, batch, heads, hd)
+    # a rank's buffer holds the rows of the 128 sequences it merges, from every rank, twice
+    assert nfloat == 2 * world * 128 * heads * 54 and nword == 2 * world + 3
+    assert nstage == batch * heads * 54
     bufs = [0x10000000 + r * 0x1000000 for r in range(world)]
     ctl = [0x90000000 + r * 0x100 for r in range(world)]
-    x = make_exchange(world, 2, bufs, ctl)
+    x = make_exchange(world, 2, bufs, ctl, 0xA0000000)
     assert (x.world, x.rank) == (4, 2)
     assert [x.partials[r] for r in range(world)] == bufs and x.partials[4] is None
     assert [x.flags[r] for r in range(world)] == ctl
-    assert x.step == ctl[2] + 4 * world
+    assert x.step == ctl[2] + 4 * world and x.stage == 0xA0000000
+    # every sequence has exactly one owner and every rank owns one (batch >= world)
+    for batch, world in ((512, 8), (6, 4), (8, 8), (7, 3), (5, 5), (9, 8)):
+        spans = [owned_sequences(batch, world, r) for r in range(world)]
+        covered = [b for first, n in spans for b in range(first, first + n)]
+        assert covered == list(range(batch)), (batch, world, spans)
+        assert min(n for _, n in spans) >= 1 and max(n for _, n in spans) <= -(-batch // world)
+    assert owned_sequences(6, 4, 3) == (5, 1)
+
+
+def test_positions_map_to_one_rank_and_row():
+    from runntime_b200.engine import shard_of_position
+    for maxPositions, world in ((448, 2), (8192, 8), (194, 4), (7, 3)):
+        shardRows = -(-maxPositions // world)
+        seen = set()
+        for t in range(maxPositions):
+            r, row = shard_of_position(t, shardRows)
+            assert 0 <= r < world and 0 <= row < shardRows and r * shardRows + row == t
+            seen.add((r, row))
+        assert len(seen) == maxPositions
+
+
+def _append_worker(rank, world, port, result):
+    """Each CPU rank keeps its shard of the caches as numpy arrays and appends the new
+    token's row only when the position is its own — the host-side rule of
+    ShardedKvCacheEngine; an all-gather of the shards must reproduce the whole cache."""
+    import torch
+    import torch.distributed as dist
+    from runntime_b200.engine import shard_of_position
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        maxPositions, width, steps = 23, 6, 23
+        shardRows = -(-maxPositions // world)
+        shard = np.zeros((shardRows, width), np.float32)
+        rng = np.random.default_rng(1)       # the same rows on every rank
+        rows = rng.standard_normal((steps, width)).astype(np.float32)
+        for t in range(steps):
+            r, local = shard_of_position(t, shardRows)
+            if r == rank:
+                shard[local] = rows[t]
+        gathered = [torch.zeros(shardRows, width) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(shard))
+        whole = torch.cat(gathered).numpy()[:maxPositions]
+        assert np.array_equal(whole, rows)
+        result[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_append_ownership_on_cpu_ranks(world):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    result = ctx.Array("i", world)
+    port = _free_port()
+    procs = [ctx.Process(target=_append_worker, args=(r, world, port, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert list(result) == [1] * world
