@@ -66,11 +66,14 @@ RT_API int rt_ctx_destroy(rt_ctx* ctx);
  * restores the context's stream. */
 RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
 /* Context options.  RT_OPT_PREFILL_TC (default 1): route eligible f16 prefill
- * shapes to a tensor-core kernel, the library choosing among its three (one or
- * two 128-row query tiles per thread block, or one tile whose key tiles alternate
- * between two softmax warpgroups); 0 sends every prefill to the FP32-pipe kernel,
- * 2 forces one tile, 3 forces two tiles, 4 forces the alternating form, each where
- * that kernel applies (all compute the same op; the switch exists for testing). */
+ * shapes to a tensor-core kernel of the library's choice (head sizes up to 128,
+ * narrow heads included: one 128-row query tile per thread block whose key tiles
+ * alternate between two softmax warpgroups; head size 256: one tile, one
+ * warpgroup).  0 sends every prefill to the FP32-pipe kernel; 2 forces one tile
+ * with one warpgroup, 3 two tiles per block, 4 the alternating form, 5 the
+ * alternating form on pairs of thread blocks that share every K/V tile — each
+ * where that kernel applies (all compute the same op; the switch exists for
+ * testing and measurement). */
 #define RT_OPT_PREFILL_TC 1
 /* RT_OPT_WAIT_POLLS (default 1 << 20, about a second): how often the merge of a
  * cross-GPU decode step polls for the other ranks' rows before it gives up, writes

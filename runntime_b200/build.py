@@ -43,11 +43,14 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if it is missing or older than its sources."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines=(), target: str = LIB) -> str:
+    """Compile the library if it is missing or older than its sources.  ``defines``
+    (extra -D macros) and ``target`` build a variant beside the product library, for
+    kernel experiments."""
+    if not force and not defines and target == LIB and not _stale():
         return LIB
-    objdir = os.path.join(HERE, "build")
+    objdir = (os.path.join(HERE, "build") if target == LIB else
+              os.path.join(os.path.dirname(target), "build_" + os.path.basename(target)))
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
     env = dict(os.environ)
@@ -57,8 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-ccbin", "/usr/bin/g++", "-I", os.path.join(ROOT, "include"),
-               "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-ccbin", "/usr/bin/g++", "-I",
+               os.path.join(ROOT, "include"), "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE,
@@ -71,10 +74,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    link = [nvcc, "-shared", "-cudart", "static", "-ccbin", "/usr/bin/g++", "-o", LIB, *objs,
+    link = [nvcc, "-shared", "-cudart", "static", "-ccbin", "/usr/bin/g++", "-o", target, *objs,
             "-Xlinker", "--exclude-libs,ALL", "-ldl", "-lpthread", "-lrt"]
     subprocess.check_call(link, env=env)
-    return LIB
+    return target
 
 
 if __name__ == "__main__":

@@ -29,11 +29,6 @@ struct rt_ctx {
 namespace {
 
 constexpr uint32_t kLive = 0x52544358u;  // 'RTCX'
-// The default routing (RT_OPT_PREFILL_TC = 1) takes the two-tile kernel once the
-// grid has this many thread blocks per SM: it runs half as many, twice as long
-// blocks, so on a small grid the last, partly filled wave costs more than the
-// faster steady state gains (measured: 512 blocks on 148 SMs lose, 16384 win).
-constexpr int64_t kTwoTileBlocksPerSm = 6;
 constexpr uint32_t kDead = 0x44454144u;  // 'DEAD'
 
 thread_local std::string tlsError;
@@ -311,8 +306,8 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
 int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
   RT_ENTER(ctx);
   if (option == RT_OPT_PREFILL_TC) {
-    if (value < 0 || value > 4)
-      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..4, got %d",
+    if (value < 0 || value > 5)
+      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..5, got %d",
                   value);
     ctx->useTc = value;
     return RT_OK;
@@ -389,23 +384,29 @@ int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* ho
 }
 
 // 0 = FP32-pipe kernel, 1 = tensor cores, one query tile per CTA, 2 = two tiles per CTA,
-// 3 = one tile with two softmax warpgroups on alternate key tiles.
+// 3 = one tile with two softmax warpgroups on alternate key tiles, 4 = the same in pairs of
+// CTAs that share every K/V tile.
 static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dtype) {
   if (!ctx->useTc) return 0;
   const bool tc3 = rt::prefill_tc3_supported(p, dtype);
-  if (ctx->useTc == 4 && tc3) return 3;
-  if (!rt::prefill_tc_supported(p, dtype)) return tc3 ? 3 : 0;   // heads narrower than 64
-  if (ctx->useTc != 2 && rt::prefill_tc2_supported(p, dtype)) {
-    const int64_t blocks = (p.qLen + 255) / 256 * p.qHeads;
-    if (ctx->useTc == 3 || blocks >= kTwoTileBlocksPerSm * ctx->smCount) return 2;
-  }
+  if (ctx->useTc == 5 && rt::prefill_tc3_pair_supported(p, dtype)) return 4;
+  if ((ctx->useTc == 4 || ctx->useTc == 5) && tc3) return 3;
+  if (!rt::prefill_tc_supported(p, dtype)) return (tc3 && ctx->useTc == 1) ? 3 : 0;  // heads narrower than 64
+  if (ctx->useTc == 3 && rt::prefill_tc2_supported(p, dtype)) return 2;
+  // The library's own choice: the alternating-warpgroup kernel up to head size 128 (measured
+  // on the large causal prefill, a second of back-to-back launches: 914 TFLOP/s against 858
+  // for two tiles per block and 770 for one tile with one softmax warpgroup); head size 256
+  // stays on the one-tile kernel, whose 64-key tiles keep three tiles in flight where this
+  // one's 128-key tiles leave its ring one and a quarter (545 against 478 TFLOP/s on the
+  // sliding-window GQA prefill).
+  if (ctx->useTc == 1 && tc3 && p.hd <= 128) return 3;
   return 1;
 }
 
 static const char* route_of(const rt_ctx* ctx, const rt_attn_args* a) {
   if (a->qLen == 1) return "decode";
   const int k = prefill_kernel_of(ctx, to_params(a), a->dtype);
-  return k == 3 ? "prefill_tc3" : k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
+  return k == 4 ? "prefill_tc3_pair" : k == 3 ? "prefill_tc3" : k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
 }
 
 int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
@@ -446,7 +447,7 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
   const int kernel = prefill_kernel_of(ctx, p, a->dtype);
   if (kernel != 0) {
     std::string err;
-    cudaError_t e = kernel == 3   ? rt::launch_prefill_tc3(p, ctx->statusDev, ctx->stream, &err)
+    cudaError_t e = kernel >= 3   ? rt::launch_prefill_tc3(p, kernel == 4, ctx->statusDev, ctx->stream, &err)
                     : kernel == 2 ? rt::launch_prefill_tc2(p, ctx->statusDev, ctx->stream, &err)
                                   : rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
     if (e != cudaSuccess)

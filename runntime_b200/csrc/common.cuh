@@ -266,7 +266,10 @@ cudaError_t launch_prefill_tc2(const AttnParams& p, int* status, cudaStream_t s,
 // One query tile per CTA, two softmax warpgroups on alternate key tiles (head sizes 64, 128,
 // 256, and heads narrower than 64 padded inside the tile).
 bool prefill_tc3_supported(const AttnParams& p, int dtype);
-cudaError_t launch_prefill_tc3(const AttnParams& p, int* status, cudaStream_t s, std::string* err);
+// ... and the same with pairs of CTAs (a cluster of two) sharing every K/V tile.
+bool prefill_tc3_pair_supported(const AttnParams& p, int dtype);
+cudaError_t launch_prefill_tc3(const AttnParams& p, bool pair, int* status, cudaStream_t s,
+                               std::string* err);
 // Fills kvPerCta/keySlots/stages/splits; returns false with a message when the shape cannot run.
 bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);

@@ -36,7 +36,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   __shared__ __align__(8) uint64_t sFull[GSTAGES], sEmpty[GSTAGES], sAcc;
   __shared__ uint32_t sTmemBase;
   __shared__ int sAbort;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   TC_TRACE_DECL
   TC_TRACE(0, 0);
   const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;

@@ -27,6 +27,19 @@
 // softmax threads with zeros in those columns, so the neighbours' columns add
 // nothing to the scores, and the output columns they produce are dropped.
 //
+// Pairs (head sizes 128 and 256).  Two CTAs of a cluster, on two SMs, take two adjacent
+// 128-row query tiles of the same head and run every product as ONE tcgen05.mma of
+// cta_group::2 (M = 256: 128 rows per CTA, each into its own tensor memory), issued by
+// the even CTA.  The B operand of such a product is split between the two CTAs' shared
+// memories — each holds 64 of a K tile's 128 keys, and half of a V tile's columns — so
+// each SM fetches only half of every K/V tile from the L2 (that traffic is what limits
+// this kernel: it burns power at head size 128 and its latency cannot be hidden behind
+// one SM's 160 KB of tile buffers at head size 256) and its ring holds twice as many
+// tiles.  Everything else is per CTA as described above; the odd CTA's MMA warps idle.
+// The peer's loads report to the even CTA's barriers (the cta_group::2 form of the bulk
+// tensor copy), its softmax warps arrive on them remotely, and the even CTA's commits
+// arrive on both CTAs' barriers.  Every copy has one destination CTA.
+//
 // Semantics are the 'attn' op's (see rt_attn.h); replaces attnFlash
 // (packages/runntime/src/core/kernels/attention/attnFlash.ts:93-276).  Every wait is
 // bounded; a wait that runs out sets the status word and the CTA winds down through
@@ -44,26 +57,33 @@ using namespace tc;
 constexpr int kThreads3 = 384;
 constexpr int kRegsSoftmax3 = 216, kRegsOther3 = 64;  // 2*128*216 + 128*64 <= 384*168
 constexpr int BK3 = 128;
-constexpr int kMaxSlots = 8;
+constexpr int kMaxSlots = 12;
 
-template <int HD>
+template <int HD, bool PAIR>
 struct Cfg3 {
   static constexpr int CHUNKS = HD / 64;                       // 64-column chunks of a row
   static constexpr int Q_BYTES = BM * HD * 2;
-  static constexpr bool SPLIT = HD == 256;                      // K and V tiles arrive in two parts
+  // One CTA alone at head size 256: K and V tiles arrive in two parts (K: 128 columns each,
+  // V: 64 keys each) so that a ring slot is 32 KB.  A pair holds half tiles anyway.
+  static constexpr bool SPLIT = HD == 256 && !PAIR;
   static constexpr int KP = SPLIT ? 2 : 1, VP = SPLIT ? 2 : 1;  // parts per key tile
-  static constexpr int SLOT_BYTES = SPLIT ? 32 * 1024 : BK3 * HD * 2;
-  static constexpr int SLOTS_FIT = (226 * 1024 - Q_BYTES) / SLOT_BYTES;
-  static constexpr int SLOTS = SLOTS_FIT > kMaxSlots ? kMaxSlots : SLOTS_FIT;
-  static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024;
+  static constexpr int K_ROWS = PAIR ? BK3 / 2 : BK3;           // keys of a K tile held by this CTA
   static constexpr int K_CHUNKS = SPLIT ? 2 : CHUNKS;           // 64-column chunks in one K part
   static constexpr int V_ROWS = SPLIT ? 64 : BK3;               // keys in one V part
+  static constexpr int V_CHUNKS = PAIR ? CHUNKS / 2 : CHUNKS;   // 64-column chunks of V held here
+  static constexpr int K_BYTES = K_CHUNKS * K_ROWS * 128, V_BYTES = V_CHUNKS * V_ROWS * 128;
+  static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
+  static constexpr int SLOTS_FIT = (225 * 1024 - Q_BYTES) / SLOT_BYTES;
+  static constexpr int SLOTS = SLOTS_FIT > kMaxSlots ? kMaxSlots : SLOTS_FIT;
+  static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024;
   static constexpr int O_COL = 2 * BK3;
   static constexpr bool P_OWN = HD <= 128;                      // P has columns of its own
   static constexpr int P_COL = O_COL + 128;
   static constexpr int TMEM_COLS = 512;
+  static constexpr int CTAS = PAIR ? 2 : 1;
   static_assert(SLOTS >= KP + VP + 1, "ring too small");
   static_assert(O_COL + HD <= TMEM_COLS, "tensor memory budget");
+  static_assert(!PAIR || HD >= 128, "a pair splits V into 64-column chunks");
 };
 
 struct Barriers3 {
@@ -81,26 +101,110 @@ __device__ __forceinline__ int seq_v(int j, int n) {
   return KP + j * (KP + VP) + (j + 1 < n ? KP : 0);
 }
 
+// ---- the cta_group::2 forms (a pair of CTAs on two SMs acting as one MMA unit) ----------
+
+// In the shared window of a cluster, bit 24 of an address tells the two CTAs of a pair
+// apart: cleared it names the even CTA's copy of the same location.
+constexpr uint32_t kPeerBit = 1u << 24;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrives on a barrier anywhere in the cluster (here: the even CTA's copy).  Default
+// semantics (release at CTA scope): what the consumer reads — P in this CTA's tensor memory
+// — is ordered by the tcgen05 fences around the arrival, and a cluster-scope release on
+// every arrival costs the arriving warp about a thousand cycles (measured).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Tiled load into this CTA's shared memory whose completion is counted on the EVEN CTA's
+// barrier at the same offset (the pair's MMA issuer waits there for both halves).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], "
+      "[%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar & ~kPeerBit)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dstSmem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+// Arrives once on the barrier at `bar`'s offset in each CTA of the pair when all MMAs issued
+// so far by this thread have completed in both: one commit per CTA, the second one naming
+// the odd CTA's copy of the barrier (measured: as fast as a single commit naming both).
+__device__ __forceinline__ void tc_commit_one(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  tc_commit_one(bar);
+  tc_commit_one(bar | kPeerBit);
+}
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
+      "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_pair(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(dTmem),
+      "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor of a pair's product: M = 256 over the two CTAs.
+constexpr uint32_t instr_desc_pair(int n, bool bMnMajor) {
+  return (instr_desc(n, bMnMajor) & ~(0x1fu << 24)) | ((uint32_t)(256 >> 4) << 24);
+}
+
 // PADDED: the head is narrower than the 64 columns the tile holds (see the file header);
 // p.hd is the real size, `shift` = (kvh * hd) & 7 the head's first column inside the box.
-template <int HD, bool PADDED>
+// PAIR: two CTAs of a cluster share every K/V tile (see the file header).
+template <int HD, bool PADDED, bool PAIR>
 __global__ void __launch_bounds__(kThreads3, 1)
 prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, const AttnParams p, int* status) {
-  using C = Cfg3<HD>;
+  using C = Cfg3<HD, PAIR>;
   constexpr int BK = BK3, KP = C::KP, VP = C::VP, NS = C::SLOTS;
-  static_assert(!PADDED || HD == 64, "narrow heads are padded to 64 columns");
+  static_assert(!PADDED || (HD == 64 && !PAIR), "narrow heads are padded to 64 columns, one CTA");
   extern __shared__ unsigned char smemRaw[];
   __shared__ Barriers3 bars;
   __shared__ uint32_t sTmemBase;
   __shared__ int sAbort;
-  __shared__ int sLoMin[4], sEndMax[4];
+  __shared__ int sLoMin[8], sEndMax[8];
   __shared__ float sMref[BM];          // the rows' reference points (log2 domain)
   __shared__ float sL[2][BM];          // the warpgroups' row sums, for the epilogue
   __shared__ volatile int sMaxDone[4];  // per warp of a warpgroup: tiles whose max phase is over
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qTile = (int)gridDim.x - 1 - (int)blockIdx.x;  // long rows first under a causal mask
+  TC_TRACE_DECL
+  // Long rows first under a causal mask; the two CTAs of a pair take adjacent row tiles.
+  const int cta = PAIR ? (int)cluster_ctarank() : 0;
+  const int unit = (int)(gridDim.x / C::CTAS) - 1 - (int)(blockIdx.x / C::CTAS);
+  const int qTile = unit * C::CTAS + cta;
+  const bool leader = cta == 0;
   const int h = blockIdx.y;
   const int kvh = h / (p.qHeads / p.kvHeads);
   const int64_t row0 = (int64_t)qTile * BM;
@@ -120,20 +224,28 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(smem_u32(&bars.sFull[b]), 1);
-      mbar_init(smem_u32(&bars.sFree[b]), 4);        // one arrival per warp of the warpgroup
-      mbar_init(smem_u32(&bars.pReady[b][0]), 4);
-      mbar_init(smem_u32(&bars.pReady[b][1]), 4);
+      // one arrival per warp of the warpgroup — of both CTAs' warpgroups in a pair, whose
+      // arrivals all go to the even CTA, where the MMA issuers wait
+      mbar_init(smem_u32(&bars.sFree[b]), 4 * C::CTAS);
+      mbar_init(smem_u32(&bars.pReady[b][0]), 4 * C::CTAS);
+      mbar_init(smem_u32(&bars.pReady[b][1]), 4 * C::CTAS);
       mbar_init(smem_u32(&bars.pvDone[b]), 1);
     }
     fence_barrier_init();
   }
   if (warp == 9) {
-    tmem_alloc(smem_u32(&sTmemBase), C::TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(&sTmemBase), C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&sTmemBase), C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
 
-  // Band of this thread's row (warpgroup 0 computes it; warpgroup 1 gets the same row's
-  // band from the same formula), then of the whole row tile.
+  // Band of this thread's row, then of the whole unit (one row tile, or the pair's two):
+  // the two CTAs of a pair walk the same key tiles, so each works the range out for both —
+  // warps 0-3 from its own rows, warps 4-7 from the other CTA's.
   const int rowInTile = tid & 127;
   int lo = 1, end = 0;  // empty
   if (warp < 8) {
@@ -146,8 +258,18 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         end = (int)e64;
       }
     }
-    if (warp < 4) {
-      int wl = lo <= end ? lo : INT_MAX, we = lo <= end ? end : -1;
+    int olo = lo, oend = end;   // the row this thread contributes to the unit's range
+    if (PAIR && warp >= 4) {
+      const int64_t other = (int64_t)(unit * 2 + (1 - cta)) * BM + rowInTile;
+      olo = 1, oend = 0;
+      if (other < p.qLen) {
+        int64_t l64, e64;
+        row_band(p, other, l64, e64);
+        if (l64 <= e64) olo = (int)l64, oend = (int)e64;
+      }
+    }
+    if (warp < 4 || PAIR) {
+      int wl = olo <= oend ? olo : INT_MAX, we = olo <= oend ? oend : -1;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         wl = min(wl, __shfl_xor_sync(0xffffffffu, wl, o));
@@ -156,17 +278,25 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if (lane == 0) {
         sLoMin[warp] = wl;
         sEndMax[warp] = we;
-        sMaxDone[warp] = 0;
       }
+    }
+    if (warp < 4) {
+      if (lane == 0) sMaxDone[warp] = 0;
       sMref[rowInTile] = p.sinks ? p.sinks[h] : kNegSeed;  // sinks arrive in the log2 domain
     }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // both CTAs' barriers exist before either is signalled from afar
   tc_fence_after_sync();
+  TC_TRACE(99, 0);
   const uint32_t tmem = sTmemBase;
-  const int tileLo = min(min(sLoMin[0], sLoMin[1]), min(sLoMin[2], sLoMin[3]));
-  const int tileEnd = max(max(sEndMax[0], sEndMax[1]), max(sEndMax[2], sEndMax[3]));
+  int tileLo = INT_MAX, tileEnd = -1;
+#pragma unroll
+  for (int w8 = 0; w8 < (PAIR ? 8 : 4); w8++) {
+    tileLo = min(tileLo, sLoMin[w8]);
+    tileEnd = max(tileEnd, sEndMax[w8]);
+  }
   const int kt0 = tileEnd >= 0 ? tileLo / BK : 0;
   const int nTiles = tileEnd >= 0 ? tileEnd / BK - kt0 + 1 : 0;
 
@@ -174,14 +304,22 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther3));
     if (warp == 8) {
       // ------------------------------ TMA producer ------------------------------
+      // In a pair every CTA loads its own Q tile and its halves of the K/V tiles into its
+      // own ring (which both CTAs walk in step: same sequence numbers, same slots); all
+      // completions are counted on the even CTA's barriers, where the byte counts expected
+      // are the pair's.
       if (lane == 0 && nTiles > 0) {
         prefetch_tensormap(&mapK);
         prefetch_tensormap(&mapV);
+        auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+          if (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
+          else tma_load_2d(dst, map, x, y, bar);
+        };
         if (!PADDED) {
           prefetch_tensormap(&mapQ);
-          mbar_expect_tx(smem_u32(&bars.fullQ), C::Q_BYTES);
+          if (leader) mbar_expect_tx(smem_u32(&bars.fullQ), C::CTAS * C::Q_BYTES);
           for (int c = 0; c < C::CHUNKS; c++)
-            tma_load_2d(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
+            load(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
         }
         const int xKV = PADDED ? ((kvh * hd) & ~7) : kvh * HD;
         int seq = 0;
@@ -193,25 +331,26 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           return ok;
         };
         auto load_k = [&](int j) {
-          const int key0 = (kt0 + j) * BK;
+          const int key0 = (kt0 + j) * BK + cta * C::K_ROWS;   // a pair: 64 keys each
           for (int part = 0; part < KP && ok; part++) {
             int slot;
             if (!slot_for(slot)) return;
             const uint32_t bar = smem_u32(&bars.full[slot]), dst = sRing + slot * C::SLOT_BYTES;
-            mbar_expect_tx(bar, C::K_CHUNKS * BK * 128);
+            if (leader) mbar_expect_tx(bar, C::CTAS * C::K_BYTES);
             for (int c = 0; c < C::K_CHUNKS; c++)
-              tma_load_2d(dst + c * (BK * 128), &mapK, xKV + (part * C::K_CHUNKS + c) * 64, key0, bar);
+              load(dst + c * (C::K_ROWS * 128), &mapK, xKV + (part * C::K_CHUNKS + c) * 64, key0, bar);
           }
         };
         auto load_v = [&](int j) {
           const int key0 = (kt0 + j) * BK;
+          const int x0 = xKV + cta * C::V_CHUNKS * 64;          // a pair: half of the columns each
           for (int part = 0; part < VP && ok; part++) {
             int slot;
             if (!slot_for(slot)) return;
             const uint32_t bar = smem_u32(&bars.full[slot]), dst = sRing + slot * C::SLOT_BYTES;
-            mbar_expect_tx(bar, C::CHUNKS * C::V_ROWS * 128);
-            for (int c = 0; c < C::CHUNKS; c++)
-              tma_load_2d(dst + c * (C::V_ROWS * 128), &mapV, xKV + c * 64, key0 + part * C::V_ROWS, bar);
+            if (leader) mbar_expect_tx(bar, C::CTAS * C::V_BYTES);
+            for (int c = 0; c < C::V_CHUNKS; c++)
+              load(dst + c * (C::V_ROWS * 128), &mapV, x0 + c * 64, key0 + part * C::V_ROWS, bar);
           }
         };
         load_k(0);
@@ -220,25 +359,27 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           if (ok) load_v(j);
         }
       }
-    } else if (warp == 9) {
+    } else if (warp == 9 && leader) {
       // ------------------------------ MMA issuer: S = Q K^T ----------------------
       // The whole warp walks the loop (waits included); the tensor-core instructions
       // run in one elected lane, which keeps their operands in uniform registers.
       if (nTiles > 0) {
-        constexpr uint32_t idescS = instr_desc(BK, false);
+        constexpr uint32_t idescS = PAIR ? instr_desc_pair(BK, false) : instr_desc(BK, false);
         constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO, version, SW128
         constexpr uint32_t kLboK = (16u >> 4) << 16;
         auto desc = [](uint32_t lo32) { return ((uint64_t)kDescHi << 32) | lo32; };
         auto wait = [&](uint64_t* bar, int parity) {
           return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), (uint32_t)parity, &sAbort)) != 0;
         };
-        const uint32_t aLo = (sQ >> 4) | kLboK;
+        // descriptors carry the 18-bit offset inside the CTA's window, not the CTA's rank bits
+        const uint32_t aLo = ((sQ & 0x3ffffu) >> 4) | kLboK;
         const int kSteps = PADDED ? (shift + hd + 15) / 16 : HD / 16;  // K = 16 per instruction
         bool ok = wait(&bars.fullQ, 0);
 #pragma unroll 1
         for (int j = 0; j < nTiles && ok; j++) {
           const int b = j & 1;
           const int s0 = seq_k<KP, VP>(j);
+          TC_TRACE(10, j);
 #pragma unroll
           for (int part = 0; part < KP; part++) {
             const int slot = (s0 + part) % NS;
@@ -250,25 +391,33 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
               ok = wait(C::P_OWN ? &bars.sFree[b] : &bars.pvDone[b], ((j >> 1) - 1) & 1);
             if (!ok) break;
             tc_fence_after_sync();
+            TC_TRACE(11, j);
             if (elect_one()) {
-              const uint32_t bLo = ((sRing + slot * C::SLOT_BYTES) >> 4) | kLboK;
+              const uint32_t bLo = (((sRing + slot * C::SLOT_BYTES) & 0x3ffffu) >> 4) | kLboK;
               constexpr int kPerPart = C::K_CHUNKS * 4;  // K = 16 steps in one part
 #pragma unroll
               for (int k2 = 0; k2 < kPerPart; k2++) {
                 const int kk = part * kPerPart + k2;
                 if (PADDED && k2 >= kSteps) break;
                 const uint32_t aOff = (kk >> 2) * ((BM * 128) >> 4) + (kk & 3) * 2;
-                const uint32_t bOff = (k2 >> 2) * ((BK * 128) >> 4) + (k2 & 3) * 2;
-                mma_f16_ss(tmem + b * BK, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
+                const uint32_t bOff = (k2 >> 2) * ((C::K_ROWS * 128) >> 4) + (k2 & 3) * 2;
+                if (PAIR) mma_f16_ss_pair(tmem + b * BK, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
+                else mma_f16_ss(tmem + b * BK, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
               }
-              tc_commit(smem_u32(&bars.empty[slot]));
-              if (part == KP - 1) tc_commit(smem_u32(&bars.sFull[b]));
+              if (PAIR) {
+                tc_commit_pair(smem_u32(&bars.empty[slot]));
+                if (part == KP - 1) tc_commit_pair(smem_u32(&bars.sFull[b]));
+              } else {
+                tc_commit(smem_u32(&bars.empty[slot]));
+                if (part == KP - 1) tc_commit(smem_u32(&bars.sFull[b]));
+              }
             }
             __syncwarp();
+            TC_TRACE(12, j);
           }
         }
       }
-    } else if (warp == 10) {
+    } else if (warp == 10 && leader) {
       // ------------------------------ MMA issuer: O += P V ------------------------
       if (nTiles > 0) {
         constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -277,7 +426,8 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         auto wait = [&](uint64_t* bar, int parity) {
           return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), (uint32_t)parity, &sAbort)) != 0;
         };
-        const uint32_t idescO = instr_desc(PADDED ? ((shift + hd + 15) & ~15) : HD, true);
+        const uint32_t idescO = PAIR ? instr_desc_pair(HD, true)
+                                     : instr_desc(PADDED ? ((shift + hd + 15) & ~15) : HD, true);
         bool ok = true;
 #pragma unroll 1
         for (int j = 0; j < nTiles && ok; j++) {
@@ -288,21 +438,32 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           for (int half = 0; half < 2; half++) {
             const int part = VP == 2 ? half : 0;
             const int slot = (s0 + part) % NS;
+            TC_TRACE(13 + 3 * half, j);
             if (VP == 2 || half == 0) ok = wait(&bars.full[slot], ((s0 + part) / NS) & 1);
+            TC_TRACE(14 + 3 * half, j);
             if (ok) ok = wait(&bars.pReady[b][half], (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after_sync();
+            TC_TRACE(15 + 3 * half, j);
             if (elect_one()) {
-              const uint32_t bLo = ((sRing + slot * C::SLOT_BYTES) >> 4) | kLboV;
+              const uint32_t bLo = (((sRing + slot * C::SLOT_BYTES) & 0x3ffffu) >> 4) | kLboV;
 #pragma unroll
               for (int k2 = 0; k2 < 4; k2++) {
                 const int kk = half * 4 + k2;              // 16 keys per step
                 const int kLocal = VP == 2 ? k2 : kk;       // within this part's rows
-                mma_f16_ts(tmem + C::O_COL, pCol + kk * 8, desc(bLo + kLocal * (2048 >> 4)), idescO,
-                           (j > 0 || kk > 0) ? 1u : 0u);
+                const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+                if (PAIR) mma_f16_ts_pair(tmem + C::O_COL, pCol + kk * 8, desc(bLo + kLocal * (2048 >> 4)), idescO, acc);
+                else mma_f16_ts(tmem + C::O_COL, pCol + kk * 8, desc(bLo + kLocal * (2048 >> 4)), idescO, acc);
               }
-              if (VP == 2 || half == 1) tc_commit(smem_u32(&bars.empty[slot]));
-              if (half == 1) tc_commit(smem_u32(&bars.pvDone[b]));
+              if (PAIR) {
+                if (half == 1) {
+                  tc_commit_pair(smem_u32(&bars.empty[slot]));
+                  tc_commit_pair(smem_u32(&bars.pvDone[b]));
+                }
+              } else {
+                if (VP == 2 || half == 1) tc_commit(smem_u32(&bars.empty[slot]));
+                if (half == 1) tc_commit(smem_u32(&bars.pvDone[b]));
+              }
             }
             __syncwarp();
           }
@@ -317,6 +478,11 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const uint32_t sCol = tmem + laneBase + g * BK;
     const uint32_t pCol = tmem + laneBase + (C::P_OWN ? C::P_COL + g * 64 : g * BK);
     const uint32_t oCol = tmem + laneBase + C::O_COL;
+    // where the MMA issuers wait for this warp: this CTA, or the even CTA of the pair
+    auto arrive = [&](uint64_t* bar) {
+      if (PAIR && !leader) mbar_arrive_cluster(smem_u32(bar) & ~kPeerBit);
+      else mbar_arrive(smem_u32(bar));
+    };
     bool ok = true;
 
     if (PADDED && nTiles > 0) {
@@ -324,15 +490,15 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       // [shift, shift + hd), zeros beside them and in rows past the end.
       const __half* qg = static_cast<const __half*>(p.q) + (int64_t)h * hd;
       for (int u = tid; u < BM * 8; u += 256) {
-        const int r = u >> 3, unit = u & 7;
+        const int r = u >> 3, unit8 = u & 7;
         const int64_t row = row0 + r;
         __align__(16) __half vals[8];
 #pragma unroll
         for (int e = 0; e < 8; e++) {
-          const int c = unit * 8 + e - shift;
+          const int c = unit8 * 8 + e - shift;
           vals[e] = (row < p.qLen && c >= 0 && c < hd) ? qg[row * p.qStride + c] : __half(0.f);
         }
-        const uint32_t addr = sQ + r * 128 + ((unit ^ (r & 7)) << 4);
+        const uint32_t addr = sQ + r * 128 + ((unit8 ^ (r & 7)) << 4);
         const uint4 v4 = *reinterpret_cast<const uint4*>(vals);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v4.x), "r"(v4.y),
                      "r"(v4.z), "r"(v4.w)
@@ -348,19 +514,23 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 #pragma unroll 1
     for (int j = g; j < nTiles && ok; j += 2) {
       const int key0 = (kt0 + j) * BK;
+      TC_TRACE(0, j);
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.sFull[g]), (j >> 1) & 1, &sAbort));
       if (!ok) break;  // the whole warp leaves together
       tc_fence_after_sync();
+      TC_TRACE(1, j);
       uint32_t sv[BK];
 #pragma unroll
       for (int c = 0; c < BK; c += 32)
         tmem_ld32(sCol + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
       tmem_wait_ld();
+      TC_TRACE(2, j);
       if (C::P_OWN) {  // S(j) is in registers: its buffer may take S(j+2)
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars.sFree[g]));
+        if (lane == 0) arrive(&bars.sFree[g]);
       }
+      TC_TRACE(20, j);
       const bool fullTile = lo <= key0 && end >= key0 + BK - 1;
       if (p.hasKeyBias) {
         const int b0 = p.biasStart - key0, b1 = p.biasEnd - key0;
@@ -387,12 +557,18 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           mx4[u] = max3(mx4[u], __uint_as_float(sv[c + 2 * u]), __uint_as_float(sv[c + 2 * u + 1]));
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
+      TC_TRACE(21, j);
 
       // ---- max phase, in tile order across the two warpgroups ----
       if (j > 0) {
+        // (an acquire load pairs with the release store below: what the other warpgroup's
+        // warp wrote before it — reference points, its rescale of O — is visible after it)
         bool arrived = false;
+        const uint32_t doneAddr = smem_u32(const_cast<int*>(&sMaxDone[w]));
         for (int i = 0; i < (1 << 22); i++) {
-          if (sMaxDone[w] >= j) { arrived = true; break; }
+          int done;
+          asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(done) : "r"(doneAddr) : "memory");
+          if (done >= j) { arrived = true; break; }
           if ((i & 63) == 63) {
             if (sAbort) break;
             __nanosleep(64);
@@ -403,9 +579,9 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           sAbort = 1;
           break;
         }
-        __threadfence_block();
         tc_fence_after_sync();
       }
+      TC_TRACE(22, j);
       float mref = sMref[rowInTile];
       if (mref != seen) {  // the other warpgroup moved the reference point since this one last looked
         l *= fast_exp2(seen - mref);
@@ -438,10 +614,12 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         sMref[rowInTile] = mnew;
       }
       __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        sMaxDone[w] = j + 1;
-      }
+      if (lane == 0)
+        asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<int*>(&sMaxDone[w]))),
+                     "r"(j + 1)
+                     : "memory");
+      TC_TRACE(3, j);
 
       // ---- exponentials, P in two halves ----
       // P's own columns were last read by P V(j-2).
@@ -450,6 +628,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                         mbar_wait(smem_u32(&bars.pvDone[g]), ((j >> 1) - 1) & 1, &sAbort));
         if (!ok) break;
       }
+      TC_TRACE(6, j);
       float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
                         make_float2(0.f, 0.f)};
       const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mref, -mref);
@@ -466,11 +645,13 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           const __half2 hp = __floats2half2_rn(pe.x, pe.y);
           pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
         }
+        TC_TRACE(7 + half, j);
         tmem_st32(pCol + half * 32, pk);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars.pReady[g][half]));
+        if (lane == 0) arrive(&bars.pReady[g][half]);
+        TC_TRACE(4 + half, j);
       }
       const float2 s01 = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
       l += s01.x + s01.y;
@@ -525,40 +706,55 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
       }
     } else if (nTiles == 0 && row < p.qLen) {
-      // no row of this tile sees a key
+      // no row of this unit sees a key
       for (int c = g * (hd / 2); c < (g + 1) * (hd / 2); c += 2)
         *reinterpret_cast<__half2*>(out + c) = __floats2half2_rn(0.f, 0.f);
     }
   }
 
-  // Common exit: every role arrives here, then the allocating warp frees TMEM.
+  // Common exit: every role arrives here, then the allocating warp frees TMEM.  In a pair
+  // neither CTA leaves while the other may still read its shared memory or signal it.
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();
   if (tid == 0 && sAbort) atomicOr(status, kStatusWaitTimeout);
   if (warp == 9) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, C::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem, C::TMEM_COLS);
+    else tmem_dealloc(tmem, C::TMEM_COLS);
   }
 }
 
-template <int HD, bool PADDED>
+template <int HD, bool PADDED, bool PAIR>
 cudaError_t launch3(const AttnParams& p, int* status, cudaStream_t s, std::string* err) {
-  using C = Cfg3<HD>;
+  using C = Cfg3<HD, PAIR>;
   CUtensorMap mq, mk, mv;
   // The narrow-head form reads Q with plain loads; its K/V maps span the real columns,
   // so a box that runs past the last head reads zeros there.
   const int64_t qCols = (int64_t)p.qHeads * p.hd, kvCols = (int64_t)p.kvHeads * p.hd;
   if ((!PADDED && !make_map(&mq, p.q, p.qLen, qCols, p.qStride, BM, err)) ||
-      !make_map(&mk, p.k, p.kvLen, kvCols, p.kvStride, BK3, err) ||
+      !make_map(&mk, p.k, p.kvLen, kvCols, p.kvStride, C::K_ROWS, err) ||
       !make_map(&mv, p.v, p.kvLen, kvCols, p.kvStride, C::V_ROWS, err))
     return cudaErrorInvalidValue;
   if (PADDED) mq = mk;  // unused by the kernel; a valid map all the same
-  auto kern = prefill_tc3_kernel<HD, PADDED>;
+  auto kern = prefill_tc3_kernel<HD, PADDED, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   if (e != cudaSuccess) return e;
-  dim3 grid((unsigned)((p.qLen + BM - 1) / BM), (unsigned)p.qHeads);
-  kern<<<grid, kThreads3, C::SMEM, s>>>(mq, mk, mv, p, status);
-  return cudaGetLastError();
+  const unsigned tiles = (unsigned)((p.qLen + BM - 1) / BM);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((tiles + C::CTAS - 1) / C::CTAS * C::CTAS, (unsigned)p.qHeads);
+  cfg.blockDim = dim3(kThreads3);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = C::CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PAIR ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, p, status);
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
@@ -579,13 +775,24 @@ bool prefill_tc3_supported(const AttnParams& p, int dtype) {
   return true;
 }
 
-cudaError_t launch_prefill_tc3(const AttnParams& p, int* status, cudaStream_t s, std::string* err) {
-  switch (p.hd) {
-    case 64: return launch3<64, false>(p, status, s, err);
-    case 128: return launch3<128, false>(p, status, s, err);
-    case 256: return launch3<256, false>(p, status, s, err);
+// Pairs of CTAs need two row tiles of the same head and one of the head sizes whose V tile
+// splits into 64-column chunks.
+bool prefill_tc3_pair_supported(const AttnParams& p, int dtype) {
+  return prefill_tc3_supported(p, dtype) && (p.hd == 128 || p.hd == 256) && p.qLen > BM;
+}
+
+cudaError_t launch_prefill_tc3(const AttnParams& p, bool pair, int* status, cudaStream_t s,
+                               std::string* err) {
+  if (pair) {
+    return p.hd == 128 ? launch3<128, false, true>(p, status, s, err)
+                       : launch3<256, false, true>(p, status, s, err);
   }
-  return launch3<64, true>(p, status, s, err);
+  switch (p.hd) {
+    case 64: return launch3<64, false, false>(p, status, s, err);
+    case 128: return launch3<128, false, false>(p, status, s, err);
+    case 256: return launch3<256, false, false>(p, status, s, err);
+  }
+  return launch3<64, true, false>(p, status, s, err);
 }
 
 }  // namespace rt

@@ -18,14 +18,16 @@ namespace tc {
 // (0,0) stores (clock, tag, index) records into its own slice of a device buffer
 // (plain stores, no atomics, so the timeline is barely disturbed).
 #ifdef RT_TC_TRACE
-constexpr int kTraceWarps = 16, kTracePerWarp = 1024;
+constexpr int kTraceWarps = 32, kTracePerWarp = 1024;
 __device__ long long gTraceBuf[kTraceWarps * kTracePerWarp * 2];
 #define TC_TRACE_DECL int traceSeq_ = 0;
+// CTAs (0,0) and (1,0): the second one's warps use slots 16 and up.
 #define TC_TRACE(tag, idx)                                                                  \
   do {                                                                                      \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 &&                    \
+    if (blockIdx.x <= 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 &&                    \
         traceSeq_ < kTracePerWarp) {                                                        \
-      long long* r_ = gTraceBuf + ((threadIdx.x >> 5) * kTracePerWarp + traceSeq_++) * 2;   \
+      long long* r_ = gTraceBuf +                                                           \
+          ((blockIdx.x * 16 + (threadIdx.x >> 5)) * kTracePerWarp + traceSeq_++) * 2;       \
       r_[0] = clock64();                                                                    \
       r_[1] = (long long)(tag)*100000 + (idx) + 1;                                          \
     }                                                                                       \
@@ -38,7 +40,13 @@ __device__ long long gTraceBuf[kTraceWarps * kTracePerWarp * 2];
 #endif
 
 constexpr int BM = 128;                   // query rows per MMA tile (= TMEM lanes)
-constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale O when a row max grew by 2^8
+// log2 units: the accumulator is rescaled when a row's maximum has grown this far past
+// its reference point.  P = 2^(s - reference) is stored as f16, so 2^threshold must stay
+// below 65504; f16 keeps its relative precision over that whole range.
+#ifndef RT_RESCALE_THRESHOLD
+#define RT_RESCALE_THRESHOLD 13
+#endif
+constexpr float kRescaleThreshold = (float)RT_RESCALE_THRESHOLD;
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

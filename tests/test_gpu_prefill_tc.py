@@ -68,15 +68,15 @@ def test_tensor_core_prefill_against_oracle(one_tile, name, c):
     check_sdpa(one_tile, c, "f16", route="prefill_tc")
 
 
-def test_default_routing_between_the_two_tensor_core_kernels(ex):
-    """Two query tiles per block only on grids of several waves (6 blocks per SM)."""
+def test_default_routing_among_the_tensor_core_kernels(ex):
+    """Head sizes up to 128 take the alternating-warpgroup kernel whatever the grid;
+    head size 256 stays on the one-tile kernel."""
     small = _c(qLen=1000, kvLen=1000, qHeads=2, kvHeads=1, headDim=128, windowRight=0)
-    check_sdpa(ex, small, "f16", route="prefill_tc")
-    # 9 row pairs x 128 heads = 1152 blocks >= 6 x 148
+    check_sdpa(ex, small, "f16", route="prefill_tc3")
     big = _c(qLen=2304, kvLen=2304, qHeads=128, kvHeads=8, headDim=64, windowLeft=64, windowRight=0)
-    check_sdpa(ex, big, "f16", route="prefill_tc2")
+    check_sdpa(ex, big, "f16", route="prefill_tc3")
     check_sdpa(ex, big.with_(headDim=256, qHeads=32, kvHeads=8, qLen=512, kvLen=512), "f16",
-               route="prefill_tc")       # head size 256 needs all of TMEM for one tile
+               route="prefill_tc")
 
 
 @pytest.mark.parametrize("hd", [64, 128, 256])
@@ -92,6 +92,7 @@ def test_matches_the_fp32_pipe_kernel(ex):
     c = _c(qLen=900, kvLen=900, qHeads=4, kvHeads=2, headDim=128, windowLeft=400, windowRight=0,
            sinks=True)
     x = make_inputs(c, "f16")
+    ex.setOption(OPT_PREFILL_TC, 2)
     tc = run_sdpa(ex, x)
     assert ex.dispatches[-1] == "prefill_tc"
     ex.setOption(OPT_PREFILL_TC, 3)
@@ -176,7 +177,7 @@ def test_greedy_packed_batch_of_ragged_sequences(ex, hd, heads, kvHeads, wl, wr,
         at += n
     x.segs = segs
     got = run_sdpa(ex, x)
-    assert ex.dispatches[-1] == "prefill_tc"
+    assert ex.dispatches[-1] == ("prefill_tc" if hd == 256 else "prefill_tc3")
     want = oracle.sdpa_ref_inputs(x)
     oracle.assert_close(got, want, "f16")
     assert (got.reshape(T, -1)[at:] == 0).all()

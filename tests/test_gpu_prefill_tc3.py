@@ -178,3 +178,59 @@ def test_greedy_packed_batch_of_ragged_sequences(alt, hd, heads, kvHeads, wl, wr
     want = oracle.sdpa_ref_inputs(x)
     oracle.assert_close(got, want, "f16")
     assert (got.reshape(T, -1)[at:] == 0).all()
+
+
+# ---- pairs of CTAs sharing every K/V tile (head sizes 128 and 256) -------------------
+
+@pytest.fixture
+def pair(ex):
+    from runntime_b200._lib import OPT_PREFILL_TC
+    ex.setOption(OPT_PREFILL_TC, 5)
+    yield ex
+    ex.setOption(OPT_PREFILL_TC, 1)
+
+
+def _pair_ok(c):
+    return c.headDim in (128, 256) and c.qLen > 128
+
+
+PAIRED = {n: c for n, c in ALL.items() if _pair_ok(c)}
+PAIRED.update({
+    "odd_number_of_row_tiles": _c(qLen=640, kvLen=640, qHeads=2, kvHeads=1, headDim=128,
+                                  windowRight=0),
+    "second_tile_of_the_pair_is_empty": _c(qLen=256, kvLen=100, qHeads=1, kvHeads=1, headDim=128,
+                                           windowLeft=0, windowRight=INF),
+    "gqa_3to1_hd256_sliding_2048": _c(qLen=2048, kvLen=2048, qHeads=3, kvHeads=1, headDim=256,
+                                      windowLeft=512, windowRight=512),
+    "causal_3000_hd128_gqa": _c(qLen=3000, kvLen=3000, qHeads=4, kvHeads=2, headDim=128,
+                                windowRight=0, sinks=True),
+})
+
+
+@pytest.mark.parametrize("name", sorted(PAIRED))
+def test_pairs_against_oracle(pair, name):
+    check_sdpa(pair, PAIRED[name], "f16", route="prefill_tc3_pair")
+
+
+@pytest.mark.parametrize("hd", [128, 256])
+def test_every_option_in_pairs(pair, hd):
+    for name, c in cases.option_cases(300, hd):
+        if c.packed and hd > 128:
+            continue
+        check_sdpa(pair, c, "f16", route="prefill_tc3_pair")
+
+
+def test_growing_scores_in_pairs(pair):
+    import runntime_b200 as rt
+    T, hd = 1100, 128
+    rng = np.random.default_rng(1)
+    q = np.ones((T, hd), np.float32) * 0.125
+    k = (np.arange(T, dtype=np.float32)[:, None] / 16.0 * np.ones((1, hd), np.float32)) / 4
+    k = oracle.round_f16(k.astype(np.float32))
+    v = oracle.round_f16(rng.standard_normal((T, hd)).astype(np.float32))
+    opts = dict(qHeads=1, kvHeads=1, headDim=hd, windowLeft=INF, windowRight=INF)
+    out = rt.toArray(rt.sdpa(pair.upload(q, [T, hd], "f16"), pair.upload(k, [T, hd], "f16"),
+                             pair.upload(v, [T, hd], "f16"), opts), pair)
+    assert pair.dispatches[-1] == "prefill_tc3_pair"
+    want = oracle.sdpa_ref(q, k, v, qHeads=1, kvHeads=1, headDim=hd)
+    oracle.assert_close(out, want, "f16")
