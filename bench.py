@@ -269,6 +269,8 @@ class Decode:
         if cfg["cross"]:
             self.ck = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
             self.cv = torch.randn(nb, cfg["cross"], w, generator=gd, device=dev, dtype=torch.float16)
+            self.q2 = (torch.randn(nb, cfg["qHeads"] * hd, generator=gd, device=dev)
+                       * hd ** -0.5).to(torch.float16)      # the cross-attention's own projection
             self.out2 = torch.empty_like(self.q)
         # KV rows split over ranks: the partials are traded through peer memory by the decode
         # kernel itself (--exchange peer, the default; the peers' blocks mapped through the
@@ -319,9 +321,6 @@ class Decode:
             total = total * self.rows / c["cacheRows"]
         return float(total)
 
-    def launches_per_step(self):
-        n = 1 + (1 if self.cfg["cross"] else 0)
-        return n + (1 if (self.sharded or self.peer) else 0)
 
     def step(self, layer=0):
         from runntime_b200.engine import decode_batched
@@ -341,12 +340,17 @@ class Decode:
                               partials=self.partials, kvLens=self.lens, kvLen=c["cacheRows"],
                               kNew=self.kNew, vNew=self.vNew, shardStart=self.shardStart, **common)
             return
+        # self-attention with the append and, where the step has one, the cross-attention
+        # over the encoder states: one launch
+        second = None
+        if c["cross"]:
+            from runntime_b200.engine import second_attention
+            second = second_attention(self.q2, self.out2, self.ck, self.cv, cacheRows=c["cross"],
+                                      qHeads=c["qHeads"], kvHeads=c["kvHeads"], headDim=c["hd"],
+                                      kvLen=c["cross"])
         decode_batched(self.ex, self.q, self.out, self.k, self.v, cacheRows=self.rows,
                        kvLen=max(self.lens_all), kvLens=self.lens, kNew=self.kNew, vNew=self.vNew,
-                       splits=int(os.environ.get("RT_BENCH_SPLITS", "0")), **common)
-        if c["cross"]:
-            decode_batched(self.ex, self.q, self.out2, self.ck, self.cv, cacheRows=c["cross"],
-                           kvLen=c["cross"], **common)
+                       splits=int(os.environ.get("RT_BENCH_SPLITS", "0")), second=second, **common)
 
     def verify(self):
         """One step, then a few sequences against the f64 oracle over their whole caches
@@ -395,7 +399,7 @@ class Decode:
             ok &= bool(np.all(err <= tol["atol"] + tol["rtol"] * np.abs(want)))
             n += 1
             if c["cross"]:
-                want = oracle.sdpa_ref(self.q[b:b + 1].float().cpu().numpy(),
+                want = oracle.sdpa_ref(self.q2[b:b + 1].float().cpu().numpy(),
                                        self.ck[b].float().cpu().numpy(), self.cv[b].float().cpu().numpy(),
                                        qHeads=H, kvHeads=c["kvHeads"], headDim=hd).reshape(-1)
                 err = np.abs(self.out2[b].float().cpu().numpy() - want)
@@ -651,6 +655,25 @@ def timed(torch, dist, world, fn, steps, warmup, flush=None, min_warm_s=0.0, min
     return total, total_steps, warm
 
 
+def bind_to_gpu_numa_node(index):
+    """Runs this rank on the host cores next to its GPU (as the driver's topology reports
+    them), before any pinned host buffer is allocated: with several ranks streaming inputs
+    from host memory at once, buffers that the first-touch policy placed on the other
+    socket halve the host-to-device rate.  Only reads the topology; changes nothing on the
+    GPU.  Any failure leaves the process where it was."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, mask in enumerate(words) for b in range(64) if (mask >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception as e:  # noqa: BLE001 - placement is an optimisation only
+        sys.stderr.write(f"no NUMA placement for GPU {index}: {type(e).__name__}: {e}\n")
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -662,10 +685,15 @@ def run_gpu(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local)
+    # This program's stdout is one JSON line.  Libraries that write banners to file
+    # descriptor 1 (NCCL's version line) get stderr instead; the line goes to the real one.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if world > 1:
-        # NCCL's version banner goes to stdout; this program's stdout is one JSON line.
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
+        bind_to_gpu_numa_node(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = rt.CudaExecutor(local)
     ex.setStream(torch.cuda.current_stream().cuda_stream)
@@ -857,7 +885,8 @@ def run_gpu(args):
                 v, cores, desc, _ = cpu_sample("c4", budget_s=6.0)
                 line["decode"]["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores,
                                                   "kind": "port", "sample": desc}
-        print(json.dumps(line), flush=True)
+        real_stdout.write(json.dumps(line) + "\n")
+        real_stdout.flush()
     ex.dispose()
     if world > 1:
         dist.destroy_process_group()

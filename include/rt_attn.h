@@ -229,6 +229,25 @@ typedef struct {
                                       merge only (for callers that put other work in between) */
 } rt_exchange;
 
+/* A second attention computed by the same launch: the cross-attention over the encoder
+ * states that follows the self-attention of a decoder layer (packages/runntime/src/zoo/
+ * moonshine/decoder.ts:58-76 then :105-109) — its own query rows, output, caches and
+ * lengths; no append and no rope; heads, head size, dtype and sinks are the call's. */
+typedef struct {
+  const void* q;          /* device [batch, qHeads*headDim] */
+  void* out;              /* device [batch, qHeads*headDim] */
+  void* kCache;           /* device slab, or NULL with kCachePtrs */
+  void* vCache;
+  const void* const* kCachePtrs; /* device [batch] of device pointers, or NULL */
+  const void* const* vCachePtrs;
+  const int32_t* kvLens;  /* device [batch] or NULL */
+  int64_t cacheSeqStride; /* elements between the sequences' caches (slab form) */
+  int64_t qRowStride;     /* elements between q rows; 0 = dense */
+  int32_t cacheRows;
+  int32_t kvLen;          /* used when kvLens == NULL */
+  int32_t windowLeft;     /* RT_WINDOW_INF for cross-attention */
+} rt_decode_second;
+
 typedef struct {
   const void* q;          /* device [batch, qHeads*headDim] */
   void* out;              /* device [batch, qHeads*headDim] (unused with partialsOut) */
@@ -264,6 +283,15 @@ typedef struct {
    * same q, kNew, vNew and lengths.  ropeByPosition uses the global position. */
   int32_t kvSharded;
   int32_t shardStart;
+  /* Per-sequence caches: device arrays [batch] of device pointers, each to one sequence's
+   * [cacheRows, kvHeads*headDim] cache — separately allocated caches, as the reference's
+   * per-sequence, per-layer K and V tensors are (transcriber.ts:111-118) — instead of the
+   * slab (kCache / vCache / cacheSeqStride are then ignored).  Each cache must start on a
+   * 16-byte boundary; one that does not makes its sequence come out as zeros and rt_sync
+   * report it. */
+  const void* const* kCachePtrs;
+  const void* const* vCachePtrs;
+  const rt_decode_second* second; /* host pointer or NULL: a second attention, same launch */
 } rt_decode_args;
 
 RT_API int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* args);

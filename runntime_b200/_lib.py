@@ -48,6 +48,16 @@ class Exchange(C.Structure):
     ]
 
 
+class DecodeSecond(C.Structure):
+    """rt_decode_second: a second attention (cross-attention) in the same decode launch."""
+    _fields_ = [
+        ("q", C.c_void_p), ("out", C.c_void_p), ("kCache", C.c_void_p), ("vCache", C.c_void_p),
+        ("kCachePtrs", C.c_void_p), ("vCachePtrs", C.c_void_p), ("kvLens", C.c_void_p),
+        ("cacheSeqStride", C.c_int64), ("qRowStride", C.c_int64),
+        ("cacheRows", C.c_int32), ("kvLen", C.c_int32), ("windowLeft", C.c_int32),
+    ]
+
+
 class DecodeArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("out", C.c_void_p), ("kCache", C.c_void_p), ("vCache", C.c_void_p),
@@ -61,6 +71,8 @@ class DecodeArgs(C.Structure):
         ("qRowStride", C.c_int64), ("kNewRowStride", C.c_int64), ("vNewRowStride", C.c_int64),
         ("exchange", C.POINTER(Exchange)),
         ("kvSharded", C.c_int32), ("shardStart", C.c_int32),
+        ("kCachePtrs", C.c_void_p), ("vCachePtrs", C.c_void_p),
+        ("second", C.POINTER(DecodeSecond)),
     ]
 
 

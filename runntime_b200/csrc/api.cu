@@ -223,8 +223,9 @@ int run_decode(rt_ctx* ctx, rt::DecodeParams& p, int dtype) {
     return fail(ctx, RT_INVALID_ARGUMENT, "%s", err.c_str());
   const int zBlocks = (p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
   if (p.splits > 1) {
-    const size_t bytes = (size_t)p.batch * p.splits * p.qHeads * (2 + p.hd) * sizeof(float);
-    int s = ensure_scratch(ctx, bytes, (size_t)p.batch * zBlocks);
+    const size_t sets = p.hasSecond ? 2 : 1;   // a second attention has its own partials and counters
+    const size_t bytes = sets * p.batch * p.splits * p.qHeads * (2 + p.hd) * sizeof(float);
+    int s = ensure_scratch(ctx, bytes, sets * p.batch * zBlocks);
     if (s != RT_OK) return s;
   }
   p.scratch = ctx->scratch;
@@ -341,7 +342,8 @@ int rt_sync(rt_ctx* ctx) {
                 "a kernel reported status 0x%x (%s)", status,
                 (status & rt::kStatusWaitTimeout)
                     ? "a bounded device-side wait ran out"
-                    : "a device-side length exceeds its buffer (kvLens entry past cacheRows)");
+                    : "a device-side length exceeds its buffer (kvLens entry past cacheRows) or a "
+                      "per-sequence cache pointer is not 16-byte aligned");
   }
   return RT_OK;
 }
@@ -463,7 +465,8 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
 int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
   RT_ENTER(ctx);
   if (!a) return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: args is NULL");
-  if (!a->q || !a->kCache || !a->vCache || (!a->out && !a->partialsOut))
+  if (!a->q || (!a->kCache && !a->kCachePtrs) || (!a->vCache && !a->vCachePtrs) ||
+      (!a->out && !a->partialsOut))
     return fail(ctx, RT_INVALID_ARGUMENT,
                 "rt_attn_decode: q, kCache, vCache and out (or partialsOut) must be device pointers");
   if (a->dtype != RT_F32 && a->dtype != RT_F16)
@@ -497,7 +500,8 @@ int rt_attn_decode(rt_ctx* ctx, const rt_decode_args* a) {
     return fail(ctx, RT_INVALID_ARGUMENT, "rt_attn_decode: splits %d out of range [0, 64]",
                 a->splits);
   if (a->cacheSeqStride < 0 ||
-      (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim))
+      (!a->kCachePtrs && a->batch > 1 &&
+       a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim))
     return fail(ctx, RT_INVALID_ARGUMENT,
                 "rt_attn_decode: cacheSeqStride %lld is smaller than one cache",
                 (long long)a->cacheSeqStride);

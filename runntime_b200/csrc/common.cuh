@@ -71,6 +71,21 @@ __device__ __forceinline__ void row_band(const AttnParams& p, int64_t row, int64
   }
 }
 
+// A second attention computed by the same decode launch (the cross-attention that follows
+// the self-attention of a decoder layer): its own q, out, caches and lengths; no append, no
+// rope; same heads, head size, dtype and sinks.
+struct DecodeSecond {
+  const void* q;
+  void* out;
+  void* kCache;
+  void* vCache;
+  const void* const* kPtrs;
+  const void* const* vPtrs;
+  const int32_t* kvLens;
+  int64_t cacheSeqStride, qRowStride;
+  int32_t cacheRows, kvLen, wl;
+};
+
 struct DecodeParams {
   const void* q;
   void* out;
@@ -109,6 +124,12 @@ struct DecodeParams {
   // KV-sequence sharding with append: this cache holds global rows [shardStart,
   // shardStart + cacheRows) of every sequence and kvLens are global lengths
   int32_t kvSharded, shardStart;
+  // per-sequence cache pointers (device arrays [batch]) instead of one slab; NULL = slab
+  const void* const* kPtrs;
+  const void* const* vPtrs;
+  // a second attention in the same launch: blockIdx.y in [batch, 2*batch)
+  int32_t hasSecond;
+  DecodeSecond s2;
 };
 
 // Who merges which sequences in the cross-GPU exchange: contiguous blocks balanced to within
@@ -175,6 +196,25 @@ inline void decode_params_from_args(const rt_decode_args& a, DecodeParams& p) {
   }
   p.kvSharded = a.kvSharded;
   p.shardStart = a.shardStart;
+  p.kPtrs = a.kCachePtrs;
+  p.vPtrs = a.vCachePtrs;
+  p.hasSecond = 0;
+  if (a.second) {
+    const rt_decode_second& x = *a.second;
+    p.hasSecond = 1;
+    p.s2.q = x.q;
+    p.s2.out = x.out;
+    p.s2.kCache = x.kCache;
+    p.s2.vCache = x.vCache;
+    p.s2.kPtrs = x.kCachePtrs;
+    p.s2.vPtrs = x.vCachePtrs;
+    p.s2.kvLens = x.kvLens;
+    p.s2.cacheSeqStride = x.cacheSeqStride;
+    p.s2.qRowStride = x.qRowStride ? x.qRowStride : (int64_t)a.qHeads * a.headDim;
+    p.s2.cacheRows = x.cacheRows;
+    p.s2.kvLen = x.kvLens ? (x.kvLen > 0 ? x.kvLen : x.cacheRows) : x.kvLen;
+    p.s2.wl = x.windowLeft;
+  }
 }
 
 // What is wrong with the rope / stride fields of decode arguments, or NULL.
@@ -196,6 +236,23 @@ inline const char* decode_rope_args_error(const rt_decode_args& a) {
     if (x.phases < 0 || x.phases > 3) return "exchange: phases must be 0..3";
     for (int r = 0; r < x.world; r++)
       if (!x.partials[r] || !x.flags[r]) return "exchange: a peer buffer is NULL";
+  }
+  if ((a.kCachePtrs == nullptr) != (a.vCachePtrs == nullptr)) return "kCachePtrs and vCachePtrs go together";
+  if (a.second) {
+    const rt_decode_second& x = *a.second;
+    if (a.exchange || a.partialsOut || a.kvSharded)
+      return "second: not with the cross-GPU exchange, partialsOut or a sharded cache";
+    if (!x.q || !x.out || (!x.kCache && !x.kCachePtrs) || (!x.vCache && !x.vCachePtrs))
+      return "second: q, out and the caches must be device pointers";
+    if ((x.kCachePtrs == nullptr) != (x.vCachePtrs == nullptr)) return "second: kCachePtrs and vCachePtrs go together";
+    if (x.cacheRows < 1 || x.kvLen < 0 || x.kvLen > x.cacheRows || (!x.kvLens && x.kvLen < 1))
+      return "second: kvLen must lie within cacheRows";
+    if (x.windowLeft < 0 || x.windowLeft > RT_WINDOW_INF) return "second: windowLeft must be a non-negative integer or Infinity";
+    if (x.cacheSeqStride < 0 || (!x.kCachePtrs && a.batch > 1 &&
+                                 x.cacheSeqStride < (int64_t)x.cacheRows * a.kvHeads * a.headDim))
+      return "second: cacheSeqStride is smaller than one cache";
+    if (x.qRowStride < 0 || (x.qRowStride && x.qRowStride < (int64_t)a.qHeads * a.headDim))
+      return "second: qRowStride is smaller than one q row";
   }
   if (a.kvSharded != 0 && a.kvSharded != 1) return "kvSharded must be 0 or 1";
   if (a.shardStart < 0 || (!a.kvSharded && a.shardStart != 0))

@@ -300,11 +300,23 @@ decode_kernel(const DecodeParams p) {
 
   const int tid = threadIdx.x;
   const int split = blockIdx.x, zb = blockIdx.z;
-  int b = blockIdx.y;
+  const int by = blockIdx.y;   // unique per (attention, sequence): indexes scratch and counters
+  int b = by;
   if (p.xWorld > 1) {   // the sequences this rank merges itself come last
     b += p.xRot;
     if (b >= p.batch) b -= p.batch;
   }
+  // The second attention of the launch (cross-attention) takes blocks [batch, 2*batch).
+  const bool sec = p.hasSecond && by >= p.batch;
+  if (sec) b = by - p.batch;
+  const void* aQ = sec ? p.s2.q : p.q;
+  void* aOut = sec ? p.s2.out : p.out;
+  const int32_t* aLens = sec ? p.s2.kvLens : p.kvLens;
+  const int64_t aSeqStride = sec ? p.s2.cacheSeqStride : p.cacheSeqStride;
+  const int64_t aQStride = sec ? p.s2.qRowStride : p.qRowStride;
+  const int aCacheRows = sec ? p.s2.cacheRows : p.cacheRows;
+  const int aKvLen = sec ? p.s2.kvLen : p.kvLen;
+  const int aWl = sec ? p.s2.wl : p.wl;
   const int hd = p.hd;
   const int group = p.qHeads / p.kvHeads;
   const int kvh0 = zb * p.kvPerCta;
@@ -331,12 +343,22 @@ decode_kernel(const DecodeParams p) {
   // L: visible rows of this cache; Lg: the sequence's length (the two differ only when the
   // cache is one rank's shard of the sequence).
   int64_t lo, end, L = 0, Lg = 0;
-  bool hasNew = p.kNew != nullptr;
+  bool hasNew = p.kNew != nullptr && !sec;
+  // This sequence's caches: its slice of the slab, or its own allocation.
+  const void* const* kPtrs = sec ? p.s2.kPtrs : p.kPtrs;
+  const void* const* vPtrs = sec ? p.s2.vPtrs : p.vPtrs;
+  const T* kSeq = kPtrs ? static_cast<const T*>(kPtrs[b])
+                        : static_cast<const T*>(sec ? p.s2.kCache : p.kCache) + (int64_t)b * aSeqStride;
+  const T* vSeq = vPtrs ? static_cast<const T*>(vPtrs[b])
+                        : static_cast<const T*>(sec ? p.s2.vCache : p.vCache) + (int64_t)b * aSeqStride;
+  // (a separately allocated cache is only known here: the bulk copies need 16-byte alignment)
+  const bool misaligned = kPtrs && BULK &&
+                          ((reinterpret_cast<uintptr_t>(kSeq) | reinterpret_cast<uintptr_t>(vSeq)) & 15u);
   if (p.useRange) {
     lo = p.lo;
     end = p.end;
   } else {
-    Lg = L = p.kvLens ? p.kvLens[b] : p.kvLen;
+    Lg = L = aLens ? aLens[b] : aKvLen;
     if (p.kvSharded) {
       // This cache holds rows [shardStart, shardStart + cacheRows) of the sequence: it sees
       // what falls inside, and takes the appended row (global row Lg-1) only if that is one
@@ -344,16 +366,17 @@ decode_kernel(const DecodeParams p) {
       const int64_t local = Lg - p.shardStart;
       hasNew = hasNew && local >= 1 && local <= p.cacheRows;
       L = local < 0 ? 0 : local > p.cacheRows ? p.cacheRows : local;
-    } else if (L > p.cacheRows) {
+    } else if (L > aCacheRows || misaligned) {
       // A length past the cache's capacity (the host checks only the scalar kvLen; this one
       // lives on the device): writeRows would refuse it ('rows exceed dst capacity').  The
       // sequence is treated as empty — nothing appended, nothing read, zeros out — and the
-      // status word reports it.
+      // status word reports it.  The same for a cache pointer the bulk copies cannot take.
       if (tid == 0) atomicOr(p.status, kStatusBadState);
       Lg = L = 0;
+      hasNew = false;
     }
     end = L - 1;
-    lo = Lg - 1 - p.wl - p.shardStart;
+    lo = Lg - 1 - aWl - p.shardStart;
     if (lo < 0) lo = 0;
     if (hasNew) end -= 1;  // row L-1 is the appended one, taken from kNew/vNew
     if (L <= 0) { lo = 1; end = -1; }
@@ -365,8 +388,8 @@ decode_kernel(const DecodeParams p) {
   if (s1 > end + 1) s1 = end + 1;
   const int ntiles = s1 > s0 ? (int)((s1 - s0 + KS - 1) / KS) : 0;
 
-  const T* kBase = static_cast<const T*>(p.kCache) + (int64_t)b * p.cacheSeqStride + kvh0 * hd;
-  const T* vBase = static_cast<const T*>(p.vCache) + (int64_t)b * p.cacheSeqStride + kvh0 * hd;
+  const T* kBase = kSeq + kvh0 * hd;
+  const T* vBase = vSeq + kvh0 * hd;
 
   // Shared-memory carve-up: [q][appended K, V slices][ring: stages x (K tile, V tile)];
   // the ring is reused for the slot merge at the end.
@@ -442,8 +465,8 @@ decode_kernel(const DecodeParams p) {
   // writeRows would do) and is attended from shared memory after the cache keys.
   const bool appendHere = hasNew && split == 0 && !p.useRange && L >= 1;
   const float* qv = sQ + hl * QS;
-  const T* qg = static_cast<const T*>(p.q) + (int64_t)b * p.qRowStride;
-  const bool roped = p.ropeCos != nullptr && !p.useRange;
+  const T* qg = static_cast<const T*>(aQ) + (int64_t)b * aQStride;
+  const bool roped = p.ropeCos != nullptr && !p.useRange && !sec;
   const int64_t ropeRow = p.ropeByPos ? (Lg >= 1 ? Lg - 1 : 0) : b;
   const float* rc = roped ? p.ropeCos + ropeRow * hd : nullptr;
   const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
@@ -669,12 +692,12 @@ decode_kernel(const DecodeParams p) {
         for (int x = slot; x < wd; x += KS) dst[2 + col0 + x] = o[c++];
       } else {
         const float invL = L > 0.f ? 1.f / L : 0.f;
-        T* dst = static_cast<T*>(p.out) + ((int64_t)b * p.qHeads + h) * hd + col0;
+        T* dst = static_cast<T*>(aOut) + ((int64_t)b * p.qHeads + h) * hd + col0;
         int c = 0;
         for (int x = slot; x < wd; x += KS) dst[x] = from_f32<T>(o[c++] * invL);
       }
     } else {
-      float* dst = p.scratch + (((int64_t)b * p.splits + split) * p.qHeads + h) * stride;
+      float* dst = p.scratch + (((int64_t)by * p.splits + split) * p.qHeads + h) * stride;
       if (slot == 0 && sub == 0) {
         dst[0] = M;
         dst[1] = L;
@@ -692,14 +715,14 @@ decode_kernel(const DecodeParams p) {
   __threadfence();
   named_barrier_sync(1, kConsumers);
   if (tid == 0) {
-    const unsigned old = atomicAdd(&p.counters[b * gridDim.z + zb], 1u);
+    const unsigned old = atomicAdd(&p.counters[by * gridDim.z + zb], 1u);
     sIsLast = (old == (unsigned)p.splits - 1);
   }
   named_barrier_sync(1, kConsumers);
   if (!sIsLast) return;
   __threadfence();
   if (active) {
-    const float* base = p.scratch + ((int64_t)b * p.splits * p.qHeads + h) * stride;
+    const float* base = p.scratch + ((int64_t)by * p.splits * p.qHeads + h) * stride;
     const int64_t ss = (int64_t)p.qHeads * stride;  // between splits
     float M = kNegSeed;
     for (int s = 0; s < p.splits; s++) M = fmaxf(M, __ldcg(base + s * ss));
@@ -716,7 +739,7 @@ decode_kernel(const DecodeParams p) {
       if (toPartials)
         partialsOut[((int64_t)b * p.qHeads + h) * stride + 2 + x] = o;
       else
-        static_cast<T*>(p.out)[((int64_t)b * p.qHeads + h) * hd + x] = from_f32<T>(o * invL);
+        static_cast<T*>(aOut)[((int64_t)b * p.qHeads + h) * hd + x] = from_f32<T>(o * invL);
     }
     if (toPartials && slot == 0 && sub == 0) {
       float* dst = partialsOut + ((int64_t)b * p.qHeads + h) * stride;
@@ -724,7 +747,7 @@ decode_kernel(const DecodeParams p) {
       dst[1] = L;
     }
   }
-  if (tid == 0) p.counters[b * gridDim.z + zb] = 0;  // ready for the next launch
+  if (tid == 0) p.counters[by * gridDim.z + zb] = 0;  // ready for the next launch
   if (p.xWorld > 0) exchange_rows(p, b, hqReal, kvh0 * group, tid, epoch, gridDim.z);
 }
 
@@ -751,8 +774,13 @@ bool bulk_ok(const DecodeParams& p, int esize) {
   if (!exact_hd(p.hd)) return false;
   const int64_t rowBytes = (int64_t)p.kvHeads * p.hd * esize;
   const int64_t sliceBytes = (int64_t)p.kvPerCta * p.hd * esize;
-  if (rowBytes % 16 || sliceBytes % 16 || (p.cacheSeqStride * esize) % 16) return false;
-  if (!aligned16(p.kCache) || !aligned16(p.vCache)) return false;
+  if (rowBytes % 16 || sliceBytes % 16) return false;
+  // (separately allocated caches are checked by the kernel, sequence by sequence)
+  if (!p.kPtrs && ((p.cacheSeqStride * esize) % 16 || !aligned16(p.kCache) || !aligned16(p.vCache)))
+    return false;
+  if (p.hasSecond && !p.s2.kPtrs &&
+      ((p.s2.cacheSeqStride * esize) % 16 || !aligned16(p.s2.kCache) || !aligned16(p.s2.vCache)))
+    return false;
   if (p.kvHeads % p.kvPerCta) return false;  // a ragged last block changes the slice size
   return true;
 }
@@ -763,7 +791,7 @@ cudaError_t launch_one(const DecodeParams& p, size_t smem, cudaStream_t s) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int zBlocks = (p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
-  dim3 grid(p.splits, p.batch, zBlocks);
+  dim3 grid(p.splits, p.batch * (p.hasSecond ? 2 : 1), zBlocks);
   kern<<<grid, BULK ? kConsumers + 32 : kConsumers, smem, s>>>(p);
   return cudaGetLastError();
 }
@@ -887,8 +915,9 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
 
   if (p.splits <= 0) {
     const int zBlocks = (p.kvHeads + kvPerCta - 1) / kvPerCta;
-    const int64_t ctas = (int64_t)p.batch * zBlocks;
+    const int64_t ctas = (int64_t)p.batch * (p.hasSecond ? 2 : 1) * zBlocks;
     int64_t nmax = p.useRange ? (p.end >= p.lo ? p.end - p.lo + 1 : 0) : p.kvLen;
+    if (p.hasSecond && p.s2.kvLen > nmax) nmax = p.s2.kvLen;
     if (p.kvSharded) {   // the longest stretch of a sequence this shard can hold
       nmax -= p.shardStart;
       nmax = nmax < 1 ? 1 : nmax > p.cacheRows ? p.cacheRows : nmax;
@@ -1021,7 +1050,8 @@ int rt_attn_decode_noalloc_status(void* cuda_stream) {
 int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
   using namespace rt;
   if (!a) return static_fail(RT_INVALID_ARGUMENT, "rt_attn_decode_noalloc: args is NULL");
-  if (!a->q || !a->kCache || !a->vCache || (!a->out && !a->partialsOut))
+  if (!a->q || (!a->kCache && !a->kCachePtrs) || (!a->vCache && !a->vCachePtrs) ||
+      (!a->out && !a->partialsOut))
     return static_fail(RT_INVALID_ARGUMENT,
                        "rt_attn_decode_noalloc: q, kCache, vCache and out (or partialsOut) must be "
                        "device pointers");
@@ -1035,7 +1065,8 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
       (!a->kvSharded && a->kvLen > a->cacheRows) || (!a->kvLens && a->kvLen < 1) || a->windowLeft < 0 ||
       a->splits < 0 || a->splits > 64 || (a->kNew == nullptr) != (a->vNew == nullptr) ||
       a->cacheSeqStride < 0 ||
-      (a->batch > 1 && a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim) ||
+      (!a->kCachePtrs && a->batch > 1 &&
+       a->cacheSeqStride < (int64_t)a->cacheRows * a->kvHeads * a->headDim) ||
       decode_rope_args_error(*a) != nullptr)
     return static_fail(RT_INVALID_ARGUMENT,
                        "rt_attn_decode_noalloc: a size or option is out of range (same rules as "
@@ -1051,8 +1082,9 @@ int rt_attn_decode_noalloc(const rt_decode_args* a, void* cuda_stream) {
   std::string err;
   if (!plan_decode(p, a->dtype, smCount, &err)) return static_fail(RT_INVALID_ARGUMENT, err);
   const size_t zBlocks = (size_t)(p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
-  const size_t needFloats = p.splits > 1 ? (size_t)p.batch * p.splits * p.qHeads * (2 + p.hd) : 0;
-  const size_t needCounters = p.splits > 1 ? (size_t)p.batch * zBlocks : 0;
+  const size_t sets = p.hasSecond ? 2 : 1;
+  const size_t needFloats = p.splits > 1 ? sets * p.batch * p.splits * p.qHeads * (2 + p.hd) : 0;
+  const size_t needCounters = p.splits > 1 ? sets * p.batch * zBlocks : 0;
   if (needFloats > kStaticScratchFloats || needCounters > kStaticCounters)
     return static_fail(
         RT_INVALID_ARGUMENT,

@@ -24,7 +24,7 @@ from __future__ import annotations
 import ctypes as C
 from typing import Optional, Tuple
 
-from ._lib import AttnArgs, DecodeArgs, DTYPE_CODE, Exchange, WINDOW_INF, check
+from ._lib import AttnArgs, DecodeArgs, DecodeSecond, DTYPE_CODE, Exchange, WINDOW_INF, check
 from .executor import CudaExecutor
 
 
@@ -66,12 +66,16 @@ def decode_batched(ex: CudaExecutor, q, out, kCache, vCache, *, dtype: str, batc
                    windowLeft=None, sinks=None, partialsOut=None, splits: int = 0,
                    ropeCos=None, ropeSin=None, ropeByPosition: bool = False, qRowStride: int = 0,
                    kNewRowStride: int = 0, vNewRowStride: int = 0, exchange=None,
-                   kvSharded: bool = False, shardStart: int = 0) -> None:
+                   kvSharded: bool = False, shardStart: int = 0, kCachePtrs=None, vCachePtrs=None,
+                   second=None) -> None:
     """One decode step for ``batch`` sequences; see rt_attn_decode in
     include/rt_attn.h.  ``kvLen`` is the (maximum) visible length including the
     appended row; ``kvLens`` gives it per sequence.  With ``ropeCos``/``ropeSin``
     q and kNew are un-rotated rows (for example windows of the fused qkv
-    projection, ``*RowStride`` apart) and the kernel rotates them."""
+    projection, ``*RowStride`` apart) and the kernel rotates them.
+    ``kCachePtrs``/``vCachePtrs``: device int64 arrays [batch] of cache addresses, for
+    caches allocated one by one (``kCache``/``vCache`` may then be None).  ``second``
+    (from ``second_attention``): a cross-attention computed by the same launch."""
     d = DecodeArgs()
     d.q, d.out = _ptr(q), _ptr(out)
     d.kCache, d.vCache = _ptr(kCache), _ptr(vCache)
@@ -87,7 +91,28 @@ def decode_batched(ex: CudaExecutor, q, out, kCache, vCache, *, dtype: str, batc
     if exchange is not None:
         d.exchange = C.pointer(exchange)
     d.kvSharded, d.shardStart = int(kvSharded), shardStart
+    d.kCachePtrs, d.vCachePtrs = _ptr(kCachePtrs), _ptr(vCachePtrs)
+    if second is not None:
+        d.second = C.pointer(second)
     check(ex._lib.rt_attn_decode(ex.ctx, C.byref(d)), ex.ctx)
+
+
+def second_attention(q, out, kCache, vCache, *, cacheRows: int, qHeads: int, kvHeads: int,
+                     headDim: int, kvLen: int = 0, kvLens=None, windowLeft=None,
+                     cacheSeqStride: Optional[int] = None, qRowStride: int = 0, kCachePtrs=None,
+                     vCachePtrs=None) -> DecodeSecond:
+    """The ``second`` argument of decode_batched: a cross-attention (no append, no rope)
+    that shares the launch of a self-attention step — the two attentions of a decoder
+    layer (packages/runntime/src/zoo/moonshine/decoder.ts:58-76, 105-109) in one kernel."""
+    x = DecodeSecond()
+    x.q, x.out = _ptr(q), _ptr(out)
+    x.kCache, x.vCache = _ptr(kCache), _ptr(vCache)
+    x.kCachePtrs, x.vCachePtrs = _ptr(kCachePtrs), _ptr(vCachePtrs)
+    x.kvLens = _ptr(kvLens)
+    x.cacheSeqStride = (cacheRows * kvHeads * headDim) if cacheSeqStride is None else cacheSeqStride
+    x.qRowStride = qRowStride
+    x.cacheRows, x.kvLen, x.windowLeft = cacheRows, (kvLen or cacheRows), _win(windowLeft)
+    return x
 
 
 def merge_partials(ex: CudaExecutor, partials, parts: int, units: int, headDim: int, out,
@@ -164,6 +189,19 @@ class KvCacheEngine:
                        cacheRows=self.maxPositions, qHeads=self.qHeads, kvHeads=self.kvHeads,
                        headDim=self.headDim, kvLen=self.maxLen, kvLens=self.lens, kNew=kNew,
                        vNew=vNew, windowLeft=self.windowLeft)
+
+    def stepWithCross(self, q, kNew, vNew, out, qCross, outCross) -> None:
+        """The self-attention step (append + causal attend) and the cross-attention over
+        the encoder states set by setCross, in one launch."""
+        k, v, rows = self.cross
+        _bind_to_torch_stream(self.ex)
+        self._advance()
+        sec = second_attention(qCross, outCross, k, v, cacheRows=rows, qHeads=self.qHeads,
+                               kvHeads=self.kvHeads, headDim=self.headDim, kvLen=rows)
+        decode_batched(self.ex, q, out, self.k, self.v, dtype=self.dtype, batch=self.batch,
+                       cacheRows=self.maxPositions, qHeads=self.qHeads, kvHeads=self.kvHeads,
+                       headDim=self.headDim, kvLen=self.maxLen, kvLens=self.lens, kNew=kNew,
+                       vNew=vNew, windowLeft=self.windowLeft, second=sec)
 
     def crossAttend(self, q, out) -> None:
         k, v, rows = self.cross

@@ -182,6 +182,103 @@ def test_device_side_length_past_the_cache_is_refused_not_written(ex, heads, hd)
         ex.setStream(None)
 
 
+@pytest.mark.parametrize("dtype,heads,kvHeads,hd", [("f16", 8, 8, 36), ("f16", 32, 8, 128),
+                                                     ("f32", 4, 4, 20)])
+def test_self_and_cross_attention_in_one_launch(ex, dtype, heads, kvHeads, hd):
+    """A decoder layer's two attentions — the step over the self cache with the append,
+    and the cross-attention over the encoder states with a query of its own — from one
+    kernel launch, for every split choice."""
+    import torch
+    from runntime_b200.engine import decode_batched, second_attention
+    batch, cacheRows, cross = 9, 448, 200
+    lens = [1, 2, 31, 32, 33, 200, 257, 447, 448]
+    q, kc, vc, kn, vn, lt = _batched_inputs(batch, cacheRows, heads, kvHeads, hd, dtype, lens)
+    q2, ck, cv, _, _, _ = _batched_inputs(batch, cross, heads, kvHeads, hd, dtype, [cross] * batch,
+                                          seed=12)
+    dev = torch.device("cuda", 0)
+    qd, kcd, vcd, knd, vnd, ld, q2d, ckd, cvd = (t.to(dev) for t in (q, kc, vc, kn, vn, lt, q2, ck, cv))
+    out = torch.full((batch, heads * hd), 7.0, dtype=qd.dtype, device=dev)
+    out2 = torch.full_like(out, 7.0)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        for splits in (0, 1, 3):
+            kcd.copy_(kc)
+            vcd.copy_(vc)
+            sec = second_attention(q2d, out2, ckd, cvd, cacheRows=cross, qHeads=heads,
+                                   kvHeads=kvHeads, headDim=hd, kvLen=cross)
+            before = ex.launchCount()
+            decode_batched(ex, qd, out, kcd, vcd, dtype=dtype, batch=batch, cacheRows=cacheRows,
+                           qHeads=heads, kvHeads=kvHeads, headDim=hd, kvLen=max(lens), kvLens=ld,
+                           kNew=knd, vNew=vnd, splits=splits, second=sec)
+            ex.sync()
+            assert ex.launchCount() == before + 1
+            got, got2 = out.float().cpu().numpy(), out2.float().cpu().numpy()
+            kc2, vc2 = kc.clone(), vc.clone()
+            for b, L in enumerate(lens):
+                kc2[b, L - 1], vc2[b, L - 1] = kn[b], vn[b]
+                want = sdpa_ref(q[b:b + 1].float().numpy(), kc2[b, :L].float().numpy(),
+                                vc2[b, :L].float().numpy(), qHeads=heads, kvHeads=kvHeads,
+                                headDim=hd, windowRight=0, qPosOffset=L - 1)
+                oracle.assert_close(got[b], want, dtype, f"self seq {b} splits {splits}")
+                want = sdpa_ref(q2[b:b + 1].float().numpy(), ck[b].float().numpy(),
+                                cv[b].float().numpy(), qHeads=heads, kvHeads=kvHeads, headDim=hd)
+                oracle.assert_close(got2[b], want, dtype, f"cross seq {b} splits {splits}")
+            assert torch.equal(kcd.cpu(), kc2) and torch.equal(vcd.cpu(), vc2)
+            assert torch.equal(ckd.cpu(), ck)
+    finally:
+        ex.setStream(None)
+
+
+@pytest.mark.parametrize("heads,hd", [(8, 52), (32, 128), (3, 37)])
+def test_caches_allocated_one_by_one(ex, heads, hd):
+    """Every sequence's K and V cache is its own allocation (as the reference's per-layer,
+    per-sequence cache tensors are), handed over as arrays of pointers."""
+    import torch
+    import runntime_b200 as rt
+    from runntime_b200.engine import decode_batched
+    batch, cacheRows = 5, 300
+    lens = [300, 1, 77, 256, 129]
+    q, kc, vc, kn, vn, lt = _batched_inputs(batch, cacheRows, heads, heads, hd, "f16", lens)
+    dev = torch.device("cuda", 0)
+    ks = [kc[b].clone().to(dev) for b in range(batch)]
+    vs = [vc[b].clone().to(dev) for b in range(batch)]
+    kp = torch.tensor([t.data_ptr() for t in ks], dtype=torch.int64, device=dev)
+    vp = torch.tensor([t.data_ptr() for t in vs], dtype=torch.int64, device=dev)
+    qd, knd, vnd, ld = q.to(dev), kn.to(dev), vn.to(dev), lt.to(dev)
+    out = torch.full((batch, heads * hd), 7.0, dtype=qd.dtype, device=dev)
+    ex.setStream(torch.cuda.current_stream().cuda_stream)
+    try:
+        decode_batched(ex, qd, out, None, None, dtype="f16", batch=batch, cacheRows=cacheRows,
+                       qHeads=heads, kvHeads=heads, headDim=hd, kvLen=max(lens), kvLens=ld, kNew=knd,
+                       vNew=vnd, kCachePtrs=kp, vCachePtrs=vp)
+        ex.sync()
+        got = out.float().cpu().numpy()
+        for b, L in enumerate(lens):
+            kb, vb = kc[b, :L].clone(), vc[b, :L].clone()
+            kb[L - 1], vb[L - 1] = kn[b], vn[b]
+            want = sdpa_ref(q[b:b + 1].float().numpy(), kb.float().numpy(), vb.float().numpy(),
+                            qHeads=heads, kvHeads=heads, headDim=hd, windowRight=0, qPosOffset=L - 1)
+            oracle.assert_close(got[b], want, "f16", f"seq {b}")
+            assert torch.equal(ks[b][:L].cpu(), kb) and torch.equal(ks[b][L:].cpu(), kc[b, L:])
+        if hd % 8 == 4:
+            # a cache that starts 8 bytes off a 16-byte boundary cannot take the bulk copies:
+            # its sequence comes out as zeros and the status says so; the others are computed
+            off = torch.zeros(cacheRows * heads * hd + 4, dtype=torch.float16, device=dev)
+            shifted = off[4:]
+            shifted.copy_(kc[1].reshape(-1))
+            kp2 = kp.clone()
+            kp2[1] = shifted.data_ptr()
+            out.fill_(7.0)
+            decode_batched(ex, qd, out, None, None, dtype="f16", batch=batch, cacheRows=cacheRows,
+                           qHeads=heads, kvHeads=heads, headDim=hd, kvLen=max(lens), kvLens=ld,
+                           kCachePtrs=kp2, vCachePtrs=vp)
+            with pytest.raises(rt.RunntimeError, match="not 16-byte aligned"):
+                ex.sync()
+            assert (out[1] == 0).all() and not (out[0] == 7.0).any()
+    finally:
+        ex.setStream(None)
+
+
 def test_batched_cross_attention_and_window(ex):
     import torch
     from runntime_b200.engine import decode_batched
