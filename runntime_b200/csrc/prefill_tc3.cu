@@ -54,6 +54,9 @@ namespace {
 using namespace sm100;
 using namespace tc;
 
+#ifndef RT_TC3_RELAXED
+#define RT_TC3_RELAXED 0
+#endif
 constexpr int kThreads3 = 384;
 constexpr int kRegsSoftmax3 = 216, kRegsOther3 = 64;  // 2*128*216 + 128*64 <= 384*168
 constexpr int BK3 = 128;
@@ -567,7 +570,12 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         const uint32_t doneAddr = smem_u32(const_cast<int*>(&sMaxDone[w]));
         for (int i = 0; i < (1 << 22); i++) {
           int done;
+#if RT_TC3_RELAXED
+          (void)doneAddr;
+          done = sMaxDone[w];
+#else
           asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(done) : "r"(doneAddr) : "memory");
+#endif
           if (done >= j) { arrived = true; break; }
           if ((i & 63) == 63) {
             if (sAbort) break;
@@ -614,19 +622,35 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         sMref[rowInTile] = mnew;
       }
       __syncwarp();
+#if RT_TC3_RELAXED
+      if (lane == 0) sMaxDone[w] = j + 1;
+#else
       if (lane == 0)
         asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(
                          smem_u32(const_cast<int*>(&sMaxDone[w]))),
                      "r"(j + 1)
                      : "memory");
+#endif
       TC_TRACE(3, j);
 
       // ---- exponentials, P in two halves ----
       // P's own columns were last read by P V(j-2).
       if (C::P_OWN && j >= 2) {
+#if RT_TC3_RELAXED
+        // (nearly always complete by now: one look by one lane, the full wait only if not)
+        const uint32_t pvBar = smem_u32(&bars.pvDone[g]);
+        const uint32_t pvPar = ((j >> 1) - 1) & 1;
+        int done = 0;
+        if (lane == 0) done = mbar_test_wait(pvBar, pvPar);
+        if (!__shfl_sync(0xffffffffu, done, 0)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(pvBar, pvPar, &sAbort));
+          if (!ok) break;
+        }
+#else
         ok = __all_sync(0xffffffffu,
                         mbar_wait(smem_u32(&bars.pvDone[g]), ((j >> 1) - 1) & 1, &sAbort));
         if (!ok) break;
+#endif
       }
       TC_TRACE(6, j);
       float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),

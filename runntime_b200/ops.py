@@ -61,11 +61,19 @@ def _lower_window(op: str, name: str, w) -> int:
 
 
 def sdpa(q: Value, k: Value, v: Value, opts: dict) -> Value:
-    """Scaled-dot-product attention over the band-mask family, with GQA and
-    optional sinks; kvLen is independent of qLen.  Key j is visible to row i
-    when qPos - windowLeft <= j <= qPos + windowRight, qPos = qPosOffset + i.
-    ``segments`` clips each row to its own key range; ``keyBias`` adds ``value``
-    to the scores of keys [start, end).  No score scale is applied."""
+    """The reference's ``sdpa`` (packages/runntime/src/core/graph/ops/attention.ts:28-141):
+    checks the arguments now, with the reference's messages, and returns a pending
+    'attn' node whose attrs vector has the reference's layout; nothing runs until the
+    value is evaluated.
+
+    What the node computes, for ``q [qLen, qHeads*headDim]`` against
+    ``k, v [kvLen, kvHeads*headDim]``: every query head attends to the kv head of its group
+    (grouped-query attention); row i stands at position ``qPosOffset + i`` and sees the
+    keys from ``windowLeft`` before that position to ``windowRight`` after it (``math.inf``
+    = no limit on that side); with ``segments`` a row is further confined to its own
+    ``[start, end)`` of keys; ``keyBias`` raises the scores of one key range by a constant;
+    ``sinks`` gives every head an extra term in the softmax denominator.  Scores are used
+    as they come: callers fold 1/sqrt(headDim) into q or k."""
     qHeads, kvHeads, headDim = opts["qHeads"], opts["kvHeads"], opts["headDim"]
     sinks: Optional[Value] = opts.get("sinks")
     segments: Optional[Value] = opts.get("segments")
@@ -134,8 +142,10 @@ def sdpa(q: Value, k: Value, v: Value, opts: dict) -> Value:
 
 
 def sdpaPacked(qkv: Value, opts: dict) -> Value:
-    """sdpa over one fused qkv tensor read in place, q, k and v as column
-    blocks.  Self-attention only, no qLen = 1 route, no key bias."""
+    """The reference's ``sdpaPacked`` (ops/attention.ts:146-212): self-attention whose
+    q, k and v are the three column blocks of ONE tensor ``qkv [T, (qHeads +
+    2*kvHeads)*headDim]`` — the fused projection's output is attended to where it lies, no
+    slicing.  More than one row, heads up to 128 wide, no key bias; otherwise ``sdpa``."""
     qHeads, kvHeads, headDim = opts["qHeads"], opts["kvHeads"], opts["headDim"]
     sinks: Optional[Value] = opts.get("sinks")
     segments: Optional[Value] = opts.get("segments")
@@ -181,12 +191,11 @@ def sdpaPacked(qkv: Value, opts: dict) -> Value:
 
 
 def rope(x: Value, cos: Value, sin: Value, opts: dict) -> Value:
-    """Rotary position embedding over every head section of x [T, W] in one
-    kernel.  Rotation is interleaved-pair, and cos/sin are pair-duplicated f32
-    tables [T, headDim] with any scale pre-folded.  ``srcStart`` and ``width``
-    optionally read a slice of a wider slab — the q or k section of a fused qkv —
-    and rope it in the same dispatch
-    (packages/runntime/src/core/graph/ops/attention.ts:214-252)."""
+    """The reference's ``rope`` (ops/attention.ts:214-252): rotates each adjacent
+    pair of columns (2i, 2i+1) of every head of ``x [T, W]`` by the row's angle, taken
+    from f32 tables ``cos, sin [T, headDim]`` that hold each pair's value twice and may
+    carry a scale.  ``srcStart``/``width`` pick a column window of a wider row — the q
+    or the k part of a fused qkv projection — so that no slice is needed first."""
     headDim = opts["headDim"]
     t, xw, dtype = want2d("rope", x, FLOAT_DTYPES)
     srcStart = opts.get("srcStart")
