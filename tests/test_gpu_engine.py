@@ -94,6 +94,23 @@ def test_kv_cache_engine_steps_like_the_decoder_loop(ex):
                     oracle.assert_close(out2[b].float().cpu().numpy(), want, "f16", f"cross t={t}")
         assert torch.equal(eng.k[:, :steps].cpu(), ks.transpose(0, 1))
         assert (eng.k[:, steps:] == 0).all()
+        # one more token with the layer's two attentions in one launch: the self step (append
+        # + attend) and the cross-attention, whose query is another projection
+        kn, vn = torch.randn(batch, w, generator=g).half(), torch.randn(batch, w, generator=g).half()
+        qa, qb = (torch.randn(batch, w, generator=g) / 6).half(), (torch.randn(batch, w, generator=g) / 6).half()
+        before = ex.launchCount()
+        eng.stepWithCross(qa.to(dev), kn.to(dev), vn.to(dev), out, qb.to(dev), out2)
+        ex.sync()
+        assert ex.launchCount() == before + 1
+        for b in range(batch):
+            kb = torch.cat([ks[:, b], kn[b:b + 1]]).float().numpy()
+            vb = torch.cat([vs[:, b], vn[b:b + 1]]).float().numpy()
+            want = sdpa_ref(qa[b:b + 1].float().numpy(), kb, vb, qHeads=heads, kvHeads=heads,
+                            headDim=hd, windowRight=0, qPosOffset=steps)
+            oracle.assert_close(out[b].float().cpu().numpy(), want, "f16", "self, one launch")
+            want = sdpa_ref(qb[b:b + 1].float().numpy(), ck[b].float().numpy(), cv[b].float().numpy(),
+                            qHeads=heads, kvHeads=heads, headDim=hd)
+            oracle.assert_close(out2[b].float().cpu().numpy(), want, "f16", "cross, one launch")
         with pytest.raises(ValueError, match="exceed dst capacity 64"):
             for _ in range(30):
                 eng.step(qs[0].to(dev), ks[0].to(dev), vs[0].to(dev), out)
