@@ -742,7 +742,7 @@ def run_gpu(args):
         flush = (lambda: flushbuf.sum()) if small else None
         sampler = ClockSampler(local) if (rank == 0 and not args.no_clocks) else None
         step_fn = lambda i: wl.step(i % layers)
-        graphed = False
+        graphed, graph_steps = False, 1
         n1 = ex.launchCount()
         for i in range(3):
             wl.step(i % layers)
@@ -751,9 +751,15 @@ def run_gpu(args):
         if cfg["kind"] == "decode" and not args.no_graph:
             # A decode step is a few short launches (kernel, merge): capture it once in a
             # CUDA graph so that the device is not left waiting for the host.
+            # Where steps run back to back (no L2 flush between them) the graph holds several:
+            # inside a graph a kernel is launched as a programmatic dependent of the one
+            # before it, as it is in a decoder's graph of a whole token, which single-kernel
+            # graphs replayed one after the other cannot show.
+            graph_steps = max(1, args.graph_steps) if flush is None else 1
             graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
             with torch.cuda.graph(graph, stream=side):
-                wl.step(0)
+                for g in range(graph_steps):
+                    wl.step(g % layers)
             ex.setStream(torch.cuda.current_stream().cuda_stream)
             step_fn = lambda i: graph.replay()
             graphed = True
@@ -766,6 +772,7 @@ def run_gpu(args):
                                             min_timed_s=1.0 if (sized and not args.short) else 0.0)
         clocks = sampler.stop() if sampler else None
         ex.sync()
+        timed_steps, warm_steps = timed_steps * graph_steps, warm_steps * graph_steps
         launches = int(round(per_step * timed_steps))
         resample = clocks is not None and (clocks.get("samples") or 0) < 3
         if world > 1:      # rank 0 holds the sampler; every rank must take the same path
@@ -780,7 +787,7 @@ def run_gpu(args):
             sampler = ClockSampler(local) if rank == 0 else None
             if sampler:
                 sampler.start()
-            n_rep = max(8, int(1500.0 / max(ms / timed_steps, 1e-3)))
+            n_rep = max(8, int(1500.0 / max(ms / timed_steps * graph_steps, 1e-3)))
             n_rep = min(n_rep, 200000)
             for i in range(n_rep):
                 step_fn(i)
@@ -822,7 +829,8 @@ def run_gpu(args):
             "warmup_steps": warm_steps, "roofline": roof,
             "clocks": clocks, "gpu_launches": launches, "verified": verified,
             "l2": "256 MB read between timed steps" if small else "inputs larger than L2",
-            "launch": "CUDA graph replay of one step" if graphed else "direct launches",
+            "launch": (f"CUDA graph replay of {graph_steps} step{'s' if graph_steps > 1 else ''}"
+                       if graphed else "direct launches"),
         }
         if with_e2e and not args.no_e2e:
             wl.make_host()
@@ -1160,6 +1168,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (e2e) leg")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi clocks")
+    ap.add_argument("--graph-steps", type=int, default=8,
+                    help="decode steps captured in one CUDA graph (back-to-back workloads)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch decode steps directly instead of replaying a CUDA graph")
     ap.add_argument("--tc-mode", type=int, default=None,

@@ -26,6 +26,28 @@ namespace {
 
 using namespace sm100;
 
+// Optional per-CTA timeline for kernel development (off unless the translation unit is
+// compiled with RT_DEC_TRACE): thread 0 of every CTA stores the global timer at a few points.
+#ifdef RT_DEC_TRACE
+constexpr int kDecTraceCtas = 8192, kDecTracePoints = 8;
+__device__ unsigned long long gDecTrace[kDecTraceCtas * kDecTracePoints];
+#define DEC_TRACE(i)                                                                        \
+  do {                                                                                      \
+    if (threadIdx.x == 0) {                                                                 \
+      const unsigned id_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;  \
+      if (id_ < kDecTraceCtas) {                                                            \
+        unsigned long long t_;                                                              \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+        gDecTrace[id_ * kDecTracePoints + (i)] = t_;                                        \
+      }                                                                                     \
+    }                                                                                       \
+  } while (0)
+#else
+#define DEC_TRACE(i) \
+  do {               \
+  } while (0)
+#endif
+
 constexpr int kConsumers = 256;
 constexpr int kConsumerWarps = kConsumers / 32;
 constexpr int kMaxStages = 8;
@@ -266,8 +288,7 @@ __device__ __forceinline__ void exchange_rows(const DecodeParams& p, int b, int 
   float* dst = p.xPartials[owner] +
                ((((int64_t)(epoch & 1u) * p.xWorld + p.xRank) * p.xPer + bl) * p.qHeads + h0) * stride;
   const int n = hq * stride;
-  __threadfence();                     // the rows written by this block's threads ...
-  named_barrier_sync(1, kConsumers);   // ... are visible to all of them
+  named_barrier_sync(1, kConsumers);   // the rows this block's threads wrote are visible to all of them
   for (int i = tid; i < n; i += kConsumers) dst[i] = __ldcg(src + i);
   __threadfence();                     // each thread's stores, before the block is counted in
   named_barrier_sync(1, kConsumers);
@@ -299,6 +320,11 @@ decode_kernel(const DecodeParams p) {
   __shared__ __align__(8) uint64_t sFull[kMaxStages], sEmpty[kMaxStages];
 
   const int tid = threadIdx.x;
+  DEC_TRACE(0);
+  // Launched as a programmatic dependent of the kernel before it in the stream (see
+  // launch_one): the blocks may become resident while that kernel's last blocks finish, and
+  // wait here until all of its writes are visible.  Nothing above reads memory.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int split = blockIdx.x, zb = blockIdx.z;
   const int by = blockIdx.y;   // unique per (attention, sequence): indexes scratch and counters
   int b = by;
@@ -351,6 +377,28 @@ decode_kernel(const DecodeParams p) {
                         : static_cast<const T*>(sec ? p.s2.kCache : p.kCache) + (int64_t)b * aSeqStride;
   const T* vSeq = vPtrs ? static_cast<const T*>(vPtrs[b])
                         : static_cast<const T*>(sec ? p.s2.vCache : p.vCache) + (int64_t)b * aSeqStride;
+  // What a consumer thread stages — q and, in split 0, the appended K/V row — is loaded into
+  // registers before the sequence's length is looked at: the length decides where the rows
+  // go, not where they come from, and under a saturated memory system every load that has
+  // to wait for another costs microseconds of set-up.
+  constexpr int kPre = 4;   // elements per thread held in registers; longer rows finish in a loop
+  const T* qg = static_cast<const T*>(aQ) + (int64_t)b * aQStride;
+  const bool roped = p.ropeCos != nullptr && !p.useRange && !sec;
+  const bool pre = R == 1 && !roped && tid < kConsumers;
+  const bool preNew = pre && hasNew && split == 0 && !p.useRange;
+  const T* kn = hasNew ? static_cast<const T*>(p.kNew) + (int64_t)b * p.kNewRowStride + kvh0 * hd : nullptr;
+  const T* vn = hasNew ? static_cast<const T*>(p.vNew) + (int64_t)b * p.vNewRowStride + kvh0 * hd : nullptr;
+  T qPre[kPre], knPre[kPre], vnPre[kPre];
+#pragma unroll
+  for (int i = 0; i < kPre; i++) {
+    const int idx = tid + i * kConsumers;
+    qPre[i] = knPre[i] = vnPre[i] = from_f32<T>(0.f);
+    if (pre && idx < hqReal * hd) qPre[i] = qg[kvh0 * group * hd + idx];   // the CTA's heads are contiguous
+    if (preNew && idx < sliceElems) {
+      knPre[i] = kn[idx];
+      vnPre[i] = vn[idx];
+    }
+  }
   // (a separately allocated cache is only known here: the bulk copies need 16-byte alignment)
   const bool misaligned = kPtrs && BULK &&
                           ((reinterpret_cast<uintptr_t>(kSeq) | reinterpret_cast<uintptr_t>(vSeq)) & 15u);
@@ -465,8 +513,6 @@ decode_kernel(const DecodeParams p) {
   // writeRows would do) and is attended from shared memory after the cache keys.
   const bool appendHere = hasNew && split == 0 && !p.useRange && L >= 1;
   const float* qv = sQ + hl * QS;
-  const T* qg = static_cast<const T*>(aQ) + (int64_t)b * aQStride;
-  const bool roped = p.ropeCos != nullptr && !p.useRange && !sec;
   const int64_t ropeRow = p.ropeByPos ? (Lg >= 1 ? Lg - 1 : 0) : b;
   const float* rc = roped ? p.ropeCos + ropeRow * hd : nullptr;
   const float* rs = roped ? p.ropeSin + ropeRow * hd : nullptr;
@@ -484,14 +530,20 @@ decode_kernel(const DecodeParams p) {
         sQ[hh * QS + x + 1] = to_f32<T>(from_f32<T>(r1));
       }
     } else {
-      for (int idx = tid; idx < hqReal * hd; idx += kConsumers) {
+#pragma unroll
+      for (int i = 0; i < kPre; i++) {
+        const int idx = tid + i * kConsumers;
+        if (idx < hqReal * hd) {
+          const int hh = idx / hd, x = idx - hh * hd;
+          sQ[hh * QS + x] = to_f32<T>(qPre[i]);
+        }
+      }
+      for (int idx = tid + kPre * kConsumers; idx < hqReal * hd; idx += kConsumers) {
         const int hh = idx / hd, x = idx - hh * hd;
         sQ[hh * QS + x] = to_f32<T>(qg[(kvh0 * group + hh) * hd + x]);
       }
     }
     if (appendHere) {
-      const T* kn = static_cast<const T*>(p.kNew) + (int64_t)b * p.kNewRowStride + kvh0 * hd;
-      const T* vn = static_cast<const T*>(p.vNew) + (int64_t)b * p.vNewRowStride + kvh0 * hd;
       T* kc = const_cast<T*>(kBase) + (L - 1) * rowElems;
       T* vc = const_cast<T*>(vBase) + (L - 1) * rowElems;
       if (roped) {
@@ -505,7 +557,17 @@ decode_kernel(const DecodeParams p) {
           kc[hh * hd + x] = t0, kc[hh * hd + x + 1] = t1;
         }
       }
-      for (int x = tid; x < sliceElems; x += kConsumers) {
+      if (preNew) {
+#pragma unroll
+        for (int i = 0; i < kPre; i++) {
+          const int x = tid + i * kConsumers;
+          if (x < sliceElems) {
+            sKn[x] = knPre[i], kc[x] = knPre[i];
+            sVn[x] = vnPre[i], vc[x] = vnPre[i];
+          }
+        }
+      }
+      for (int x = tid + (preNew ? kPre * kConsumers : 0); x < sliceElems; x += kConsumers) {
         if (!roped) {
           const T t = kn[x];
           if (R == 1) sKn[x] = t;
@@ -518,6 +580,7 @@ decode_kernel(const DecodeParams p) {
     }
     named_barrier_sync(1, kConsumers);
   }
+  DEC_TRACE(1);
 
   float m = kNegSeed, l = 0.f;
   float acc[W];
@@ -601,6 +664,7 @@ decode_kernel(const DecodeParams p) {
     T* tV = reinterpret_cast<T*>(ring + (size_t)s * 2 * tileBytes + tileBytes);
     if (BULK) {
       if (!mbar_wait(smem_u32(&sFull[s]), (it / stages) & 1, &sAbort)) { ok = false; break; }
+      if (it == 0) DEC_TRACE(2);
     } else {
       named_barrier_sync(1, kConsumers);
       for (int idx = tid; idx < nk * sliceElems; idx += kConsumers) {
@@ -621,6 +685,10 @@ decode_kernel(const DecodeParams p) {
     }
   }
 
+  DEC_TRACE(3);
+  // This block has streamed its keys: once every block has, the next kernel's blocks may
+  // take the freed slots (they wait for this grid to finish before they read anything).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // Fused append: split 0 attends to the new row it staged (and stored) above.
   if (appendHere && active && slot == 0) {
     const int off = kvl * hd + sub * W;
@@ -669,45 +737,43 @@ decode_kernel(const DecodeParams p) {
   const int wd = R == 1 ? hd : W;   // columns this thread column owns ...
   const int col0 = sub * W;         // ... starting here in the head
   if (active) {
+    // Every thread of a head's column walks the head's KS slot rows: first for the maximum,
+    // then for the sum, then once per output column it owns (columns slot, slot+KS, ...).
+    // The slot weights are recomputed per column — a register array indexed by the column
+    // counter would live in local memory, whose round trips queue behind the cache streams.
     float M = kNegSeed;
     for (int s = 0; s < KS; s++) M = fmaxf(M, sM[(s * hqMax + hv) * MS]);
     float L = 0.f;
-    float o[W];  // entry c holds output column col0 + slot + c*KS
-    for (int c = 0, x = slot; x < wd; x += KS, c++) o[c] = 0.f;
     for (int s = 0; s < KS; s++) {
       const float* r = sM + (s * hqMax + hv) * MS;
-      const float w = fast_exp2(r[0] - M);
-      L = fmaf(r[1], w, L);
-      for (int c = 0, x = slot; x < wd; x += KS, c++) o[c] = fmaf(r[2 + x], w, o[c]);
+      L = fmaf(r[1], fast_exp2(r[0] - M), L);
     }
     const bool toPartials = partialsOut != nullptr;
-    if (p.splits == 1) {
-      if (toPartials) {
-        float* dst = partialsOut + ((int64_t)b * p.qHeads + h) * stride;
-        if (slot == 0 && sub == 0) {
-          dst[0] = L > 0.f ? M * 0.6931471805599453f : kNegSeed;
-          dst[1] = L;
-        }
-        int c = 0;
-        for (int x = slot; x < wd; x += KS) dst[2 + col0 + x] = o[c++];
-      } else {
-        const float invL = L > 0.f ? 1.f / L : 0.f;
-        T* dst = static_cast<T*>(aOut) + ((int64_t)b * p.qHeads + h) * hd + col0;
-        int c = 0;
-        for (int x = slot; x < wd; x += KS) dst[x] = from_f32<T>(o[c++] * invL);
+    const bool whole = p.splits == 1;
+    const float invL = L > 0.f ? 1.f / L : 0.f;
+    float* rowF = !whole ? p.scratch + (((int64_t)by * p.splits + split) * p.qHeads + h) * stride
+                         : toPartials ? partialsOut + ((int64_t)b * p.qHeads + h) * stride : nullptr;
+    T* rowT = static_cast<T*>(aOut) + ((int64_t)b * p.qHeads + h) * hd + col0;
+    if (rowF && slot == 0 && sub == 0) {
+      // finished rows carry the maximum in natural-log units, split rows in log2 units
+      rowF[0] = !whole ? M : L > 0.f ? M * 0.6931471805599453f : kNegSeed;
+      rowF[1] = L;
+    }
+    for (int x = slot; x < wd; x += KS) {
+      float o = 0.f;
+#pragma unroll 4
+      for (int s = 0; s < KS; s++) {
+        const float* r = sM + (s * hqMax + hv) * MS;
+        o = fmaf(r[2 + x], fast_exp2(r[0] - M), o);
       }
-    } else {
-      float* dst = p.scratch + (((int64_t)by * p.splits + split) * p.qHeads + h) * stride;
-      if (slot == 0 && sub == 0) {
-        dst[0] = M;
-        dst[1] = L;
-      }
-      int c = 0;
-      for (int x = slot; x < wd; x += KS) dst[2 + col0 + x] = o[c++];
+      if (rowF) rowF[2 + col0 + x] = o;
+      else rowT[x] = from_f32<T>(o * invL);
     }
   }
+  DEC_TRACE(4);
   if (p.splits == 1) {
     if (p.xWorld > 0) exchange_rows(p, b, hqReal, kvh0 * group, tid, epoch, gridDim.z);
+    DEC_TRACE(5);
     return;
   }
 
@@ -792,8 +858,17 @@ cudaError_t launch_one(const DecodeParams& p, size_t smem, cudaStream_t s) {
   if (e != cudaSuccess) return e;
   const int zBlocks = (p.kvHeads + p.kvPerCta - 1) / p.kvPerCta;
   dim3 grid(p.splits, p.batch * (p.hasSecond ? 2 : 1), zBlocks);
-  kern<<<grid, BULK ? kConsumers + 32 : kConsumers, smem, s>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(BULK ? kConsumers + 32 : kConsumers);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <typename T>

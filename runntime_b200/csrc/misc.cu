@@ -74,6 +74,10 @@ __global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
                                        int owned, int firstSeq, int heads, int hd,
                                        T* __restrict__ out, int* status, int limit) {
   __shared__ int sOk;
+  // A programmatic dependent of the decode kernel: resident early, reading nothing before
+  // that grid has finished; the kernel after this one may be made resident at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(step);
   if (threadIdx.x == 0) sOk = 1;
   __syncthreads();
@@ -106,23 +110,35 @@ __global__ void merge_exchanged_kernel(const float* __restrict__ buffer,
   const int64_t stride = 2 + hd;
   const int64_t slot = (int64_t)per * heads * stride;   // one source rank's rows
   const float* partials = buffer + (int64_t)(epoch & 1u) * world * slot + u * stride;
-  float M = kNegSeed;
-  for (int p = lane; p < world; p += 32) M = fmaxf(M, __ldcg(partials + p * slot));
-  M = warp_max(M);
-  float L = 0.f;
-  for (int p = lane; p < world; p += 32) {
-    const float* r = partials + p * slot;
-    L += __ldcg(r + 1) * __expf(__ldcg(r) - M);
+  // One round trip to memory: every load of the unit goes out before the first is used (the
+  // rows came in through peer stores, so they are read from L2 or DRAM, and loads that wait
+  // for one another would add a microsecond each).  Lane p holds rank p's (m, l); lane x
+  // holds output columns x, x+32, ... of every rank's row.
+  constexpr int kCols = 4;   // head sizes up to 128
+  float mv = kNegSeed, lv = 0.f;
+  if (lane < world) {
+    mv = __ldcg(partials + lane * slot);
+    lv = __ldcg(partials + lane * slot + 1);
   }
-  L = warp_sum(L);
+  float val[kCols][RT_MAX_PEERS];
+#pragma unroll
+  for (int c = 0; c < kCols; c++) {
+    const int x = lane + 32 * c;
+#pragma unroll
+    for (int p = 0; p < RT_MAX_PEERS; p++)
+      val[c][p] = (x < hd && p < world) ? __ldcg(partials + p * slot + 2 + x) : 0.f;
+  }
+  const float M = warp_max(mv);
+  const float w = lane < world ? __expf(mv - M) : 0.f;
+  const float L = warp_sum(lv * w);
   const float invL = L > 0.f ? 1.f / L : 0.f;
-  for (int x = lane; x < hd; x += 32) {
+#pragma unroll
+  for (int c = 0; c < kCols; c++) {
+    const int x = lane + 32 * c;
     float o = 0.f;
-    for (int p = 0; p < world; p++) {
-      const float* r = partials + p * slot;
-      o = fmaf(__ldcg(r + 2 + x), __expf(__ldcg(r) - M), o);
-    }
-    dst[x] = from_f32<T>(o * invL);
+#pragma unroll
+    for (int p = 0; p < RT_MAX_PEERS; p++) o = fmaf(val[c][p], __shfl_sync(0xffffffffu, w, p), o);
+    if (x < hd) dst[x] = from_f32<T>(o * invL);
   }
 }
 
@@ -324,15 +340,20 @@ cudaError_t launch_merge_exchanged(const float* buffer, const uint32_t* flags, c
   const int warps = 8;
   const int64_t units = (int64_t)owned * heads;
   const unsigned grid = (unsigned)((units + warps - 1) / warps);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(warps * 32);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   if (dtype == RT_F16)
-    merge_exchanged_kernel<__half><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, per, owned,
-                                                                firstSeq, heads, hd,
-                                                                static_cast<__half*>(out), status, limit);
-  else
-    merge_exchanged_kernel<float><<<grid, warps * 32, 0, s>>>(buffer, flags, step, world, per, owned,
-                                                               firstSeq, heads, hd,
-                                                               static_cast<float*>(out), status, limit);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, merge_exchanged_kernel<__half>, buffer, flags, step, world, per, owned,
+                              firstSeq, heads, hd, static_cast<__half*>(out), status, limit);
+  return cudaLaunchKernelEx(&cfg, merge_exchanged_kernel<float>, buffer, flags, step, world, per, owned,
+                            firstSeq, heads, hd, static_cast<float*>(out), status, limit);
 }
 
 cudaError_t launch_merge_partials(const float* partials, int parts, int64_t units, int hd,
