@@ -17,9 +17,10 @@
 // ordered by a per-warp counter, so both warpgroups always exponentiate against
 // the same reference point and the accumulator is rescaled by exactly one of them.
 //
-// Head sizes: 64 and 128 (P in its own columns), 256 (the accumulator takes half of
-// tensor memory, P overwrites the S columns it came from; K arrives as two
-// 128-column halves and V as two 64-key halves so that every ring slot is 32 KB and
+// Head sizes: 64 and 128 (two S buffers), 256 (the accumulator takes half of tensor
+// memory, so there is ONE S buffer — free again as soon as its scores are in a warpgroup's
+// registers, which is when the next S is issued — beside the two P buffers; K arrives as
+// two 128-column halves and V as two 64-key halves so that every ring slot is 32 KB and
 // S keeps the full-rate 128-key tile), and the narrow heads 32, 36, 52, ... (any
 // multiple of 4 up to 60) padded to 64 inside the tile: K and V tiles are fetched
 // with a 64-column box that starts on the 16-byte boundary at or below the head
@@ -79,9 +80,12 @@ struct Cfg3 {
   static constexpr int SLOTS_FIT = (225 * 1024 - Q_BYTES) / SLOT_BYTES;
   static constexpr int SLOTS = SLOTS_FIT > kMaxSlots ? kMaxSlots : SLOTS_FIT;
   static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024;
+  // Tensor memory: S | O | P up to head size 128 (two S buffers, 2 x 64 columns of P behind
+  // the accumulator); at head size 256 the accumulator takes the upper half and one S buffer
+  // shares the lower half with the two P buffers.
+  static constexpr int S_BUFS = HD == 256 ? 1 : 2;
   static constexpr int O_COL = 2 * BK3;
-  static constexpr bool P_OWN = HD <= 128;                      // P has columns of its own
-  static constexpr int P_COL = O_COL + 128;
+  static constexpr int P_COL = HD == 256 ? BK3 : O_COL + 128;
   static constexpr int TMEM_COLS = 512;
   static constexpr int CTAS = PAIR ? 2 : 1;
   static_assert(SLOTS >= KP + VP + 1, "ring too small");
@@ -381,17 +385,19 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 #pragma unroll 1
         for (int j = 0; j < nTiles && ok; j++) {
           const int b = j & 1;
+          const uint32_t sBuf = C::S_BUFS == 2 ? b * BK : 0;
           const int s0 = seq_k<KP, VP>(j);
           TC_TRACE(10, j);
 #pragma unroll
           for (int part = 0; part < KP; part++) {
             const int slot = (s0 + part) % NS;
             ok = wait(&bars.full[slot], ((s0 + part) / NS) & 1);
-            // The S buffer is free once its previous contents are dead: after the softmax
-            // warpgroup has loaded S(j-2) into registers, or — where P overwrites S — after
-            // P V(j-2) has read it.
-            if (ok && part == 0 && j >= 2)
-              ok = wait(C::P_OWN ? &bars.sFree[b] : &bars.pvDone[b], ((j >> 1) - 1) & 1);
+            // The S buffer is free once its previous contents are in the registers of the
+            // warpgroup that took them: S(j-2) with two buffers, S(j-1) with one.
+            if (ok && part == 0 && j >= C::S_BUFS) {
+              const int jp = j - C::S_BUFS;
+              ok = wait(&bars.sFree[jp & 1], (jp >> 1) & 1);
+            }
             if (!ok) break;
             tc_fence_after_sync();
             TC_TRACE(11, j);
@@ -404,8 +410,8 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                 if (PADDED && k2 >= kSteps) break;
                 const uint32_t aOff = (kk >> 2) * ((BM * 128) >> 4) + (kk & 3) * 2;
                 const uint32_t bOff = (k2 >> 2) * ((C::K_ROWS * 128) >> 4) + (k2 & 3) * 2;
-                if (PAIR) mma_f16_ss_pair(tmem + b * BK, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
-                else mma_f16_ss(tmem + b * BK, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
+                if (PAIR) mma_f16_ss_pair(tmem + sBuf, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
+                else mma_f16_ss(tmem + sBuf, desc(aLo + aOff), desc(bLo + bOff), idescS, kk > 0);
               }
               if (PAIR) {
                 tc_commit_pair(smem_u32(&bars.empty[slot]));
@@ -436,7 +442,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         for (int j = 0; j < nTiles && ok; j++) {
           const int b = j & 1;
           const int s0 = seq_v<KP, VP>(j, nTiles);
-          const uint32_t pCol = tmem + (C::P_OWN ? C::P_COL + b * 64 : b * BK);
+          const uint32_t pCol = tmem + C::P_COL + b * 64;
 #pragma unroll
           for (int half = 0; half < 2; half++) {
             const int part = VP == 2 ? half : 0;
@@ -478,8 +484,8 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax3));
     const int g = warp >> 2, w = warp & 3;
     const uint32_t laneBase = (uint32_t)(w * 32) << 16;
-    const uint32_t sCol = tmem + laneBase + g * BK;
-    const uint32_t pCol = tmem + laneBase + (C::P_OWN ? C::P_COL + g * 64 : g * BK);
+    const uint32_t sCol = tmem + laneBase + (C::S_BUFS == 2 ? g * BK : 0);
+    const uint32_t pCol = tmem + laneBase + C::P_COL + g * 64;
     const uint32_t oCol = tmem + laneBase + C::O_COL;
     // where the MMA issuers wait for this warp: this CTA, or the even CTA of the pair
     auto arrive = [&](uint64_t* bar) {
@@ -528,11 +534,10 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tmem_ld32(sCol + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
       tmem_wait_ld();
       TC_TRACE(2, j);
-      if (C::P_OWN) {  // S(j) is in registers: its buffer may take S(j+2)
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) arrive(&bars.sFree[g]);
-      }
+      // S(j) is in registers: its buffer may take the next S
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) arrive(&bars.sFree[g]);
       TC_TRACE(20, j);
       const bool fullTile = lo <= key0 && end >= key0 + BK - 1;
       if (p.hasKeyBias) {
@@ -635,7 +640,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
       // ---- exponentials, P in two halves ----
       // P's own columns were last read by P V(j-2).
-      if (C::P_OWN && j >= 2) {
+      if (j >= 2) {
 #if RT_TC3_RELAXED
         // (nearly always complete by now: one look by one lane, the full wait only if not)
         const uint32_t pvBar = smem_u32(&bars.pvDone[g]);

@@ -18,16 +18,19 @@ namespace tc {
 // (0,0) stores (clock, tag, index) records into its own slice of a device buffer
 // (plain stores, no atomics, so the timeline is barely disturbed).
 #ifdef RT_TC_TRACE
+#ifndef RT_TC_TRACE_X0
+#define RT_TC_TRACE_X0 0u   // first of the two traced CTAs (blockIdx.x; blockIdx.y is 0)
+#endif
 constexpr int kTraceWarps = 32, kTracePerWarp = 1024;
 __device__ long long gTraceBuf[kTraceWarps * kTracePerWarp * 2];
 #define TC_TRACE_DECL int traceSeq_ = 0;
-// CTAs (0,0) and (1,0): the second one's warps use slots 16 and up.
+// CTAs (X0,0) and (X0+1,0): the second one's warps use slots 16 and up.
 #define TC_TRACE(tag, idx)                                                                  \
   do {                                                                                      \
-    if (blockIdx.x <= 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 &&                    \
+    if (blockIdx.x - RT_TC_TRACE_X0 <= 1u && blockIdx.y == 0 && (threadIdx.x & 31) == 0 &&  \
         traceSeq_ < kTracePerWarp) {                                                        \
-      long long* r_ = gTraceBuf +                                                           \
-          ((blockIdx.x * 16 + (threadIdx.x >> 5)) * kTracePerWarp + traceSeq_++) * 2;       \
+      long long* r_ = gTraceBuf + (((blockIdx.x - RT_TC_TRACE_X0) * 16 + (threadIdx.x >> 5)) * \
+                                       kTracePerWarp + traceSeq_++) * 2;                     \
       r_[0] = clock64();                                                                    \
       r_[1] = (long long)(tag)*100000 + (idx) + 1;                                          \
     }                                                                                       \
