@@ -71,8 +71,9 @@ RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
  * alternate between two softmax warpgroups; head size 256: one tile, one
  * warpgroup).  0 sends every prefill to the FP32-pipe kernel; 2 forces one tile
  * with one warpgroup, 3 two tiles per block, 4 the alternating form, 5 the
- * alternating form on pairs of thread blocks that share every K/V tile — each
- * where that kernel applies (all compute the same op; the switch exists for
+ * alternating form on pairs of thread blocks that share every K/V tile, 6 the
+ * alternating form as one persistent thread block per SM over a queue of query
+ * tiles — each where that kernel applies (all compute the same op; the switch exists for
  * testing and measurement). */
 #define RT_OPT_PREFILL_TC 1
 /* RT_OPT_WAIT_POLLS (default 1 << 20, about a second): how often the merge of a

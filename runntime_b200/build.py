@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "librt_attn.so")
-SOURCES = ["api.cu", "prefill_simt.cu", "prefill_tc.cu", "prefill_tc2.cu", "prefill_tc3.cu", "decode.cu", "exchange.cu", "misc.cu", "softmax.cu",
+SOURCES = ["api.cu", "prefill_simt.cu", "prefill_tc.cu", "prefill_tc2.cu", "prefill_tc3.cu", "prefill_tc4.cu", "decode.cu", "exchange.cu", "misc.cu", "softmax.cu",
            "local_attn.cu", "matmul.cu",
            "matmul_tc.cu"]
 HEADERS = ["common.cuh", "sm100.cuh", "tc_common.cuh", os.path.join(ROOT, "include", "rt_attn.h")]

@@ -29,6 +29,9 @@ struct rt_ctx {
 namespace {
 
 constexpr uint32_t kLive = 0x52544358u;  // 'RTCX'
+// statusDev: the status word, then the two words of the persistent prefill kernel's work
+// queue (units drawn, CTAs finished), zero between launches.
+constexpr int kStatusWords = 3;
 constexpr uint32_t kDead = 0x44454144u;  // 'DEAD'
 
 thread_local std::string tlsError;
@@ -272,8 +275,8 @@ int rt_ctx_create(int device, rt_ctx** out) {
   ctx->waitPolls = 1 << 20;   // about a second with the kernel's sleeps
   if ((e = cudaSetDevice(device)) != cudaSuccess ||
       (e = cudaStreamCreateWithFlags(&ctx->own, cudaStreamNonBlocking)) != cudaSuccess ||
-      (e = cudaMalloc(&ctx->statusDev, sizeof(int))) != cudaSuccess ||
-      (e = cudaMemset(ctx->statusDev, 0, sizeof(int))) != cudaSuccess) {
+      (e = cudaMalloc(&ctx->statusDev, kStatusWords * sizeof(int))) != cudaSuccess ||
+      (e = cudaMemset(ctx->statusDev, 0, kStatusWords * sizeof(int))) != cudaSuccess) {
     delete ctx;
     return fail(nullptr, RT_EXECUTION_FAILED, "context setup: %s", cudaGetErrorString(e));
   }
@@ -307,8 +310,8 @@ int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external) {
 int rt_ctx_set_option(rt_ctx* ctx, int option, int value) {
   RT_ENTER(ctx);
   if (option == RT_OPT_PREFILL_TC) {
-    if (value < 0 || value > 5)
-      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..5, got %d",
+    if (value < 0 || value > 6)
+      return fail(ctx, RT_INVALID_ARGUMENT, "rt_ctx_set_option: RT_OPT_PREFILL_TC takes 0..6, got %d",
                   value);
     ctx->useTc = value;
     return RT_OK;
@@ -334,7 +337,9 @@ int rt_sync(rt_ctx* ctx) {
   int status = 0;
   RT_CUDA(ctx, cudaMemcpy(&status, ctx->statusDev, sizeof(int), cudaMemcpyDeviceToHost));
   if (status != 0) {
-    cudaMemset(ctx->statusDev, 0, sizeof(int));
+    // (with the status word, the work counter of the persistent prefill kernel, which a
+    // block that gave up never rewound)
+    cudaMemset(ctx->statusDev, 0, kStatusWords * sizeof(int));
     // A block that gave up never counted itself in: the arrival counters of the split
     // merge are no longer zero, and the next split launch would pick the wrong last block.
     if (ctx->counters) cudaMemset(ctx->counters, 0, ctx->counterCount * sizeof(unsigned));
@@ -387,10 +392,12 @@ int rt_buf_download(rt_ctx* ctx, const void* device_ptr, size_t offset, void* ho
 
 // 0 = FP32-pipe kernel, 1 = tensor cores, one query tile per CTA, 2 = two tiles per CTA,
 // 3 = one tile with two softmax warpgroups on alternate key tiles, 4 = the same in pairs of
-// CTAs that share every K/V tile.
+// CTAs that share every K/V tile, 5 = the persistent form of 3 (one CTA per SM, units
+// overlapping).
 static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dtype) {
   if (!ctx->useTc) return 0;
   const bool tc3 = rt::prefill_tc3_supported(p, dtype);
+  if (ctx->useTc == 6 && rt::prefill_tc4_supported(p, dtype)) return 5;
   if (ctx->useTc == 5 && rt::prefill_tc3_pair_supported(p, dtype)) return 4;
   if ((ctx->useTc == 4 || ctx->useTc == 5) && tc3) return 3;
   if (!rt::prefill_tc_supported(p, dtype)) return (tc3 && ctx->useTc == 1) ? 3 : 0;  // heads narrower than 64
@@ -408,7 +415,7 @@ static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dty
 static const char* route_of(const rt_ctx* ctx, const rt_attn_args* a) {
   if (a->qLen == 1) return "decode";
   const int k = prefill_kernel_of(ctx, to_params(a), a->dtype);
-  return k == 4 ? "prefill_tc3_pair" : k == 3 ? "prefill_tc3" : k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
+  return k == 5 ? "prefill_tc4" : k == 4 ? "prefill_tc3_pair" : k == 3 ? "prefill_tc3" : k == 2 ? "prefill_tc2" : k == 1 ? "prefill_tc" : "prefill_simt";
 }
 
 int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route) {
@@ -449,7 +456,9 @@ int rt_attn(rt_ctx* ctx, const rt_attn_args* a) {
   const int kernel = prefill_kernel_of(ctx, p, a->dtype);
   if (kernel != 0) {
     std::string err;
-    cudaError_t e = kernel >= 3   ? rt::launch_prefill_tc3(p, kernel == 4, ctx->statusDev, ctx->stream, &err)
+    cudaError_t e = kernel == 5   ? rt::launch_prefill_tc4(p, ctx->statusDev, ctx->statusDev + 1, ctx->smCount,
+                                                           ctx->stream, &err)
+                    : kernel >= 3 ? rt::launch_prefill_tc3(p, kernel == 4, ctx->statusDev, ctx->stream, &err)
                     : kernel == 2 ? rt::launch_prefill_tc2(p, ctx->statusDev, ctx->stream, &err)
                                   : rt::launch_prefill_tc(p, a->dtype, ctx->statusDev, ctx->stream, &err);
     if (e != cudaSuccess)

@@ -327,6 +327,11 @@ bool prefill_tc3_supported(const AttnParams& p, int dtype);
 bool prefill_tc3_pair_supported(const AttnParams& p, int dtype);
 cudaError_t launch_prefill_tc3(const AttnParams& p, bool pair, int* status, cudaStream_t s,
                                std::string* err);
+// Persistent form (one CTA per SM over a queue of units); `work`: two zeroed ints the kernel
+// leaves zeroed.
+bool prefill_tc4_supported(const AttnParams& p, int dtype);
+cudaError_t launch_prefill_tc4(const AttnParams& p, int* status, int* work, int smCount,
+                               cudaStream_t s, std::string* err);
 // Fills kvPerCta/keySlots/stages/splits; returns false with a message when the shape cannot run.
 bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err);
 cudaError_t launch_decode(const DecodeParams& p, int dtype, cudaStream_t s);

@@ -362,11 +362,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         // of a row see the same numbers and so take the same decision).
         const bool grow = mx > mref + kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
-          const float mnew = fmaxf(mref, mx);
+          // A row still at the seed has seen no key: its accumulator row is exactly zero and
+          // needs no pass.  When only such rows have grown, they alone move; the pass over O,
+          // when there is one, moves every row.
+          const bool scaleO = j > 0 && __any_sync(0xffffffffu, grow && mref != kNegSeed);
+          const float mnew = (scaleO || j == 0 || mref == kNegSeed) ? fmaxf(mref, mx) : mref;
           const float f = fast_exp2(mref - mnew);
           mref = mnew;
           l *= f;
-          if (j > 0) {
+          if (scaleO) {
             // O holds the tiles up to j-1: wait for the last P V to land, then scale
             // this thread's share of the accumulator columns.
             ok = mbar_wait(smem_u32(&bars.pvDone[(j - 1) & 1]), ((j - 1) >> 1) & 1, &sAbort);

@@ -222,9 +222,21 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   const uint32_t sQ = smemBase;
   const uint32_t sRing = sQ + C::Q_BYTES;
 
+  // One CTA alone: the Q tile needs nothing but the CTA's coordinates, so the producer's lane
+  // sets up its barrier and starts its copy before the rest of the set-up (tensor memory,
+  // the rows' bands, which read sequence lengths from memory) instead of after it.
+  constexpr bool EARLY_Q = !PAIR && !PADDED;
+  if (EARLY_Q && tid == 8 * 32) {
+    mbar_init(smem_u32(&bars.fullQ), 1);
+    fence_barrier_init();
+    prefetch_tensormap(&mapQ);
+    mbar_expect_tx(smem_u32(&bars.fullQ), C::Q_BYTES);
+    for (int c = 0; c < C::CHUNKS; c++)
+      tma_load_2d(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
+  }
   if (tid == 0) {
     sAbort = 0;
-    mbar_init(smem_u32(&bars.fullQ), 1);
+    if (!EARLY_Q) mbar_init(smem_u32(&bars.fullQ), 1);
     for (int s = 0; s < kMaxSlots; s++) {
       mbar_init(smem_u32(&bars.full[s]), 1);
       mbar_init(smem_u32(&bars.empty[s]), 1);
@@ -315,6 +327,8 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       // own ring (which both CTAs walk in step: same sequence numbers, same slots); all
       // completions are counted on the even CTA's barriers, where the byte counts expected
       // are the pair's.
+      // (a unit that sees no key leaves only after its Q tile has landed)
+      if (EARLY_Q && lane == 0 && nTiles == 0) mbar_wait(smem_u32(&bars.fullQ), 0, &sAbort);
       if (lane == 0 && nTiles > 0) {
         prefetch_tensormap(&mapK);
         prefetch_tensormap(&mapV);
@@ -322,7 +336,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           if (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
           else tma_load_2d(dst, map, x, y, bar);
         };
-        if (!PADDED) {
+        if (!PADDED && !EARLY_Q) {
           prefetch_tensormap(&mapQ);
           if (leader) mbar_expect_tx(smem_u32(&bars.fullQ), C::CTAS * C::Q_BYTES);
           for (int c = 0; c < C::CHUNKS; c++)
@@ -600,10 +614,16 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         l *= fast_exp2(seen - mref);
         seen = mref;
       }
-      if (__any_sync(0xffffffffu, mx > mref + kRescaleThreshold)) {
-        const float mnew = fmaxf(mref, mx);
+      const bool grow = mx > mref + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        // A row whose reference point is still the seed has seen no key in any tile so far:
+        // its accumulator row is exactly zero and needs no pass (the rows of a band's first,
+        // partly masked tile meet their first keys in the second one).  When only such rows
+        // have grown, they alone move; the pass over O, when there is one, moves every row.
+        const bool pass = j > 0 && __any_sync(0xffffffffu, grow && mref != kNegSeed);
+        const float mnew = (pass || j == 0 || mref == kNegSeed) ? fmaxf(mref, mx) : mref;
         const float f = fast_exp2(mref - mnew);
-        if (j > 0) {
+        if (pass) {
           // O holds the tiles up to j-1 once P V(j-1) has landed (the products complete in order)
           ok = __all_sync(0xffffffffu,
                           mbar_wait(smem_u32(&bars.pvDone[(j - 1) & 1]), ((j - 1) >> 1) & 1, &sAbort));
