@@ -968,7 +968,12 @@ bool plan_decode(DecodeParams& p, int dtype, int smCount, std::string* err) {
     if (twoFit) {
       const Geom two = geometry(kSmemBudgetTwoPerSm, lanes);
       const int64_t seqCtas = (int64_t)p.batch * ((p.kvHeads + one.kvPerCta - 1) / one.kvPerCta);
-      const bool fewSequences = lanes > 1 && one.fits && seqCtas * 8 <= smCount;
+      // Fewer blocks than SMs (a decode step of a small batch): a block alone on its SM takes
+      // the whole shared memory for a ring twice as deep or more, and a block's copy rate is
+      // what its ring keeps in flight over the memory latency (measured: 63 GB/s with two
+      // 36 KB stages).
+      const bool alone = seqCtas * (p.hasSecond ? 2 : 1) <= smCount;
+      const bool fewSequences = one.fits && ((lanes > 1 && seqCtas * 8 <= smCount) || alone);
       if (two.fits && !fewSequences) {
         g = two;
         ctasPerSm = 2;

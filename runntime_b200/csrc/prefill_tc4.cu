@@ -43,17 +43,20 @@ namespace {
 using namespace sm100;
 using namespace tc;
 
-constexpr int kThreads4 = 384;
-constexpr int kRegsSoftmax4 = 216, kRegsOther4 = 64;  // 2*128*216 + 128*64 <= 384*168
+#ifndef RT_TC4_ONE_Q
+#define RT_TC4_ONE_Q 256   // head sizes from here up have one Q buffer
+#endif
+constexpr int kThreads4 = 512;
+constexpr int kRegsSoftmax4 = 216, kRegsOther4 = 40;  // 2*128*216 + 2*128*40 = 512*128
 constexpr int BK4 = 128;
 constexpr int kDescSlots = 4;     // queue entries between the scheduler and the other warps
-constexpr int kDescReaders = 11;  // eight softmax warps, the producer and the two MMA issuers
+constexpr int kDescReaders = 15;  // eight softmax warps, the producer, the two MMA issuers, four read-out warps
 
 template <int HD>
 struct Cfg4 {
   static constexpr int CHUNKS = HD / 64;                  // 64-column chunks of a row
   static constexpr int Q_BYTES = BM * HD * 2;
-  static constexpr int Q_BUFS = HD == 256 ? 1 : 2;
+  static constexpr int Q_BUFS = HD >= RT_TC4_ONE_Q ? 1 : 2;
   // Head size 256: K and V tiles arrive in two parts (K: 128 columns each, V: 64 keys each)
   // so that a ring slot is 32 KB.
   static constexpr bool SPLIT = HD == 256;
@@ -63,8 +66,9 @@ struct Cfg4 {
   static constexpr int K_BYTES = K_CHUNKS * BK4 * 128, V_BYTES = CHUNKS * V_ROWS * 128;
   static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
   static constexpr int SLOTS_FIT = (224 * 1024 - Q_BUFS * Q_BYTES) / SLOT_BYTES;
-  static constexpr int SLOTS = SLOTS_FIT > 12 ? 12 : SLOTS_FIT;
-  static constexpr int SMEM = Q_BUFS * Q_BYTES + SLOTS * SLOT_BYTES + 1024;
+  static constexpr int SLOTS_MAX = HD == 64 ? 11 : 12;   // (the barriers of a twelfth slot would not fit)
+  static constexpr int SLOTS = SLOTS_FIT > SLOTS_MAX ? SLOTS_MAX : SLOTS_FIT;
+  static constexpr int SMEM = Q_BUFS * Q_BYTES + SLOTS * SLOT_BYTES;   // 1024-byte aligned by declaration
   // Tensor memory: S | O | P up to head size 128 (two S buffers, 2 x 64 columns of P behind
   // the accumulator); at head size 256 the accumulator takes the upper half and one S buffer
   // shares the lower half with the two P buffers.
@@ -79,20 +83,46 @@ struct Desc4 {
   int item;     // unit index, or -1: no more work
   int kt0;      // first key tile of the unit's band
   int nTiles;   // key tiles in the band (at least one: empty units are not published)
-  int pad;
+  // Padded-batch form, when the unit's 128 rows lie in one sequence: the sequence's first row
+  // and its length, looked up once by the scheduler (else seqBase = -1 and every thread
+  // works its row's band out from the arguments).
+  int seqBase, seqLen;
+  int pad[3];
 };
+
+// The band of one row, from the unit's descriptor where that has the sequence (no division,
+// no load), else as row_band does.
+__device__ __forceinline__ void row_band4(const AttnParams& p, const Desc4& d, int64_t row, int& lo,
+                                          int& end) {
+  lo = 1, end = 0;   // empty
+  if (row >= p.qLen) return;
+  int64_t l64, e64;
+  if (d.seqBase >= 0) {
+    if (row - d.seqBase >= d.seqLen) return;
+    const int64_t qPos = p.qPosOffset + row, last = (int64_t)d.seqBase + d.seqLen - 1;
+    l64 = qPos - p.wl;
+    if (l64 < d.seqBase) l64 = d.seqBase;
+    e64 = qPos + p.wr;
+    if (e64 > last) e64 = last;
+    if (e64 > p.kvLen - 1) e64 = p.kvLen - 1;
+  } else {
+    row_band(p, row, l64, e64);
+  }
+  if (l64 <= e64) lo = (int)l64, end = (int)e64;
+}
 
 template <int NS>
 struct Shared4 {
   uint64_t full[NS], empty[NS];
   uint64_t fullQ[2], qFree[2];
   uint64_t sFull[2], sFree[2], pReady[2][2], pvDone[2];
-  uint64_t oFree;
+  uint64_t oFree, lReady;
   uint64_t descFull[kDescSlots], descFree[kDescSlots];
   Desc4 desc[kDescSlots];
   float mref[BM];        // the rows' reference points (log2 domain), current unit
   float lOther[BM];      // mailbox: the row sums of the warpgroup that did not take the last tile ...
   float seenOther[BM];   // ... and the reference points they are relative to
+  float invL[BM];        // 1 / row sum of the unit whose accumulator is complete, for the read-out warps
   int maxDone[4];        // per warp of a warpgroup: tiles (CTA-wide count) whose max phase is over
   int lWritten[4], lRead[4];   // mailbox sequence numbers, per warp of a warpgroup
   uint32_t tmemBase;
@@ -138,7 +168,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                    int* work) {
   using C = Cfg4<HD>;
   constexpr int BK = BK4, KP = C::KP, VP = C::VP, NS = C::SLOTS;
-  extern __shared__ unsigned char smemRaw[];
+  extern __shared__ __align__(1024) unsigned char smemRaw[];   // swizzled tiles need this alignment
   __shared__ Shared4<NS> sh;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -148,8 +178,12 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   const int group = p.qHeads / p.kvHeads;
   volatile int* abortFlag = &sh.abort;
 
-  const uint32_t smemBase = (smem_u32(smemRaw) + 1023u) & ~1023u;
+  const uint32_t smemBase = smem_u32(smemRaw);
   const uint32_t sRing = smemBase + C::Q_BUFS * C::Q_BYTES;
+  if (smemBase & 1023u) {   // the declared alignment was not honoured: refuse, loudly
+    if (tid == 0) atomicOr(status, kStatusBadState);
+    return;
+  }
 
   if (tid == 0) {
     sh.abort = 0;
@@ -167,6 +201,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       mbar_init(smem_u32(&sh.pvDone[b]), 1);
     }
     mbar_init(smem_u32(&sh.oFree), 4);            // the four warps that read a unit out
+    mbar_init(smem_u32(&sh.lReady), 4);           // the four warps that took the unit's last tile
     for (int s = 0; s < kDescSlots; s++) {
       mbar_init(smem_u32(&sh.descFull[s]), 1);
       mbar_init(smem_u32(&sh.descFree[s]), kDescReaders);
@@ -210,29 +245,32 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         if (lane == 0) item = atomicAdd(work, 1);
         item = __shfl_sync(0xffffffffu, item, 0);
         Desc4 d;
-        d.item = -1, d.kt0 = 0, d.nTiles = 0, d.pad = 0;
+        d.item = -1, d.kt0 = 0, d.nTiles = 0, d.seqBase = -1, d.seqLen = 0;
         if (item < total) {
           const int unit = units - 1 - item % units, h = item / units;
           const int64_t row0 = (int64_t)unit * BM;
+          if (p.seqStride > 0 && !p.segs) {
+            const int64_t b0 = row0 / p.seqStride, base = b0 * p.seqStride;
+            if (row0 + BM <= base + p.seqStride) {   // the unit's rows share a sequence
+              d.seqBase = (int)base;
+              d.seqLen = p.seqLens[b0];
+            }
+          }
           // the band of the unit's 128 rows: four rows per lane
-          int64_t lo = INT64_MAX, end = -1;
+          int lo = INT_MAX, end = -1;
 #pragma unroll
           for (int i = 0; i < BM / 32; i++) {
-            const int64_t row = row0 + lane + 32 * i;
-            if (row < p.qLen) {
-              int64_t l64, e64;
-              row_band(p, row, l64, e64);
-              if (l64 <= e64) {
-                lo = l64 < lo ? l64 : lo;
-                end = e64 > end ? e64 : end;
-              }
+            int l32, e32;
+            row_band4(p, d, row0 + lane + 32 * i, l32, e32);
+            if (l32 <= e32) {
+              lo = min(lo, l32);
+              end = max(end, e32);
             }
           }
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) {
-            const int64_t lo2 = __shfl_xor_sync(0xffffffffu, lo, o), e2 = __shfl_xor_sync(0xffffffffu, end, o);
-            lo = lo2 < lo ? lo2 : lo;
-            end = e2 > end ? e2 : end;
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+            end = max(end, __shfl_xor_sync(0xffffffffu, end, o));
           }
           if (end < 0) {
             // No row of the unit sees a key: its rows are zeros, written here.
@@ -246,11 +284,28 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             continue;
           }
           d.item = item;
-          d.kt0 = (int)(lo / BK);
-          d.nTiles = (int)(end / BK) - d.kt0 + 1;
+          d.kt0 = lo / BK;
+          d.nTiles = end / BK - d.kt0 + 1;
         }
         const int slot = n % kDescSlots;
-        if (n >= kDescSlots) ok = wait(&sh.descFree[slot], (n / kDescSlots) - 1);
+        if (n >= kDescSlots) {
+          // Four units ahead of the slowest reader there is nothing to hurry for: poll
+          // rarely, so that the softmax warps on this scheduler keep their issue slots.
+          const uint32_t bar = smem_u32(&sh.descFree[slot]), parity = (uint32_t)((n / kDescSlots) - 1) & 1u;
+          bool freed = false;
+          for (int i = 0; i < (1 << 21) && !freed; i++) {
+            if (lane == 0) freed = mbar_test_wait(bar, parity);
+            freed = __shfl_sync(0xffffffffu, freed, 0);
+            if (!freed) {
+              if (*abortFlag) break;
+              __nanosleep(1000);
+            }
+          }
+          if (!freed) {
+            *abortFlag = 1;
+            ok = false;
+          }
+        }
         if (!ok) break;
         if (lane == 0) {
           sh.desc[slot] = d;
@@ -441,9 +496,69 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         seqBase += d.nTiles * (KP + VP);
         qn++;
       }
+    } else if (warp >= 12) {
+      // ------------------------------ read-out ------------------------------
+      // Warp 12 + i reads lanes 32 i .. 32 i + 31 of tensor memory (one query row per lane):
+      // when a unit's last product has landed, its rows are scaled by 1/l, rounded to f16 and
+      // stored, 16 columns at a time; after the last load the accumulator belongs to the next
+      // unit.
+      const int rowInTile = (warp - 12) * 32 + lane;
+      const uint32_t oCol = tmem + ((uint32_t)((warp - 12) * 32) << 16) + C::O_COL;
+      const bool wide = (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0;   // rows start on 32 bytes
+      int qn = 0, tG = 0;
+      bool ok = true;
+      for (int n = 0; ok; n++) {
+        Desc4 d;
+        if (!next_desc(n, d) || d.item < 0) break;
+        const int unit = units - 1 - d.item % units, h = d.item / units;
+        const int64_t row = (int64_t)unit * BM + rowInTile;
+        const int tLast = tG + d.nTiles - 1;
+        ok = wait(&sh.lReady, qn);
+        if (!ok) break;
+        const float invL = sh.invL[rowInTile];
+        ok = wait(&sh.pvDone[tLast & 1], tLast >> 1);
+        if (!ok) break;
+        tc_fence_after_sync();
+        TC_TRACE(30, tLast);
+        __half* out = static_cast<__half*>(p.out) + row * ((int64_t)p.qHeads * HD) + (int64_t)h * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(oCol + c, o);
+          tmem_wait_ld();
+          if (c == HD - 16) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.oFree));
+          }
+          uint32_t pk[8];
+#pragma unroll
+          for (int x = 0; x < 16; x += 2) {
+            const __half2 hp = __floats2half2_rn(__uint_as_float(o[x]) * invL,
+                                                 __uint_as_float(o[x + 1]) * invL);
+            pk[x / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+          if (row < p.qLen) {
+            // a 32-byte store where the rows allow it: a row's piece is then one full sector
+            // per request (the stores of a warp go to 32 different rows)
+            if (wide) {
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out + c),
+                           "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                           "r"(pk[6]), "r"(pk[7])
+                           : "memory");
+            } else {
+              reinterpret_cast<uint4*>(out + c)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              reinterpret_cast<uint4*>(out + c)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+          }
+        }
+        TC_TRACE(31, tLast);
+        tG += d.nTiles;
+        qn++;
+      }
     }
   } else {
-    // ------------------------------ softmax + read-out ------------------------
+    // ------------------------------ softmax ------------------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax4));
     const int g = warp >> 2, w = warp & 3;
     const int rowInTile = tid & 127;
@@ -452,29 +567,28 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const uint32_t pCol = tmem + laneBase + C::P_COL + g * 64;
     const uint32_t oCol = tmem + laneBase + C::O_COL;
     const float seed = kNegSeed;
-    int tG = 0, qn = 0, mailSeq = 0;   // tiles, units, units with two or more tiles so far
+    int tG = 0;   // tiles of the units before this one (the CTA-wide tile count)
     bool ok = true;
-    for (int n = 0; ok; n++) {
-      Desc4 d;
-      if (!next_desc(n, d) || d.item < 0) break;
-      const int unit = units - 1 - d.item % units, h = d.item / units;
-      const int64_t row = (int64_t)unit * BM + rowInTile;
-      int lo = 1, end = 0;   // this thread's row: empty unless it sees a key
-      if (row < p.qLen) {
-        int64_t l64, e64;
-        row_band(p, row, l64, e64);
-        if (l64 <= e64) lo = (int)l64, end = (int)e64;
+    for (int n = 0; ok; n++) {   // n: units so far (every published unit has a tile)
+      int lo, end;   // this thread's row: lo > end unless it sees a key
+      int tEnd, keyBase;
+      float start;
+      {
+        Desc4 d;
+        if (!next_desc(n, d) || d.item < 0) break;
+        const int unit = units - 1 - d.item % units, h = d.item / units;
+        row_band4(p, d, (int64_t)unit * BM + rowInTile, lo, end);
+        tEnd = tG + d.nTiles;
+        keyBase = (d.kt0 - tG) * BK;                 // key0 of tile t is keyBase + t * BK
+        start = p.sinks ? p.sinks[h] : seed;         // sinks arrive in the log2 domain
       }
-      const int nTiles = d.nTiles;
-      const int first = tG & 1, lastOwner = (tG + nTiles - 1) & 1;
-      const float start = p.sinks ? p.sinks[h] : seed;   // sinks arrive in the log2 domain
-      float seen = start;                                 // the reference point l is relative to
-      float l = (p.sinks && g == first) ? 1.f : 0.f;
+      float seen = start;                            // the reference point l is relative to
+      float l = (p.sinks && g == (tG & 1)) ? 1.f : 0.f;   // the sink counts once, in the first tile's warpgroup
       float mref = start;
 #pragma unroll 1
-      for (int j = (g - tG) & 1; j < nTiles && ok; j += 2) {
-        const int t = tG + j;
-        const int key0 = (d.kt0 + j) * BK;
+      for (int t = tG + ((g - tG) & 1); t < tEnd && ok; t += 2) {
+        const int key0 = keyBase + t * BK;
+        const bool firstTile = t == tG;
         TC_TRACE(0, t);
         ok = wait(&sh.sFull[g], t >> 1);
         if (!ok) break;  // the whole warp leaves together
@@ -529,7 +643,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
         TC_TRACE(22, t);
         // a unit's first tile starts the rows' reference points; later tiles read them
-        if (j > 0) mref = sh.mref[rowInTile];
+        if (!firstTile) mref = sh.mref[rowInTile];
         if (mref != seen) {  // the other warpgroup moved the reference point since this one last looked
           l *= fast_exp2(seen - mref);
           seen = mref;
@@ -540,8 +654,8 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           // A row whose reference point is still the seed has seen no key in any tile so far:
           // its accumulator row is exactly zero and needs no pass.  When only such rows have
           // grown, they alone move; the pass over O, when there is one, moves every row.
-          const bool pass = j > 0 && __any_sync(0xffffffffu, grow && mref != seed);
-          const float mnew = (pass || j == 0 || mref == seed) ? fmaxf(mref, mx) : mref;
+          const bool pass = !firstTile && __any_sync(0xffffffffu, grow && mref != seed);
+          const float mnew = (pass || firstTile || mref == seed) ? fmaxf(mref, mx) : mref;
           const float f = fast_exp2(mref - mnew);
           if (pass) {
             // O holds the unit's tiles up to j-1 once P V(t-1) has landed (in-order products)
@@ -563,7 +677,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           l *= f;
           mref = seen = mnew;
         }
-        if (anyGrow || j == 0) sh.mref[rowInTile] = mref;
+        if (anyGrow || firstTile) sh.mref[rowInTile] = mref;
         __syncwarp();
         if (lane == 0) st_release_shared(&sh.maxDone[w], t + 1);
         TC_TRACE(3, t);
@@ -580,19 +694,23 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mref, -mref);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-          uint32_t pk[32];
+          // (stored 32 keys at a time: sixteen packed registers live instead of thirty-two)
 #pragma unroll
-          for (int c = 0; c < 64; c += 2) {
-            const int cc = half * 64 + c;
-            const float2 tt = fma2(make_float2(__uint_as_float(sv[cc]), __uint_as_float(sv[cc + 1])),
-                                   scale2, shift2);
-            const float2 pe = exp2_pair(tt, c >> 1);
-            sum2[(c >> 1) & 3] = add2(sum2[(c >> 1) & 3], pe);
-            const __half2 hp = __floats2half2_rn(pe.x, pe.y);
-            pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          for (int q = 0; q < 2; q++) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const int cc = half * 64 + q * 32 + c;
+              const float2 tt = fma2(make_float2(__uint_as_float(sv[cc]), __uint_as_float(sv[cc + 1])),
+                                     scale2, shift2);
+              const float2 pe = exp2_pair(tt, (q * 32 + c) >> 1);
+              sum2[(c >> 1) & 3] = add2(sum2[(c >> 1) & 3], pe);
+              const __half2 hp = __floats2half2_rn(pe.x, pe.y);
+              pk[c / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+            }
+            tmem_st16(pCol + half * 32 + q * 16, pk);
           }
           TC_TRACE(7 + half, t);
-          tmem_st32(pCol + half * 32, pk);
           tmem_wait_st();
           tc_fence_before_sync();
           __syncwarp();
@@ -605,60 +723,33 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if (!ok) break;
 
       // ---- the unit's row sums meet in the warpgroup that took its last tile ----
-      if (nTiles >= 2 && g != lastOwner) {
+      // (one message per unit, also when the other warpgroup had no tile in it)
+      if (g != ((tEnd - 1) & 1)) {
         // mailbox: free once the previous message has been read
-        ok = wait_count(&sh.lRead[w], mailSeq, abortFlag);
+        ok = wait_count(&sh.lRead[w], n, abortFlag);
         if (!ok) break;
         sh.lOther[rowInTile] = l;
         sh.seenOther[rowInTile] = seen;
         __syncwarp();
-        if (lane == 0) st_release_shared(&sh.lWritten[w], mailSeq + 1);
-      }
-      if (g == lastOwner) {
+        if (lane == 0) st_release_shared(&sh.lWritten[w], n + 1);
+      } else {
         // `seen` is the rows' final reference point: this warpgroup's max phase was the last
-        if (nTiles >= 2) {
-          ok = wait_count(&sh.lWritten[w], mailSeq + 1, abortFlag);
-          if (!ok) break;
-          l += sh.lOther[rowInTile] * fast_exp2(sh.seenOther[rowInTile] - seen);
-          __syncwarp();
-          if (lane == 0) st_release_shared(&sh.lRead[w], mailSeq + 1);
-        }
-        const int tLast = tG + nTiles - 1;
-        ok = wait(&sh.pvDone[tLast & 1], tLast >> 1);
+        ok = wait_count(&sh.lWritten[w], n + 1, abortFlag);
         if (!ok) break;
-        tc_fence_after_sync();
-        TC_TRACE(30, tLast);
-        const float invL = (l > 0.f && lo <= end) ? 1.f / l : 0.f;  // a row that saw no key: zeros
-        __half* out = static_cast<__half*>(p.out) + row * ((int64_t)p.qHeads * HD) + (int64_t)h * HD;
-#pragma unroll
-        for (int c = 0; c < HD; c += 32) {
-          uint32_t o[32];
-          tmem_ld32(oCol + c, o);
-          tmem_wait_ld();
-          if (c == HD - 32) {
-            // the accumulator is in registers: the next unit's first product may overwrite it
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sh.oFree));
-          }
-          if (row < p.qLen) {
-            uint4 pkd[4];
-            uint32_t* wds = reinterpret_cast<uint32_t*>(pkd);
-#pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const __half2 hp = __floats2half2_rn(__uint_as_float(o[x]) * invL,
-                                                   __uint_as_float(o[x + 1]) * invL);
-              wds[x / 2] = *reinterpret_cast<const uint32_t*>(&hp);
-            }
-#pragma unroll
-            for (int v = 0; v < 4; v++) reinterpret_cast<uint4*>(out + c)[v] = pkd[v];
-          }
+        l += sh.lOther[rowInTile] * fast_exp2(sh.seenOther[rowInTile] - seen);
+        __syncwarp();
+        if (lane == 0) st_release_shared(&sh.lRead[w], n + 1);
+        // The read-out warps take it from here: 1/l per row (zero for a row that saw no key),
+        // once they are through with the previous unit's.
+        if (n >= 1) {
+          ok = wait(&sh.oFree, n - 1);
+          if (!ok) break;
         }
-        TC_TRACE(31, tLast);
+        sh.invL[rowInTile] = (l > 0.f && lo <= end) ? 1.f / l : 0.f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.lReady));
       }
-      if (nTiles >= 2) mailSeq++;
-      tG += nTiles;
-      qn++;
+      tG = tEnd;
     }
   }
 
