@@ -10,13 +10,15 @@
 // there the fill and the drain are most of the time.  Here the roles of that kernel — a
 // TMA producer warp, one warp issuing S = Q K^T, one issuing O += P V, two softmax
 // warpgroups taking alternate key tiles — each run their own loop over the units a
-// scheduler warp draws from a device-wide counter, and every barrier's phase follows a
-// count that runs on across units.  The tile sequence of the CTA is one long alternation of
-// the two warpgroups: while the warpgroup that took a unit's last tile finishes its
-// softmax, waits for the last P V and writes the unit out, the producer has fetched the
-// next unit's Q and K, the S issuer has computed its first scores and the other warpgroup
-// is in its first softmax.  Only the accumulator is not doubled: the first P V of a unit
-// waits until the previous unit's rows have been read out of tensor memory.
+// scheduler warp draws from a device-wide counter, every barrier's phase follows a count
+// that runs on across units, and a fourth warpgroup does nothing but read finished units
+// out of tensor memory.  The tile sequence of the CTA is one long alternation of the two
+// softmax warpgroups: while the one that took a unit's last tile finishes its softmax, the
+// producer has fetched the next unit's Q and K, the S issuer has computed its first scores
+// and the other warpgroup is in its first softmax; when the last P V has landed, the
+// read-out warps scale the rows by 1/l (handed over through shared memory), round and store
+// them.  Only the accumulator is not doubled: the first P V of a unit waits until the
+// previous unit's rows have left tensor memory.
 //
 // Work queue: unit i is row tile (units - 1 - i % units) of head i / units (long rows
 // first under a causal mask); the scheduler warp draws i with one atomicAdd, works out
@@ -368,10 +370,10 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                 tma_load_2d(dst + c * (C::V_ROWS * 128), &mapV, xKV + c * 64, key0 + part * C::V_ROWS, bar);
             }
           };
-          // The first K tile does not wait for the Q buffer, which is free once the S products
-          // of the unit that used it have completed.
-          load_k(0);
-          if (ok && qn >= C::Q_BUFS)
+          // Q goes out before the first K tile: K has to wait for ring slots, which the unit
+          // before holds until its last products are through, and the S issuer needs Q first.
+          // (With one Q buffer it is free once the last S of the unit before has completed.)
+          if (qn >= C::Q_BUFS)
             ok = mbar_wait(smem_u32(&sh.qFree[qb]), (uint32_t)((qn / C::Q_BUFS) - 1) & 1u, abortFlag);
           if (ok) {
             const uint32_t bar = smem_u32(&sh.fullQ[qb]), dst = smemBase + qb * C::Q_BYTES;
@@ -379,6 +381,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             for (int c = 0; c < C::CHUNKS; c++)
               tma_load_2d(dst + c * (BM * 128), &mapQ, h * HD + c * 64, row0, bar);
           }
+          if (ok) load_k(0);
           for (int j = 0; j < d.nTiles && ok; j++) {
             if (j + 1 < d.nTiles) load_k(j + 1);
             if (ok) load_v(j);
@@ -662,14 +665,15 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             ok = wait(&sh.pvDone[(t - 1) & 1], (t - 1) >> 1);
             if (!ok) break;
             tc_fence_after_sync();
-#pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-              uint32_t o[32];
-              tmem_ld32(oCol + c, o);
+            // (16 columns at a time: the tile's 128 scores stay in registers meanwhile)
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 16) {
+              uint32_t o[16];
+              tmem_ld16(oCol + c, o);
               tmem_wait_ld();
 #pragma unroll
-              for (int x = 0; x < 32; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
-              tmem_st32(oCol + c, o);
+              for (int x = 0; x < 16; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
+              tmem_st16(oCol + c, o);
             }
             tmem_wait_st();
             tc_fence_before_sync();
