@@ -66,10 +66,9 @@ RT_API int rt_ctx_destroy(rt_ctx* ctx);
  * restores the context's stream. */
 RT_API int rt_ctx_set_stream(rt_ctx* ctx, void* cuda_stream, int external);
 /* Context options.  RT_OPT_PREFILL_TC (default 1): route eligible f16 prefill
- * shapes to a tensor-core kernel of the library's choice (head sizes up to 128,
- * narrow heads included: one 128-row query tile per thread block whose key tiles
- * alternate between two softmax warpgroups; head size 256: one tile, one
- * warpgroup).  0 sends every prefill to the FP32-pipe kernel; 2 forces one tile
+ * shapes to a tensor-core kernel of the library's choice (head sizes 64, 128,
+ * 256 and the narrow heads: one 128-row query tile per thread block whose key
+ * tiles alternate between two softmax warpgroups).  0 sends every prefill to the FP32-pipe kernel; 2 forces one tile
  * with one warpgroup, 3 two tiles per block, 4 the alternating form, 5 the
  * alternating form on pairs of thread blocks that share every K/V tile, 6 the
  * alternating form as one persistent thread block per SM over a queue of query

@@ -402,13 +402,12 @@ static int prefill_kernel_of(const rt_ctx* ctx, const rt::AttnParams& p, int dty
   if ((ctx->useTc == 4 || ctx->useTc == 5) && tc3) return 3;
   if (!rt::prefill_tc_supported(p, dtype)) return (tc3 && ctx->useTc == 1) ? 3 : 0;  // heads narrower than 64
   if (ctx->useTc == 3 && rt::prefill_tc2_supported(p, dtype)) return 2;
-  // The library's own choice: the alternating-warpgroup kernel up to head size 128 (measured
-  // on the large causal prefill, a second of back-to-back launches: 914 TFLOP/s against 858
-  // for two tiles per block and 770 for one tile with one softmax warpgroup); head size 256
-  // stays on the one-tile kernel, whose 64-key tiles keep three tiles in flight where this
-  // one's 128-key tiles leave its ring one and a quarter (545 against 478 TFLOP/s on the
-  // sliding-window GQA prefill).
-  if (ctx->useTc == 1 && tc3 && p.hd <= 128) return 3;
+  // The library's own choice: the alternating-warpgroup kernel (measured, a second of
+  // back-to-back launches: the large causal prefill at head size 128, 914 TFLOP/s against 858
+  // for two tiles per block and 770 for one tile with one softmax warpgroup; the sliding-window
+  // GQA prefill at head size 256 over padded sequences, 584 against 545 for one tile — once a
+  // unit past a sequence's end stopped costing it 9 us of 4-byte zero stores).
+  if (ctx->useTc == 1 && tc3) return 3;
   return 1;
 }
 

@@ -482,10 +482,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           }
         }
       }
-    } else if (nTiles == 0 && row < p.qLen) {
-      const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int c = 0; c < OW; c += 8) *reinterpret_cast<uint4*>(out + c) = z;
+    } else if (nTiles == 0) {
+      // No row of this unit sees a key (in a padded batch: every unit past a sequence's end):
+      // zeros, consecutive threads on consecutive 16-byte pieces of a row.
+      constexpr int kPerRow = HD / 8;
+      __half* base = static_cast<__half*>(p.out) + row0 * ((int64_t)p.qHeads * HD) + (int64_t)h * HD;
+      for (int i = tid; i < BM * kPerRow; i += C::SOFTMAX_THREADS) {
+        const int r = i / kPerRow, c = i - r * kPerRow;
+        if (row0 + r < p.qLen)
+          reinterpret_cast<uint4*>(base + (int64_t)r * p.qHeads * HD)[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
   }
 

@@ -55,6 +55,9 @@ namespace {
 using namespace sm100;
 using namespace tc;
 
+#ifndef RT_TC3_CHECK_EMPTY
+#define RT_TC3_CHECK_EMPTY 1   // look a padded batch's length up before asking for the Q tile
+#endif
 #ifndef RT_TC3_RELAXED
 #define RT_TC3_RELAXED 0
 #endif
@@ -226,13 +229,23 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   // sets up its barrier and starts its copy before the rest of the set-up (tensor memory,
   // the rows' bands, which read sequence lengths from memory) instead of after it.
   constexpr bool EARLY_Q = !PAIR && !PADDED;
+  // (In a padded batch the units past a sequence's end see no key and must not pay for a Q
+  // tile: the lane looks the length up first.)
+  bool earlyQ = false;
   if (EARLY_Q && tid == 8 * 32) {
     mbar_init(smem_u32(&bars.fullQ), 1);
     fence_barrier_init();
-    prefetch_tensormap(&mapQ);
-    mbar_expect_tx(smem_u32(&bars.fullQ), C::Q_BYTES);
-    for (int c = 0; c < C::CHUNKS; c++)
-      tma_load_2d(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
+    earlyQ = true;
+    if (RT_TC3_CHECK_EMPTY && p.seqStride > 0 && !p.segs) {
+      const int64_t b0 = row0 / p.seqStride;
+      earlyQ = row0 - b0 * p.seqStride < p.seqLens[b0];
+    }
+    if (earlyQ) {
+      prefetch_tensormap(&mapQ);
+      mbar_expect_tx(smem_u32(&bars.fullQ), C::Q_BYTES);
+      for (int c = 0; c < C::CHUNKS; c++)
+        tma_load_2d(sQ + c * (BM * 128), &mapQ, h * HD + c * 64, (int)row0, smem_u32(&bars.fullQ));
+    }
   }
   if (tid == 0) {
     sAbort = 0;
@@ -327,8 +340,8 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       // own ring (which both CTAs walk in step: same sequence numbers, same slots); all
       // completions are counted on the even CTA's barriers, where the byte counts expected
       // are the pair's.
-      // (a unit that sees no key leaves only after its Q tile has landed)
-      if (EARLY_Q && lane == 0 && nTiles == 0) mbar_wait(smem_u32(&bars.fullQ), 0, &sAbort);
+      // (a unit that sees no key leaves only after the Q tile it asked for has landed)
+      if (EARLY_Q && lane == 0 && nTiles == 0 && earlyQ) mbar_wait(smem_u32(&bars.fullQ), 0, &sAbort);
       if (lane == 0 && nTiles > 0) {
         prefetch_tensormap(&mapK);
         prefetch_tensormap(&mapV);
@@ -336,7 +349,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           if (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
           else tma_load_2d(dst, map, x, y, bar);
         };
-        if (!PADDED && !EARLY_Q) {
+        if (!PADDED && !earlyQ) {
           prefetch_tensormap(&mapQ);
           if (leader) mbar_expect_tx(smem_u32(&bars.fullQ), C::CTAS * C::Q_BYTES);
           for (int c = 0; c < C::CHUNKS; c++)
@@ -754,10 +767,24 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           }
         }
       }
-    } else if (nTiles == 0 && row < p.qLen) {
-      // no row of this unit sees a key
-      for (int c = g * (hd / 2); c < (g + 1) * (hd / 2); c += 2)
-        *reinterpret_cast<__half2*>(out + c) = __floats2half2_rn(0.f, 0.f);
+    } else if (nTiles == 0) {
+      // No row of this unit sees a key (in a padded batch: every unit past a sequence's end).
+      if (PADDED) {
+        if (row < p.qLen)
+          for (int c = g * (hd / 2); c < (g + 1) * (hd / 2); c += 2)
+            *reinterpret_cast<__half2*>(out + c) = __floats2half2_rn(0.f, 0.f);
+      } else {
+        // 16-byte stores, consecutive threads on consecutive pieces of a row: a thread per
+        // row writing its own row in 4-byte pieces made such a unit cost ~9 us of store
+        // traffic, a third of a padded batch's time.
+        constexpr int kPerRow = HD / 8;
+        __half* base = static_cast<__half*>(p.out) + row0 * ((int64_t)p.qHeads * HD) + (int64_t)h * HD;
+        for (int i = tid; i < BM * kPerRow; i += 256) {
+          const int r = i / kPerRow, c = i - r * kPerRow;
+          if (row0 + r < p.qLen)
+            reinterpret_cast<uint4*>(base + (int64_t)r * p.qHeads * HD)[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
     }
   }
 

@@ -60,7 +60,7 @@ def test_c5_causal_prefill_one_full_sequence(ex, mode, route):
     assert worst <= 2e-3          # the benchmark contract's bar for f16: max absolute error
 
 
-@pytest.mark.parametrize("mode", [1, 4])
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("wl,wr", [(512, 512), (None, None)])
 def test_c3_gqa_prefill_full_sequence_with_padded_neighbours(ex, mode, wl, wr):
     """2048 rows, 3 query heads on 1 kv head of 256, f16, N(0, 0.5): a full-length
