@@ -55,6 +55,9 @@ namespace {
 using namespace sm100;
 using namespace tc;
 
+#ifndef RT_TC3_WIDE_STORES
+#define RT_TC3_WIDE_STORES 1  // 32-byte stores in the read-out where the rows allow
+#endif
 #ifndef RT_TC3_CHECK_EMPTY
 #define RT_TC3_CHECK_EMPTY 1   // look a padded batch's length up before asking for the Q tile
 #endif
@@ -731,6 +734,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     l = sL[0][rowInTile] + sL[1][rowInTile];
     const int64_t row = row0 + rowInTile;
     __half* out = static_cast<__half*>(p.out) + row * ((int64_t)p.qHeads * hd) + (int64_t)h * hd;
+    const bool wide = !PADDED && (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0;   // rows start on 32 bytes
     if (nTiles > 0 && ok && !sAbort) {
       ok = mbar_wait(smem_u32(&bars.pvDone[(nTiles - 1) & 1]), ((nTiles - 1) >> 1) & 1, &sAbort);
       if (ok) {
@@ -761,8 +765,20 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                                                      __uint_as_float(o[x + 1]) * invL);
                 wds[x / 2] = *reinterpret_cast<const uint32_t*>(&hp);
               }
+              if (RT_TC3_WIDE_STORES && wide) {
+                // a row's piece is then one full 32-byte sector per request instead of half of
+                // one (the stores of a warp go to 32 different rows)
 #pragma unroll
-              for (int v = 0; v < 4; v++) reinterpret_cast<uint4*>(out + c)[v] = pkd[v];
+                for (int v = 0; v < 2; v++)
+                  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(
+                                   out + c + 16 * v),
+                               "r"(wds[8 * v]), "r"(wds[8 * v + 1]), "r"(wds[8 * v + 2]), "r"(wds[8 * v + 3]),
+                               "r"(wds[8 * v + 4]), "r"(wds[8 * v + 5]), "r"(wds[8 * v + 6]), "r"(wds[8 * v + 7])
+                               : "memory");
+              } else {
+#pragma unroll
+                for (int v = 0; v < 4; v++) reinterpret_cast<uint4*>(out + c)[v] = pkd[v];
+              }
             }
           }
         }
