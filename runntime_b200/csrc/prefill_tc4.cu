@@ -46,10 +46,7 @@ using namespace sm100;
 using namespace tc;
 
 #ifndef RT_TC4_ONE_Q
-#define RT_TC4_ONE_Q 256   // head sizes from here up have one Q buffer
-#endif
-#ifndef RT_TC4_SPLIT_REGS
-#define RT_TC4_SPLIT_REGS 0
+#define RT_TC4_ONE_Q 256   // head sizes from here up have one Q buffer (128: one more ring slot, +2 % measured)
 #endif
 constexpr int kThreads4 = 512;
 constexpr int kRegsSoftmax4 = 216, kRegsOther4 = 40;  // 2*128*216 + 2*128*40 = 512*128
@@ -239,13 +236,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   };
 
   if (warp >= 8) {
-#if RT_TC4_SPLIT_REGS
-    // (variant: the issuing warpgroup takes what the read-out warpgroup can spare)
-    if (warp >= 12) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(32));
-    else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(48));
-#else
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther4));
-#endif
     if (warp == 11) {
       // ------------------------------ scheduler ------------------------------
       const int64_t outStride = (int64_t)p.qHeads * HD;
