@@ -154,7 +154,9 @@ typedef struct {
 RT_API int rt_attn(rt_ctx* ctx, const rt_attn_args* args);
 
 /* Which kernel rt_attn would run for these arguments: writes a short static
- * name ("prefill_simt", "prefill_tc", "decode") into *route. */
+ * name into *route: "decode", "prefill_simt" (FP32 pipes), or one of the
+ * tensor-core kernels "prefill_tc3" (the default), "prefill_tc3_pair",
+ * "prefill_tc4", "prefill_tc2", "prefill_tc" (see RT_OPT_PREFILL_TC). */
 RT_API int rt_attn_route(rt_ctx* ctx, const rt_attn_args* args, const char** route);
 
 /* ---- batched single-token decode over KV caches -----------------------------
